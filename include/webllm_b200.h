@@ -1,0 +1,168 @@
+/*
+ * webllm_b200 — C ABI of the B200 (sm_100a) implementation of webllm's quantized-linear path.
+ *
+ * This header is the whole drop-in boundary: plain pointers, sizes and integer handles, no C++ or
+ * framework types. A TypeScript host binds it through N-API / FFI, a Python host through ctypes.
+ * Each entry point names the function of the reference (intplusplus/webllm, TypeScript) whose job it
+ * takes over.
+ *
+ * Conventions
+ *   - Every function returns a wb_status (0 = ok, negative = error class). The text of the last error
+ *     on the calling thread is wb_last_error(); where the reference throws with a message, the text
+ *     is the reference's. Nothing throws or aborts across this boundary.
+ *   - One context per GPU. Calls on one context are not re-entrant; different contexts may be driven
+ *     from different threads.
+ *   - Tensors are addressed as (arena, byte offset), offsets 256-byte aligned — the reference's Tensor
+ *     {buffer, offset, length, shape} (src/gpu/buffer.ts:11-18, ALIGN = 256 at :3-9).
+ *   - All device work is ordered on the context's stream (this replaces the reference's passBreak(),
+ *     src/model/qwen.ts:551-559). wb_synchronize and wb_download are the only blocking calls.
+ *   - Host pointers are borrowed for the duration of the call only.
+ */
+#ifndef WEBLLM_B200_H
+#define WEBLLM_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define WB_API __attribute__((visibility("default")))
+
+typedef struct wb_context wb_context;
+typedef struct wb_qwen wb_qwen;
+typedef int32_t wb_handle; /* index of a registered weight; < 0 = none */
+
+typedef enum {
+    WB_OK = 0,
+    WB_ERR_BAD_ARG = -1,     /* validation failure (the reference's `throw new Error`) */
+    WB_ERR_OOM = -2,         /* arena or device memory exhausted */
+    WB_ERR_CUDA = -3,        /* a CUDA runtime / driver call failed */
+    WB_ERR_NCCL = -4,
+    WB_ERR_TIMEOUT = -5,     /* a bounded device-side wait ran out */
+    WB_ERR_NOT_FOUND = -6,   /* unknown weight name ("缺少 f16 权重") */
+    WB_ERR_EXISTS = -7,      /* duplicate weight name ("权重已存在") */
+    WB_ERR_UNSUPPORTED = -8
+} wb_status;
+
+typedef enum { WB_F32 = 0, WB_F16 = 1 } wb_dtype;
+typedef enum { WB_ARENA_WEIGHTS = 0, WB_ARENA_ACT = 1 } wb_arena;
+
+/* Which kernel a linear call uses (see wb_plan_query). */
+typedef enum {
+    WB_KERNEL_GEMV_MMA = 1,   /* M <= 32: weights streamed once, register unpack, warp-level MMA, split-K */
+    WB_KERNEL_GEMM_TC = 2,    /* tcgen05 / TMEM GEMM, TMA-fed, dequant in shared memory */
+    WB_KERNEL_GENERIC = 3,    /* shape-agnostic CUDA kernel for ragged sizes (K%8, N%4, group%32 != 0) */
+    WB_KERNEL_DENSE_GEMV = 4  /* fp16 [N,K] weight, M <= 8 */
+} wb_kernel_kind;
+
+typedef struct {
+    int32_t kernel;      /* wb_kernel_kind */
+    int32_t split_k;     /* number of K slices (1 = unsplit); the planGemvSplit analogue */
+    int32_t grid_x, grid_y, grid_z;
+    int32_t block;       /* threads per block */
+    int32_t tile_m, tile_n; /* GEMM_TC: tokens x output columns per CTA; otherwise 0 */
+    int32_t launches;    /* kernels this call enqueues */
+    uint64_t scratch_bytes; /* split-K partial sums / fp16 staging taken from the context workspace */
+} wb_plan;
+
+/* ---- library ---------------------------------------------------------------------------------- */
+WB_API const char *wb_last_error(void);
+WB_API int wb_version(void);
+
+/* ---- context: one per GPU. Replaces initGpu (src/gpu/device.ts:40-98). ------------------------- */
+WB_API int wb_context_create(int device, wb_context **out);
+WB_API int wb_context_destroy(wb_context *ctx);
+/* Use a caller-owned cudaStream_t (e.g. the host framework's current stream); NULL restores the
+ * context's own stream. */
+WB_API int wb_set_stream(wb_context *ctx, void *cuda_stream);
+WB_API int wb_get_stream(wb_context *ctx, void **cuda_stream);
+WB_API int wb_synchronize(wb_context *ctx);
+/* Number of kernels this context has launched since creation (profilers rebuild the launch list from
+ * wb_plan_query, as the reference's decode profiler does from planGemvSplit,
+ * src/tests/perf/profile-decode.ts:55-82). */
+WB_API int wb_launch_count(wb_context *ctx, uint64_t *count);
+
+/* ---- arenas. Replaces Arena / alignTo (src/gpu/arena.ts:17-59, src/gpu/buffer.ts:3-9). ---------- */
+/* One slab per arena, either allocated here or adopted from the caller (no copy, not freed here). */
+WB_API int wb_arena_create(wb_context *ctx, int arena, uint64_t bytes);
+WB_API int wb_arena_adopt(wb_context *ctx, int arena, void *device_ptr, uint64_t bytes);
+/* Arena.allocFloat32 generalised to bytes: returns a 256-byte-aligned offset. */
+WB_API int wb_arena_alloc(wb_context *ctx, int arena, uint64_t bytes, uint64_t *offset);
+/* Arena.reset(): everything allocated since the last reset is recycled. The weight arena refuses
+ * while weights are registered. */
+WB_API int wb_arena_reset(wb_context *ctx, int arena);
+WB_API int wb_arena_used(wb_context *ctx, int arena, uint64_t *used, uint64_t *capacity);
+/* Partial reset: hands back everything allocated after the point where `used` was `mark`. */
+WB_API int wb_arena_rewind(wb_context *ctx, int arena, uint64_t mark);
+WB_API int wb_arena_base(wb_context *ctx, int arena, void **device_ptr);
+/* queue.writeBuffer / readbackF32 (src/gpu/buffer.ts:37-52,123-145). */
+WB_API int wb_upload(wb_context *ctx, int arena, uint64_t offset, const void *host, uint64_t bytes);
+WB_API int wb_download(wb_context *ctx, int arena, uint64_t offset, void *host, uint64_t bytes);
+
+/* ---- weights. Replaces QwenGpt.allocF16 / writeF16Chunk / uploadF16 / uploadF32
+ *      (src/model/qwen.ts:247-276) and the GPTQ half of loadQwenWeights
+ *      (src/weights/qwen-loader.ts:55-67). Names are the reference's ("L3.qW", "embed", ...). ------- */
+
+/* Takes the three GPTQ tensors as they sit in the checkpoint and keeps them packed on the device:
+ *   qweight  bytes of I32 [ceil(K/8), N]    nibble j of word [r,n] = input channel 8r+j
+ *   qzeros   bytes of I32 [ceil(K/g), ceil(N/8)] or NULL (symmetric, zero point 8); stored value is zero-1
+ *   scales   fp16 bits [ceil(K/g), N]
+ * Validates exactly what dequantizeGptqInt4 validates (src/weights/quant.ts:46-79): bits == 4,
+ * group > 0, in/out > 0, byte lengths, group % 8 == 0. */
+WB_API int wb_gptq_register(wb_context *ctx, const char *name, const void *qweight, uint64_t qweight_bytes,
+                            const void *qzeros, uint64_t qzeros_bytes, const uint16_t *scales_f16,
+                            uint64_t scales_len, int64_t in_features, int64_t out_features, int64_t group_size,
+                            int bits, wb_handle *out);
+/* Registers the column slice [col_begin, col_begin+col_count) of a GPTQ linear (output-column
+ * sharding across GPUs). col_begin and col_count must be multiples of 8 so no zero word is split.
+ * No counterpart in the reference, which has one device. */
+WB_API int wb_gptq_register_cols(wb_context *ctx, const char *name, const void *qweight, uint64_t qweight_bytes,
+                                 const void *qzeros, uint64_t qzeros_bytes, const uint16_t *scales_f16,
+                                 uint64_t scales_len, int64_t in_features, int64_t out_features,
+                                 int64_t group_size, int bits, int64_t col_begin, int64_t col_count,
+                                 wb_handle *out);
+/* allocF16(name, length) with the logical shape [rows, cols] (rows*cols == length). */
+WB_API int wb_f16_alloc(wb_context *ctx, const char *name, int64_t rows, int64_t cols, wb_handle *out);
+/* writeF16Chunk: f32 -> fp16 round-to-nearest-even with the reference's edge rules
+ * (f32ToF16Bits, src/gpu/buffer.ts:57-100: NaN -> 0x7e00, |x| < 2^-24 -> +-0). */
+WB_API int wb_f16_write_chunk(wb_context *ctx, wb_handle h, int64_t elem_offset, const float *data, int64_t n);
+/* Same, from fp16 bits as stored in a safetensors file (no f32 round trip). */
+WB_API int wb_f16_write_bits(wb_context *ctx, wb_handle h, int64_t elem_offset, const uint16_t *bits, int64_t n);
+/* uploadF32(name, data): norm weights and biases. */
+WB_API int wb_f32_upload(wb_context *ctx, const char *name, const float *data, int64_t n, wb_handle *out);
+WB_API int wb_weight_lookup(wb_context *ctx, const char *name, wb_handle *out);
+/* Drops the most recently registered weight and returns its arena space (stack order). Lets a host
+ * implement the pure function dequantizeGptqInt4(params) -> array as register / export / pop. */
+WB_API int wb_weight_pop(wb_context *ctx);
+/* readWeightF16Bytes (src/model/qwen.ts:527-531): raw fp16 bits of a dense fp16 weight. */
+WB_API int wb_read_weight_f16(wb_context *ctx, wb_handle h, int64_t elem_offset, int64_t n, uint16_t *out_bits);
+/* weightBytes (src/model/qwen.ts:222-242): device bytes held by registered weights. */
+WB_API int wb_weight_bytes(wb_context *ctx, uint64_t *bytes);
+
+/* ---- dequant export. Replaces dequantizeGptqInt4 (src/weights/quant.ts:42-118) and its fp16 device
+ *      copy (writeF16, src/gpu/buffer.ts:103-120). Output [N, K] row-major in the activation arena:
+ *      f32 equal to the reference's Float32Array bit for bit, fp16 equal to f32ToF16Bits of it. ---- */
+WB_API int wb_gptq_dequant_f32(wb_context *ctx, wb_handle h, uint64_t out_offset);
+WB_API int wb_gptq_dequant_f16(wb_context *ctx, wb_handle h, uint64_t out_offset);
+
+/* ---- linear. Replaces QwenGpt.gemm (src/model/qwen.ts:568-618) and the four WGSL kernels behind it
+ *      (gemm_gemv_f16, gemm_gemv_split_f16, gemm_gemv_split_reduce, gemm_nt_f16_from_f32).
+ *      C[M,N] = A[M,K] . W[N,K]^T (+ bias[N]); A at a_offset and C at c_offset in the activation
+ *      arena, row-major, dense; bias is an f32 weight handle or -1 and is added once, after the full-K
+ *      sum. act_dtype / out_dtype are wb_dtype. `exact` != 0 asks for the fp32-activation mode: f32
+ *      activations keep ~22 bits through the tensor-core paths (hi/lo split) instead of being rounded
+ *      to fp16 as the reference's tiled GEMM does (gemm_nt_f16_from_f32.wgsl:58-62). ---------------- */
+WB_API int wb_linear(wb_context *ctx, wb_handle weight, uint64_t a_offset, uint64_t c_offset, wb_handle bias,
+                     int64_t M, int act_dtype, int out_dtype, int exact);
+/* planGemvSplit (src/model/qwen.ts:61-74) generalised: which kernel, how many K slices, what grid. */
+WB_API int wb_plan_query(wb_context *ctx, wb_handle weight, int64_t M, int act_dtype, int exact, wb_plan *out);
+/* Forces a kernel (wb_kernel_kind) and/or split for the next wb_linear calls; 0 = planner's choice.
+ * Used by tests to cover every path at every shape, as the reference's tests drive the split kernel with
+ * explicit S (src/tests/kernels.ts:1378-1400). */
+WB_API int wb_plan_override(wb_context *ctx, int kernel, int split_k);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* WEBLLM_B200_H */

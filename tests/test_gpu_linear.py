@@ -1,0 +1,184 @@
+"""GPU parity: the fused int4 linear (GEMV / split-K / small batch / ragged) and the fp16 dense GEMV
+against gemmNTRef on the oracle's dequantised weights, through the C ABI."""
+import numpy as np
+import pytest
+
+from helpers import assert_close, oracle_weight, register, run_linear
+from webllm_b200 import WebllmError, _lib, synthetic
+
+pytestmark = pytest.mark.gpu
+
+F32_RTOL = 1e-5   # fp32-activation mode
+F16_RTOL = 1e-3   # fp16 activations
+
+
+def _x(M, K, seed, f16=False):
+    x = np.random.default_rng(seed).standard_normal((M, K)).astype(np.float32)
+    return x.astype(np.float16) if f16 else x
+
+
+def test_single_linear_benchmark_case(gpu, oracle):
+    """K=896 -> N=4864, batch 1, group 128, stored zeros in {7,8}, scales |N(0.01,0.003)|, x ~ N(0,1), seed 0
+    (draw order: qweight, qzeros, scales, x)."""
+    rng = np.random.default_rng(0)
+    t = synthetic.random_gptq(896, 4864, 128, rng=rng)
+    x = rng.standard_normal((1, 896)).astype(np.float32)
+    h = register(gpu, "up_proj", t)
+    ref = oracle.gemm_nt_ref(x, oracle_weight(oracle, t), 1, 4864, 896)
+    p = gpu.plan(h, 1)
+    assert p["kernel_name"] == "gemv_mma"
+    assert_close(oracle, run_linear(gpu, h, x, 1, 4864), ref, F32_RTOL, "f32 activations")
+    x16 = x.astype(np.float16)
+    ref16 = oracle.gemm_nt_ref(x16.astype(np.float32), oracle_weight(oracle, t), 1, 4864, 896)
+    assert_close(oracle, run_linear(gpu, h, x16, 1, 4864, act="f16"), ref16, F16_RTOL, "f16 activations")
+    # the reference's own GEMV bar (atol 1e-5 + rtol 1e-4, src/tests/kernels.ts:61-74,1267)
+    assert oracle.check_tolerance(run_linear(gpu, h, x, 1, 4864), ref, 1e-5, 1e-4).ok
+
+
+@pytest.mark.parametrize("name,K,N", [(n, k, nn) for n, (k, nn) in synthetic.QWEN05B_SHAPES.items() if n in ("q", "k", "gate", "down")]
+                         + [("q7b", 3584, 3584), ("kv7b", 3584, 512), ("down7b", 18944, 3584)])
+@pytest.mark.parametrize("M", [1, 2, 3, 4, 8, 9, 16, 32])
+def test_small_batch_all_shapes(gpu, oracle, name, K, N, M):
+    if K == 18944 and M not in (1, 8):
+        pytest.skip("one small and one larger batch are enough at the largest K")
+    key = f"sb_{name}"
+    try:
+        h = gpu.weight(key)
+        t = test_small_batch_all_shapes.cache[key]
+    except WebllmError:
+        t = synthetic.random_gptq(K, N, 128, seed=K + N, zeros="any")
+        h = register(gpu, key, t)
+        test_small_batch_all_shapes.cache[key] = t
+    W = test_small_batch_all_shapes.wcache.setdefault(key, oracle_weight(oracle, t))
+    bias_key = f"sbb_{name}"
+    try:
+        hb = gpu.weight(bias_key)
+    except WebllmError:
+        hb = gpu.f32_upload(bias_key, np.random.default_rng(N).standard_normal(N).astype(np.float32))
+    bias = np.random.default_rng(N).standard_normal(N).astype(np.float32)
+    gpu.plan_override(_lib.WB_KERNEL_GEMV_MMA, 0)
+    try:
+        x = _x(M, K, M * 31 + K)
+        ref = oracle.gemm_nt_ref(x, W, M, N, K, bias, threads=oracle.max_threads())
+        assert_close(oracle, run_linear(gpu, h, x, M, N, hb), ref, F32_RTOL, f"{name} M={M} f32")
+        x16 = _x(M, K, M * 31 + K + 1, f16=True)
+        ref = oracle.gemm_nt_ref(x16.astype(np.float32), W, M, N, K, None, threads=oracle.max_threads())
+        got = run_linear(gpu, h, x16, M, N, None, act="f16", out="f16")
+        assert_close(oracle, got, ref, F16_RTOL, f"{name} M={M} f16 in/out")
+    finally:
+        gpu.plan_override(0, 0)
+
+
+test_small_batch_all_shapes.cache = {}
+test_small_batch_all_shapes.wcache = {}
+
+
+@pytest.mark.parametrize("K,N,S", [(896, 128, 2), (896, 128, 7), (896, 896, 4), (4864, 896, 8), (4864, 896, 38), (896, 4864, 3)])
+def test_split_k_is_deterministic_and_adds_bias_once(gpu, oracle, K, N, S):
+    """Forced split counts (the reference tests S in {3, 4, 8}, src/tests/kernels.ts:1378-1400): the sum of the
+    slices plus the bias, added once at the reduce (gemm_gemv_split_reduce.wgsl:36-38), bitwise repeatable."""
+    t = synthetic.random_gptq(K, N, 128, seed=S, zeros="any")
+    h = register(gpu, f"split{K}x{N}s{S}", t)
+    hb = gpu.f32_upload(f"splitb{K}x{N}s{S}", np.full(N, 1000.0, np.float32))
+    W = oracle_weight(oracle, t)
+    x = _x(1, K, S)
+    gpu.plan_override(_lib.WB_KERNEL_GEMV_MMA, S)
+    try:
+        assert gpu.plan(h, 1)["split_k"] == min(S, -(-K // 128))
+        ref = oracle.gemm_nt_ref(x, W, 1, N, K, np.full(N, 1000.0, np.float32))
+        a = run_linear(gpu, h, x, 1, N, hb)
+        assert_close(oracle, a - 1000.0, ref - 1000.0, 2e-4, "split with bias")  # 1000 costs f32 ulps
+        outs = [run_linear(gpu, h, x, 1, N, None) for _ in range(3)]
+        assert all(np.array_equal(o.view(np.uint32), outs[0].view(np.uint32)) for o in outs)
+        assert_close(oracle, outs[0], oracle.gemm_nt_ref(x, W, 1, N, K), F32_RTOL, "split no bias")
+        x3 = _x(3, K, S + 1)
+        assert_close(oracle, run_linear(gpu, h, x3, 3, N, None), oracle.gemm_nt_ref(x3, W, 3, N, K), F32_RTOL, "split M=3")
+    finally:
+        gpu.plan_override(0, 0)
+
+
+def test_planner_never_splits_when_columns_fill_the_gpu(gpu):
+    t = synthetic.random_gptq(896, 151936 // 8, 128, seed=9)
+    h = register(gpu, "wide", t)
+    p = gpu.plan(h, 1)
+    assert p["split_k"] == 1 and p["launches"] == 1 and p["scratch_bytes"] == 0
+
+
+@pytest.mark.parametrize("M,N,K,group", [(1, 53, 42, 8), (1, 5, 16, 8), (3, 53, 40, 8), (37, 53, 41, 8), (2, 12, 136, 32)])
+def test_ragged_shapes_take_the_generic_kernel(gpu, oracle, M, N, K, group):
+    """Odd sizes as in the reference's tests (N=53,K=42; M=37,N=53,K=41): K % 8, N % 4, small groups."""
+    t = synthetic.random_gptq(K, N, group, seed=M + N + K, zeros="any")
+    h = register(gpu, f"rag{M}_{N}_{K}", t)
+    assert gpu.plan(h, M)["kernel_name"] == "generic"
+    bias = np.random.default_rng(1).standard_normal(N).astype(np.float32)
+    hb = gpu.f32_upload(f"ragb{M}_{N}_{K}", bias)
+    W = oracle_weight(oracle, t)
+    x = _x(M, K, 3)
+    got = run_linear(gpu, h, x, M, N, hb, exact=True)
+    assert_close(oracle, got, oracle.gemm_nt_ref(x, W, M, N, K, bias), 1e-6, "generic exact")
+    if M > 1:
+        # default mode rounds f32 activations to fp16 for M > 1, like gemm_nt_f16_from_f32.wgsl:58-62
+        got = run_linear(gpu, h, x, M, N, hb)
+        assert_close(oracle, got, oracle.gemm_nt_ref(oracle.round_f16(x), W, M, N, K, bias), 1e-6, "generic rounded A")
+
+
+def test_reference_seeded_gemv_cases_with_dense_f16_weights(gpu, oracle, golden):
+    """testGemmGemvF16 / testGemmGemvSplitF16 / testGemmNtF16 (src/tests/kernels.ts:1261-1269, 1378-1400,
+    545-585): the reference's seeds and its own tolerance (atol 1e-5, rtol 1e-4; 5e-3 for the f16 GEMM),
+    with the dense fp16 weight the reference uploads."""
+    for i, c in enumerate(golden["gemv_cases"]):
+        M, N, K = c["M"], c["N"], c["K"]
+        rng = oracle.Rng(c["seed"])
+        A = rng.random_f32(M * K)
+        B = oracle.round_f16(rng.random_f32(N * K))
+        bias = rng.random_f32(N)
+        if c["round_a"]:
+            A = oracle.round_f16(A)
+        h = gpu.f16_alloc(f"ref_dense_{i}", N, K)
+        gpu.f16_write_chunk(h, 0, B)
+        hb = gpu.f32_upload(f"ref_bias_{i}", bias)
+        rtol = 5e-3 if c["kind"] == "gemm_nt_f16" else 1e-4
+        for b, key in ((hb, "want_bias_bits"), (None, "want_nobias_bits")):
+            got = run_linear(gpu, h, A, M, N, b, exact=True)
+            want = np.array(c[key], np.uint32).view(np.float32).reshape(M, N)
+            r = oracle.check_tolerance(got, want, 1e-5, rtol)
+            assert r.ok, (c["kind"], N, K, r)
+
+
+@pytest.mark.parametrize("M", [1, 2, 5, 8])
+def test_dense_f16_gemv_lm_head_shape(gpu, oracle, M):
+    """Tied lm_head: fp16 [V, 896]; V trimmed to keep the CPU side quick, with a ragged tail of rows."""
+    V, K = 151936 // 16 + 3, 896
+    try:
+        h = gpu.weight("lm_head_small")
+    except WebllmError:
+        rng = np.random.default_rng(4)
+        test_dense_f16_gemv_lm_head_shape.W = rng.normal(0, 0.02, size=(V, K)).astype(np.float16)
+        h = gpu.f16_alloc("lm_head_small", V, K)
+        gpu.f16_write_bits(h, 0, test_dense_f16_gemv_lm_head_shape.W)
+    W = test_dense_f16_gemv_lm_head_shape.W.astype(np.float32)
+    assert gpu.plan(h, M)["kernel_name"] == "dense_gemv"
+    x = _x(M, K, M)
+    ref = oracle.gemm_nt_ref(x, W, M, V, K, threads=oracle.max_threads())
+    assert_close(oracle, run_linear(gpu, h, x, M, V), ref, F32_RTOL, "dense f32")
+    x16 = _x(M, K, M + 9, f16=True)
+    ref = oracle.gemm_nt_ref(x16.astype(np.float32), W, M, V, K, threads=oracle.max_threads())
+    assert_close(oracle, run_linear(gpu, h, x16, M, V, act="f16"), ref, F32_RTOL, "dense f16 in")
+
+
+def test_argument_errors(gpu):
+    t = synthetic.random_gptq(128, 8, 128, seed=1)
+    h = register(gpu, "argerr", t)
+    gpu.arena.reset()
+    A = gpu.arena.alloc(128)
+    Cc = gpu.arena.alloc(8)
+    with pytest.raises(WebllmError, match="M must be positive"):
+        gpu.linear(h, A, Cc, None, 0)
+    hb = gpu.f32_upload("argerr_bias", np.zeros(9, np.float32))
+    with pytest.raises(WebllmError, match="bias"):
+        gpu.linear(h, A, Cc, hb, 1)
+    from webllm_b200 import Tensor
+    with pytest.raises(WebllmError, match="outside arena"):
+        gpu.linear(h, Tensor(gpu.arena.capacity - 256, 128), Cc, None, 1)
+    with pytest.raises(WebllmError, match="缺少 f16 权重"):
+        gpu.linear(hb, A, Cc, None, 1)

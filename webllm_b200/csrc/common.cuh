@@ -1,0 +1,122 @@
+// Shared declarations of the webllm_b200 CUDA library: context layout, error plumbing, device helpers.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "../../include/webllm_b200.h"
+
+namespace wb {
+
+// ---------------------------------------------------------------- errors
+void set_error(const char *fmt, ...);
+int fail(int code, const char *fmt, ...);
+
+#define WB_CUDA(expr)                                                                         \
+    do {                                                                                      \
+        cudaError_t _e = (expr);                                                              \
+        if (_e != cudaSuccess)                                                                \
+            return wb::fail(WB_ERR_CUDA, "CUDA error %s at %s:%d: %s", cudaGetErrorName(_e), \
+                            __FILE__, __LINE__, cudaGetErrorString(_e));                      \
+    } while (0)
+
+#define WB_CHECK(expr)          \
+    do {                        \
+        int _s = (expr);        \
+        if (_s != WB_OK) return _s; \
+    } while (0)
+
+// ---------------------------------------------------------------- weights
+enum class WeightKind : int { Gptq = 1, DenseF16 = 2, F32 = 3 };
+
+struct Weight {
+    std::string name;
+    WeightKind kind;
+    int64_t K = 0, N = 0;     // in_features, out_features (DenseF16: cols, rows; F32: N = length)
+    int64_t group = 0;        // GPTQ group size
+    int64_t pack_rows = 0;    // ceil(K/8)
+    int64_t groups = 0;       // ceil(K/group)
+    int64_t zcols = 0;        // ceil(N/8)
+    uint64_t off_main = 0;    // qweight / fp16 matrix / f32 vector (byte offset in the weight arena)
+    uint64_t off_zeros = 0;   // qzeros (valid if has_zeros)
+    uint64_t off_scales = 0;  // fp16 scales
+    bool has_zeros = false;
+    uint64_t bytes = 0;
+};
+
+struct ArenaState {
+    char *base = nullptr;
+    uint64_t capacity = 0, used = 0;
+    bool owned = false;
+};
+
+constexpr uint64_t kAlign = 256;
+inline uint64_t align_up(uint64_t n, uint64_t a = kAlign) { return (n + a - 1) / a * a; }
+
+// Split-K partial sums, fp16 staging of activations and arrival counters live here; sized at context
+// creation so that no linear call allocates.
+constexpr uint64_t kWorkspaceBytes = 96ull << 20;
+constexpr int kMaxCounters = 16384;
+
+}  // namespace wb
+
+struct wb_context {
+    int device = 0;
+    int sm_count = 148;
+    cudaStream_t own_stream = nullptr;
+    cudaStream_t stream = nullptr;
+    wb::ArenaState arena[2];
+    std::vector<wb::Weight> weights;
+    std::unordered_map<std::string, int> by_name;
+    char *workspace = nullptr;       // kWorkspaceBytes of scratch
+    unsigned *counters = nullptr;    // kMaxCounters arrival counters, zero between calls
+    int *status_word = nullptr;      // device-side error flag for bounded waits (mapped pinned host memory)
+    int *status_host = nullptr;
+    uint64_t launches = 0;
+    int force_kernel = 0, force_split = 0;
+    void *tmap_encode = nullptr;     // cuTensorMapEncodeTiled, resolved at context creation
+};
+
+namespace wb {
+
+inline char *arena_ptr(wb_context *ctx, int arena, uint64_t off) { return ctx->arena[arena].base + off; }
+int check_range(wb_context *ctx, int arena, uint64_t off, uint64_t bytes, const char *what);
+int get_weight(wb_context *ctx, wb_handle h, Weight **out);
+
+// kernels' host entry points (one per .cu file)
+int launch_dequant(wb_context *ctx, const Weight &w, void *out, bool f16);
+int launch_f32_to_f16_ref(wb_context *ctx, const float *in, __half *out, int64_t n);
+int plan_linear(wb_context *ctx, const Weight &w, int64_t M, int act_dtype, int exact, wb_plan *plan);
+int launch_linear(wb_context *ctx, const Weight &w, const void *A, void *C, const float *bias, int64_t M,
+                  int act_dtype, int out_dtype, int exact);
+
+// ---------------------------------------------------------------- device helpers
+#ifdef __CUDACC__
+
+// f32 -> fp16 bits with the rules of the reference's f32ToF16Bits (src/gpu/buffer.ts:57-100):
+// IEEE round-to-nearest-even, except NaN -> 0x7e00 and |x| < 2^-24 -> signed zero.
+__device__ __forceinline__ unsigned short f32_to_f16_bits_ref(float f)
+{
+    if (f != f) return 0x7e00;
+    unsigned short h = __half_as_ushort(__float2half_rn(f));
+    if (fabsf(f) < 5.9604644775390625e-8f) h &= 0x8000;
+    return h;
+}
+
+__device__ __forceinline__ uint4 ldg_stream_v4(const void *p)
+{
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+#endif  // __CUDACC__
+
+}  // namespace wb

@@ -1,0 +1,607 @@
+// Decode-side linear kernels: the fused int4 GEMV / small-batch kernel, the fp16 dense GEMV (tied
+// lm_head) and the shape-agnostic kernel for ragged sizes. Together with gemm_tc.cu they replace the four
+// WGSL kernels behind QwenGpt.gemm (src/model/qwen.ts:568-618): gemm_gemv_f16.wgsl,
+// gemm_gemv_split_f16.wgsl, gemm_gemv_split_reduce.wgsl and gemm_nt_f16_from_f32.wgsl.
+#include "common.cuh"
+
+namespace wb {
+
+// =====================================================================================================
+// Fused int4 GEMV for 1 <= M <= 32  (C[M,N] = A[M,K] . W[N,K]^T + bias)
+//
+// HBM-bound: every packed word is read exactly once with 128-bit loads straight from the checkpoint
+// layout qweight[K/8, N] (a warp reads 4 packed rows x 32 columns = four full 128-byte lines per load
+// instruction). A scalar-FMA unpack needs >= 3 issue slots per weight, which at 2 weights per byte is
+// more than the SMs can issue at HBM speed, so the products run on the warp-level tensor-core MMA
+// (m16n8k16, fp16 in, f32 accumulate) with the weight tile as the 16-row operand and up to 8 activation
+// rows as the 8-column operand: ~1.3 issue slots per weight.
+//
+//   * unpack: (w & 0x000f000f) | 0x6400'6400 is the half2 (1024+q_j, 1024+q_{j+4}); the 0x00f000f0 mask
+//     gives (1024+16 q). Subtracting 1024+zero (resp. one fma with 1/16 and -(64+zero)) yields the exact
+//     integers q - zero in fp16. Per-group scales are applied in f32 to the group's partial sum, so no
+//     product is ever rounded to fp16.
+//   * the MMA only needs the two operands to agree on which k sits in which slot, so the nibble order
+//     that the masks produce is used as is and the activations are staged in shared memory in the same
+//     order: 16 bytes per (row m, packed row r) holding (x0,x4)(x1,x5)(x2,x6)(x3,x7) as half2.
+//   * f32 activations are split into hi + lo fp16 halves (two MMAs per tile), which keeps ~22 bits of
+//     them: the reference's GEMV reads A as f32 (gemm_gemv_f16.wgsl:45-58). fp16 activations need one.
+//   * split-K: grid.y slices of whole 128-k chunks. Each slice writes its partial tile to the workspace;
+//     the last CTA to arrive for a column tile (arrival counter, no waiting) adds the slices in slice
+//     order and the bias once, so the result does not depend on scheduling
+//     (cf. gemm_gemv_split_reduce.wgsl:36-38).
+// =====================================================================================================
+
+struct GemvParams {
+    const uint32_t *qw;
+    const uint32_t *qz;  // nullable
+    const __half *sc;
+    const void *x;
+    void *out;
+    const float *bias;  // nullable
+    float *partial;
+    unsigned *counters;
+    int M, N, K;
+    int pack_rows, zcols;
+    int chunks;         // ceil(pack_rows / 16)
+    int chunks_per_split;
+    int group_chunks;   // group / 128
+    int S;
+    int wn, wk;         // warps across columns / across k
+    int x_f16, out_f16;
+    int xs_stride;      // uint4 per staged activation row
+};
+
+__device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                          uint32_t b0, uint32_t b1)
+{
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t h2_as_u32(__half2 h) { return *reinterpret_cast<uint32_t *>(&h); }
+__device__ __forceinline__ __half2 u32_as_h2(uint32_t u) { return *reinterpret_cast<__half2 *>(&u); }
+
+// 8 nibbles of `w` -> h[0]=(q0,q4) h[1]=(q1,q5) h[2]=(q2,q6) h[3]=(q3,q7), each minus the zero point.
+__device__ __forceinline__ void unpack_word(uint32_t w, __half2 zsub, __half2 zfma, uint32_t (&h)[4])
+{
+    const __half2 sixteenth = __float2half2_rn(0.0625f);
+    const uint32_t lo0 = (w & 0x000f000fu) | 0x64006400u;
+    const uint32_t hi0 = (w & 0x00f000f0u) | 0x64006400u;
+    w >>= 8;
+    const uint32_t lo1 = (w & 0x000f000fu) | 0x64006400u;
+    const uint32_t hi1 = (w & 0x00f000f0u) | 0x64006400u;
+    h[0] = h2_as_u32(__hsub2(u32_as_h2(lo0), zsub));
+    h[1] = h2_as_u32(__hfma2(u32_as_h2(hi0), sixteenth, zfma));
+    h[2] = h2_as_u32(__hsub2(u32_as_h2(lo1), zsub));
+    h[3] = h2_as_u32(__hfma2(u32_as_h2(hi1), sixteenth, zfma));
+}
+
+template <int MB, bool EXACT>
+__global__ void __launch_bounds__(512) gptq_gemv_mma_kernel(const GemvParams p)
+{
+    extern __shared__ uint4 smem_u4[];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int wn = warp % p.wn, wk = warp / p.wn;
+    const int nthreads = blockDim.x;
+
+    const int ch_begin = blockIdx.y * p.chunks_per_split;
+    const int ch_end = min(p.chunks, ch_begin + p.chunks_per_split);
+    const int row_begin = ch_begin * 16;
+    const int rows_cta = max(0, min(p.pack_rows, ch_end * 16) - row_begin);
+
+    uint4 *xs_hi = smem_u4;
+    uint4 *xs_lo = smem_u4 + (size_t)p.M * p.xs_stride;  // EXACT only
+
+    // ---- stage this slice of the activations, permuted to the MMA's k-slot order ----
+    for (int idx = tid; idx < p.M * rows_cta; idx += nthreads) {
+        const int m = idx / rows_cta, rl = idx - m * rows_cta;
+        const int64_t k0 = (int64_t)(row_begin + rl) * 8;
+        float v[8];
+        if (p.x_f16) {
+            const uint4 raw = *reinterpret_cast<const uint4 *>((const __half *)p.x + (int64_t)m * p.K + k0);
+            const __half2 *h = reinterpret_cast<const __half2 *>(&raw);
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const float2 f = __half22float2(h[j]);
+                v[2 * j] = f.x;
+                v[2 * j + 1] = f.y;
+            }
+        } else {
+            const float4 a = *reinterpret_cast<const float4 *>((const float *)p.x + (int64_t)m * p.K + k0);
+            const float4 b = *reinterpret_cast<const float4 *>((const float *)p.x + (int64_t)m * p.K + k0 + 4);
+            v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
+        }
+        __half hi[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) hi[j] = __float2half_rn(v[j]);
+        uint4 o;
+        o.x = h2_as_u32(__halves2half2(hi[0], hi[4]));
+        o.y = h2_as_u32(__halves2half2(hi[1], hi[5]));
+        o.z = h2_as_u32(__halves2half2(hi[2], hi[6]));
+        o.w = h2_as_u32(__halves2half2(hi[3], hi[7]));
+        xs_hi[m * p.xs_stride + rl] = o;
+        if constexpr (EXACT) {
+            __half lo[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++) lo[j] = __float2half_rn(v[j] - __half2float(hi[j]));
+            o.x = h2_as_u32(__halves2half2(lo[0], lo[4]));
+            o.y = h2_as_u32(__halves2half2(lo[1], lo[5]));
+            o.z = h2_as_u32(__halves2half2(lo[2], lo[6]));
+            o.w = h2_as_u32(__halves2half2(lo[3], lo[7]));
+            xs_lo[m * p.xs_stride + rl] = o;
+        }
+    }
+    __syncthreads();
+
+    // ---- main loop: this warp owns columns [c0w, c0w+32), this thread columns c .. c+3 ----
+    const int c0w = (blockIdx.x * p.wn + wn) * 32;
+    const int c = c0w + 4 * g;
+    const bool col_ok = c < p.N;  // N % 4 == 0: a thread's four columns are in or out together
+
+    float tot[MB][2][4];
+#pragma unroll
+    for (int mb = 0; mb < MB; mb++)
+#pragma unroll
+        for (int s = 0; s < 2; s++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) tot[mb][s][i] = 0.f;
+
+    const uint4 zero4 = make_uint4(0, 0, 0, 0);
+    for (int ch = ch_begin + wk; ch < ch_end; ch += p.wk) {
+        // issue the chunk's four 128-bit loads first
+        uint4 wq[4];
+#pragma unroll
+        for (int st = 0; st < 4; st++) {
+            const int r = ch * 16 + st * 4 + t;
+            wq[st] = (col_ok && r < p.pack_rows) ? ldg_stream_v4(p.qw + (int64_t)r * p.N + c) : zero4;
+        }
+        const int G = ch / p.group_chunks;
+        float scale[4] = {0.f, 0.f, 0.f, 0.f};
+        __half2 zsub[4], zfma[4];
+        {
+            uint32_t znib = 0x7777u;  // stored zero 7 -> zero point 8 when the checkpoint has no qzeros
+            if (col_ok) {
+                const uint2 sraw = *reinterpret_cast<const uint2 *>(p.sc + (int64_t)G * p.N + c);
+                const float2 s01 = __half22float2(u32_as_h2(sraw.x)), s23 = __half22float2(u32_as_h2(sraw.y));
+                scale[0] = s01.x, scale[1] = s01.y, scale[2] = s23.x, scale[3] = s23.y;
+                if (p.qz) znib = p.qz[(int64_t)G * p.zcols + (c >> 3)] >> ((c & 7) * 4);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const float z = (float)(((znib >> (4 * j)) & 15u) + 1u);
+                zsub[j] = __float2half2_rn(1024.f + z);
+                zfma[j] = __float2half2_rn(-(64.f + z));
+            }
+        }
+
+        float acc[MB][2][4];
+#pragma unroll
+        for (int mb = 0; mb < MB; mb++)
+#pragma unroll
+            for (int s = 0; s < 2; s++)
+#pragma unroll
+                for (int i = 0; i < 4; i++) acc[mb][s][i] = 0.f;
+
+#pragma unroll
+        for (int st = 0; st < 4; st++) {
+            const int rl = ch * 16 + st * 4 + t - row_begin;
+            const bool row_ok = rl < rows_cta;
+            uint32_t h0[4], h1[4], h2[4], h3[4];
+            unpack_word(wq[st].x, zsub[0], zfma[0], h0);
+            unpack_word(wq[st].y, zsub[1], zfma[1], h1);
+            unpack_word(wq[st].z, zsub[2], zfma[2], h2);
+            unpack_word(wq[st].w, zsub[3], zfma[3], h3);
+#pragma unroll
+            for (int mb = 0; mb < MB; mb++) {
+                const int m = mb * 8 + g;
+                const bool ok = row_ok && m < p.M;
+                const uint4 xb = ok ? xs_hi[m * p.xs_stride + rl] : zero4;
+                mma_16816(acc[mb][0], h0[0], h1[0], h0[1], h1[1], xb.x, xb.y);
+                mma_16816(acc[mb][0], h0[2], h1[2], h0[3], h1[3], xb.z, xb.w);
+                mma_16816(acc[mb][1], h2[0], h3[0], h2[1], h3[1], xb.x, xb.y);
+                mma_16816(acc[mb][1], h2[2], h3[2], h2[3], h3[3], xb.z, xb.w);
+                if constexpr (EXACT) {
+                    const uint4 xl = ok ? xs_lo[m * p.xs_stride + rl] : zero4;
+                    mma_16816(acc[mb][0], h0[0], h1[0], h0[1], h1[1], xl.x, xl.y);
+                    mma_16816(acc[mb][0], h0[2], h1[2], h0[3], h1[3], xl.z, xl.w);
+                    mma_16816(acc[mb][1], h2[0], h3[0], h2[1], h3[1], xl.x, xl.y);
+                    mma_16816(acc[mb][1], h2[2], h3[2], h2[3], h3[3], xl.z, xl.w);
+                }
+            }
+        }
+        // accumulator rows g / g+8 of set s are columns c+2s / c+2s+1
+#pragma unroll
+        for (int mb = 0; mb < MB; mb++)
+#pragma unroll
+            for (int s = 0; s < 2; s++) {
+                tot[mb][s][0] = fmaf(scale[2 * s], acc[mb][s][0], tot[mb][s][0]);
+                tot[mb][s][1] = fmaf(scale[2 * s], acc[mb][s][1], tot[mb][s][1]);
+                tot[mb][s][2] = fmaf(scale[2 * s + 1], acc[mb][s][2], tot[mb][s][2]);
+                tot[mb][s][3] = fmaf(scale[2 * s + 1], acc[mb][s][3], tot[mb][s][3]);
+            }
+    }
+
+    // ---- reduce over the wk warps that share a column tile (fixed order), then write / split-K ----
+    __syncthreads();  // xs is dead; reuse shared memory as float red[wk][wn][MB*8][32]
+    float *red = reinterpret_cast<float *>(smem_u4);
+    constexpr int J = MB * 8;
+#pragma unroll
+    for (int mb = 0; mb < MB; mb++)
+#pragma unroll
+        for (int s = 0; s < 2; s++)
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+                red[((wk * p.wn + wn) * J + (mb * 2 + s) * 4 + i) * 32 + lane] = tot[mb][s][i];
+    __syncthreads();
+
+    const int tile_cols = p.wn * 32;
+    const int n_base = blockIdx.x * tile_cols;
+    const int outputs = p.M * tile_cols;
+    const bool direct = p.S == 1;
+    for (int idx = tid; idx < outputs; idx += nthreads) {
+        const int m = idx / tile_cols, cl_all = idx - m * tile_cols;
+        const int n = n_base + cl_all;
+        if (n >= p.N) continue;
+        const int w_n = cl_all >> 5, cl = cl_all & 31;
+        const int gg = cl >> 2, s = (cl & 3) >> 1, hi = cl & 1;
+        const int mb = m >> 3, tt = (m & 7) >> 1, i = hi * 2 + (m & 1);
+        const int src_lane = gg * 4 + tt, j = (mb * 2 + s) * 4 + i;
+        float v = 0.f;
+        for (int k = 0; k < p.wk; k++) v += red[((k * p.wn + w_n) * J + j) * 32 + src_lane];
+        if (direct) {
+            if (p.bias) v += p.bias[n];
+            if (p.out_f16) ((__half *)p.out)[(int64_t)m * p.N + n] = __float2half_rn(v);
+            else ((float *)p.out)[(int64_t)m * p.N + n] = v;
+        } else {
+            p.partial[((int64_t)blockIdx.y * p.M + m) * p.N + n] = v;
+        }
+    }
+    if (direct) return;
+
+    __shared__ int is_last;
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const unsigned prev = atomicAdd(&p.counters[blockIdx.x], 1u);
+        is_last = (prev == (unsigned)(p.S - 1));
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    for (int idx = tid; idx < outputs; idx += nthreads) {
+        const int m = idx / tile_cols;
+        const int n = n_base + (idx - m * tile_cols);
+        if (n >= p.N) continue;
+        float v = 0.f;
+        for (int s = 0; s < p.S; s++) v += __ldcg(&p.partial[((int64_t)s * p.M + m) * p.N + n]);
+        if (p.bias) v += p.bias[n];
+        if (p.out_f16) ((__half *)p.out)[(int64_t)m * p.N + n] = __float2half_rn(v);
+        else ((float *)p.out)[(int64_t)m * p.N + n] = v;
+    }
+    if (tid == 0) p.counters[blockIdx.x] = 0u;  // leave the counters clean for the next call
+}
+
+// =====================================================================================================
+// fp16 dense GEMV (tied lm_head / embed, [N, K] row-major), 1 <= M <= 8. One warp per output row pair,
+// lanes stride K in 16-byte chunks, activations in shared memory as f32, f32 accumulate, shuffle reduce.
+// Replaces gemm_gemv_f16.wgsl for dense weights (src/gpu/kernels/gemm/gemm_gemv_f16.wgsl:36-69).
+// =====================================================================================================
+template <int MM>
+__global__ void __launch_bounds__(256) dense_gemv_f16_kernel(const __half *__restrict__ W, const void *__restrict__ x,
+                                                             void *__restrict__ out, const float *__restrict__ bias,
+                                                             int M, int N, int K, int x_f16, int out_f16)
+{
+    extern __shared__ float xsf[];  // [M][K]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    for (int idx = tid; idx < M * K; idx += blockDim.x)
+        xsf[idx] = x_f16 ? __half2float(((const __half *)x)[idx]) : ((const float *)x)[idx];
+    __syncthreads();
+
+    constexpr int ROWS = 4;  // rows per warp pass: 4 independent 16-byte loads in flight per lane
+    const int chunks = K >> 3;
+    const int64_t warp_global = (int64_t)blockIdx.x * (blockDim.x >> 5) + warp;
+    const int64_t n0 = warp_global * ROWS;
+    if (n0 >= N) return;
+
+    float acc[ROWS][MM];
+#pragma unroll
+    for (int r = 0; r < ROWS; r++)
+#pragma unroll
+        for (int m = 0; m < MM; m++) acc[r][m] = 0.f;
+
+    for (int ck = lane; ck < chunks; ck += 32) {
+        uint4 wv[ROWS];
+#pragma unroll
+        for (int r = 0; r < ROWS; r++) {
+            const int64_t n = n0 + r;
+            wv[r] = n < N ? ldg_stream_v4(W + n * K + (int64_t)ck * 8) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int m = 0; m < MM; m++) {
+            if (m >= M) break;
+            const float4 xa = *reinterpret_cast<const float4 *>(&xsf[m * K + ck * 8]);
+            const float4 xb = *reinterpret_cast<const float4 *>(&xsf[m * K + ck * 8 + 4]);
+#pragma unroll
+            for (int r = 0; r < ROWS; r++) {
+                const float2 w0 = __half22float2(u32_as_h2(wv[r].x)), w1 = __half22float2(u32_as_h2(wv[r].y));
+                const float2 w2 = __half22float2(u32_as_h2(wv[r].z)), w3 = __half22float2(u32_as_h2(wv[r].w));
+                float a = acc[r][m];
+                a = fmaf(w0.x, xa.x, a), a = fmaf(w0.y, xa.y, a), a = fmaf(w1.x, xa.z, a), a = fmaf(w1.y, xa.w, a);
+                a = fmaf(w2.x, xb.x, a), a = fmaf(w2.y, xb.y, a), a = fmaf(w3.x, xb.z, a), a = fmaf(w3.y, xb.w, a);
+                acc[r][m] = a;
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < ROWS; r++)
+#pragma unroll
+        for (int m = 0; m < MM; m++) {
+            float v = acc[r][m];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            acc[r][m] = v;
+        }
+    if (lane == 0) {
+#pragma unroll
+        for (int r = 0; r < ROWS; r++) {
+            const int64_t n = n0 + r;
+            if (n >= N) break;
+#pragma unroll
+            for (int m = 0; m < MM; m++) {
+                if (m >= M) break;
+                float v = acc[r][m] + (bias ? bias[n] : 0.f);
+                if (out_f16) ((__half *)out)[(int64_t)m * N + n] = __float2half_rn(v);
+                else ((float *)out)[(int64_t)m * N + n] = v;
+            }
+        }
+    }
+}
+
+// =====================================================================================================
+// Shape-agnostic kernel: any M, N, K (K % 8 != 0, N % 4 != 0, small groups), GPTQ or dense fp16 weight.
+// One thread per output, k ascending, double accumulator, bias added in double, one rounding on the
+// store: the arithmetic of gemmNTRef (src/reference/qwen-ref.ts:126-145). Correctness path for ragged
+// shapes such as the reference's own (N=53, K=42) and (M=37, N=53, K=41) tests, not a fast path.
+// =====================================================================================================
+__global__ void __launch_bounds__(128) linear_generic_kernel(const uint32_t *__restrict__ qw,
+                                                             const uint32_t *__restrict__ qz,
+                                                             const __half *__restrict__ sc,
+                                                             const __half *__restrict__ dense,
+                                                             const void *__restrict__ x, void *__restrict__ out,
+                                                             const float *__restrict__ bias, int64_t M, int64_t N,
+                                                             int64_t K, int64_t pack_rows, int64_t group,
+                                                             int64_t zcols, int x_f16, int out_f16, int round_x_f16)
+{
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= M * N) return;
+    const int64_t m = idx / N, n = idx - m * N;
+    auto xat = [&](int64_t k) -> float {
+        float v = x_f16 ? __half2float(((const __half *)x)[m * K + k]) : ((const float *)x)[m * K + k];
+        return round_x_f16 ? __half2float(__float2half_rn(v)) : v;
+    };
+    double acc = 0.0;
+    if (dense) {
+        for (int64_t k = 0; k < K; k++) acc += (double)xat(k) * (double)__half2float(dense[n * K + k]);
+    } else {
+        for (int64_t r = 0; r < pack_rows; r++) {
+            const uint32_t word = qw[r * N + n];
+            const int64_t g = (r * 8) / group;
+            const float scale = __half2float(sc[g * N + n]);
+            int zero = 8;
+            if (qz) zero = (int)((qz[g * zcols + (n >> 3)] >> (4 * (n & 7))) & 15u) + 1;
+            for (int j = 0; j < 8; j++) {
+                const int64_t k = r * 8 + j;
+                if (k >= K) break;
+                const float w = (float)((int)((word >> (4 * j)) & 15u) - zero) * scale;
+                acc += (double)xat(k) * (double)w;
+            }
+        }
+    }
+    if (bias) acc += (double)bias[n];
+    if (out_f16) ((__half *)out)[idx] = __float2half_rn((float)acc);
+    else ((float *)out)[idx] = (float)acc;
+}
+
+// =====================================================================================================
+// Planner and dispatch
+// =====================================================================================================
+
+int launch_gemm_tc(wb_context *ctx, const Weight &w, const void *A, void *C, const float *bias, int64_t M,
+                   int act_dtype, int out_dtype, int exact, const wb_plan &plan);
+int plan_gemm_tc(wb_context *ctx, const Weight &w, int64_t M, int act_dtype, int exact, wb_plan *plan);
+bool gemm_tc_supports(const Weight &w, int64_t M);
+
+static bool gemv_mma_supports(const Weight &w, int64_t M)
+{
+    return w.kind == WeightKind::Gptq && M <= 32 && w.K % 8 == 0 && w.N % 4 == 0 && w.group % 128 == 0;
+}
+
+static bool dense_gemv_supports(const Weight &w, int64_t M)
+{
+    return w.kind == WeightKind::DenseF16 && M <= 8 && w.K % 8 == 0 && (uint64_t)M * w.K * 4 <= 160 * 1024;
+}
+
+constexpr int kGemvSmemLimit = 200 * 1024;
+
+static void plan_gemv_mma(wb_context *ctx, const Weight &w, int64_t M, int two_halves, wb_plan *plan)
+{
+    const int chunks = (int)((w.pack_rows + 15) / 16);
+    const int col_tiles = (int)((w.N + 31) / 32);
+    int wn = M <= 2 ? 1 : (M <= 4 ? 2 : 4);
+    while (wn > 1 && col_tiles < wn) wn >>= 1;
+    int wk = wn == 1 ? 8 : (wn == 2 ? 8 : 4);
+    if (wk > chunks) wk = chunks;
+    const int ctas_n = (col_tiles + wn - 1) / wn;
+    const int target = 2 * ctx->sm_count;
+    int S = 1;
+    const int per_warp = (chunks + wk - 1) / wk;
+    if (ctas_n < target && per_warp > 2) {
+        const int by_work = (per_warp + 1) / 2;
+        const int by_fill = (target + ctas_n - 1) / ctas_n;
+        S = by_work < by_fill ? by_work : by_fill;
+    }
+    // shared memory: staged activations (16 bytes per row per packed row, twice in exact mode)
+    auto smem_for = [&](int s) {
+        const int cps = (chunks + s - 1) / s;
+        const uint64_t xs = (uint64_t)M * (cps * 16 + 4) * 16 * (two_halves ? 2 : 1);
+        const int MB = M <= 8 ? 1 : (M <= 16 ? 2 : 4);
+        const uint64_t red = (uint64_t)wn * wk * MB * 8 * 32 * 4;
+        return xs > red ? xs : red;
+    };
+    while (smem_for(S) > (uint64_t)kGemvSmemLimit && S < chunks) S++;
+    if (ctx->force_split > 0) S = ctx->force_split;
+    if (S > chunks) S = chunks;
+    if (S < 1) S = 1;
+    int cps = (chunks + S - 1) / S;
+    S = (chunks + cps - 1) / cps;  // drop empty slices
+    plan->kernel = WB_KERNEL_GEMV_MMA;
+    plan->split_k = S;
+    plan->grid_x = ctas_n;
+    plan->grid_y = S;
+    plan->grid_z = 1;
+    plan->block = wn * wk * 32;
+    plan->tile_m = wn;  // reused to carry the warp layout to the launcher
+    plan->tile_n = wk;
+    plan->launches = 1;
+    plan->scratch_bytes = S > 1 ? (uint64_t)S * M * w.N * 4 : 0;
+}
+
+int plan_linear(wb_context *ctx, const Weight &w, int64_t M, int act_dtype, int exact, wb_plan *plan)
+{
+    memset(plan, 0, sizeof *plan);
+    int kind = ctx->force_kernel;
+    if (kind == 0) {
+        if (gemv_mma_supports(w, M) && (M <= 16 || !gemm_tc_supports(w, M))) kind = WB_KERNEL_GEMV_MMA;
+        else if (dense_gemv_supports(w, M)) kind = WB_KERNEL_DENSE_GEMV;
+        else if (gemm_tc_supports(w, M)) kind = WB_KERNEL_GEMM_TC;
+        else kind = WB_KERNEL_GENERIC;
+    }
+    switch (kind) {
+    case WB_KERNEL_GEMV_MMA:
+        if (!gemv_mma_supports(w, M))
+            return fail(WB_ERR_UNSUPPORTED, "GEMV_MMA needs a GPTQ weight, M <= 32, K %% 8 == 0, N %% 4 == 0, group %% 128 == 0");
+        plan_gemv_mma(ctx, w, M, act_dtype == WB_F32, plan);
+        if ((uint64_t)plan->grid_x > (uint64_t)kMaxCounters)
+            return fail(WB_ERR_UNSUPPORTED, "N too large for the split-K counter table");
+        if (plan->scratch_bytes > kWorkspaceBytes) return fail(WB_ERR_OOM, "split-K partials exceed the workspace");
+        return WB_OK;
+    case WB_KERNEL_DENSE_GEMV:
+        if (!dense_gemv_supports(w, M)) return fail(WB_ERR_UNSUPPORTED, "DENSE_GEMV needs an fp16 weight, M <= 8, K %% 8 == 0");
+        plan->kernel = kind;
+        plan->split_k = 1;
+        plan->block = 256;
+        plan->grid_x = (int)((w.N + 31) / 32);  // 8 warps x 4 rows per CTA
+        plan->grid_y = plan->grid_z = 1;
+        plan->launches = 1;
+        return WB_OK;
+    case WB_KERNEL_GEMM_TC:
+        if (!gemm_tc_supports(w, M)) return fail(WB_ERR_UNSUPPORTED, "GEMM_TC does not support this shape");
+        return plan_gemm_tc(ctx, w, M, act_dtype, exact, plan);
+    case WB_KERNEL_GENERIC:
+        plan->kernel = kind;
+        plan->split_k = 1;
+        plan->block = 128;
+        plan->grid_x = (int)((M * w.N + 127) / 128);
+        plan->grid_y = plan->grid_z = 1;
+        plan->launches = 1;
+        return WB_OK;
+    }
+    return fail(WB_ERR_BAD_ARG, "unknown kernel kind %d", kind);
+}
+
+template <int MB>
+static cudaError_t launch_gemv_mb(const GemvParams &p, dim3 grid, int block, size_t smem, bool exact, cudaStream_t st)
+{
+    if (exact) {
+        cudaFuncSetAttribute(gptq_gemv_mma_kernel<MB, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemvSmemLimit);
+        gptq_gemv_mma_kernel<MB, true><<<grid, block, smem, st>>>(p);
+    } else {
+        cudaFuncSetAttribute(gptq_gemv_mma_kernel<MB, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemvSmemLimit);
+        gptq_gemv_mma_kernel<MB, false><<<grid, block, smem, st>>>(p);
+    }
+    return cudaGetLastError();
+}
+
+int launch_linear(wb_context *ctx, const Weight &w, const void *A, void *C, const float *bias, int64_t M,
+                  int act_dtype, int out_dtype, int exact)
+{
+    wb_plan plan;
+    // exact mode only changes anything for f32 activations
+    const int ex = (exact && act_dtype == WB_F32) ? 1 : 0;
+    WB_CHECK(plan_linear(ctx, w, M, act_dtype, ex, &plan));
+    // The streaming kernel always keeps f32 activations at ~22 bits (hi + lo halves): the reference's
+    // GEMV reads A as f32 (gemm_gemv_f16.wgsl:45-58) and the extra MMAs are free in an HBM-bound kernel.
+    const int ex_gemv = act_dtype == WB_F32 ? 1 : 0;
+    const char *base = ctx->arena[WB_ARENA_WEIGHTS].base;
+    switch (plan.kernel) {
+    case WB_KERNEL_GEMV_MMA: {
+        GemvParams p;
+        p.qw = (const uint32_t *)(base + w.off_main);
+        p.qz = w.has_zeros ? (const uint32_t *)(base + w.off_zeros) : nullptr;
+        p.sc = (const __half *)(base + w.off_scales);
+        p.x = A, p.out = C, p.bias = bias;
+        p.partial = (float *)ctx->workspace;
+        p.counters = ctx->counters;
+        p.M = (int)M, p.N = (int)w.N, p.K = (int)w.K;
+        p.pack_rows = (int)w.pack_rows, p.zcols = (int)w.zcols;
+        p.chunks = (int)((w.pack_rows + 15) / 16);
+        p.S = plan.split_k;
+        p.chunks_per_split = (p.chunks + p.S - 1) / p.S;
+        p.group_chunks = (int)(w.group / 128);
+        p.wn = plan.tile_m, p.wk = plan.tile_n;
+        p.x_f16 = act_dtype == WB_F16, p.out_f16 = out_dtype == WB_F16;
+        p.xs_stride = p.chunks_per_split * 16 + 4;
+        const int MB = M <= 8 ? 1 : (M <= 16 ? 2 : 4);
+        const size_t xs_bytes = (size_t)M * p.xs_stride * 16 * (ex_gemv ? 2 : 1);
+        const size_t red_bytes = (size_t)p.wn * p.wk * MB * 8 * 32 * 4;
+        const size_t smem = xs_bytes > red_bytes ? xs_bytes : red_bytes;
+        if (smem > (size_t)kGemvSmemLimit) return fail(WB_ERR_UNSUPPORTED, "GEMV_MMA: activations do not fit shared memory");
+        dim3 grid(plan.grid_x, plan.grid_y);
+        cudaError_t e = MB == 1   ? launch_gemv_mb<1>(p, grid, plan.block, smem, ex_gemv, ctx->stream)
+                        : MB == 2 ? launch_gemv_mb<2>(p, grid, plan.block, smem, ex_gemv, ctx->stream)
+                                  : launch_gemv_mb<4>(p, grid, plan.block, smem, ex_gemv, ctx->stream);
+        ctx->launches++;
+        WB_CUDA(e);
+        return WB_OK;
+    }
+    case WB_KERNEL_DENSE_GEMV: {
+        const __half *W = (const __half *)(base + w.off_main);
+        const size_t smem = (size_t)M * w.K * 4;
+        auto go = [&](auto kern) {
+            cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+            kern<<<plan.grid_x, 256, smem, ctx->stream>>>(W, A, C, bias, (int)M, (int)w.N, (int)w.K,
+                                                           act_dtype == WB_F16, out_dtype == WB_F16);
+        };
+        if (M == 1) go(dense_gemv_f16_kernel<1>);
+        else if (M == 2) go(dense_gemv_f16_kernel<2>);
+        else if (M <= 4) go(dense_gemv_f16_kernel<4>);
+        else go(dense_gemv_f16_kernel<8>);
+        ctx->launches++;
+        WB_CUDA(cudaGetLastError());
+        return WB_OK;
+    }
+    case WB_KERNEL_GEMM_TC:
+        return launch_gemm_tc(ctx, w, A, C, bias, M, act_dtype, out_dtype, ex, plan);
+    case WB_KERNEL_GENERIC: {
+        const bool gptq = w.kind == WeightKind::Gptq;
+        // f32 activations are rounded to fp16 for M > 1 unless exact mode is on, as the reference's
+        // tiled GEMM does when it stages A (gemm_nt_f16_from_f32.wgsl:58-62); its GEMV keeps f32.
+        const int round_x = (act_dtype == WB_F32 && !ex && M > 1) ? 1 : 0;
+        linear_generic_kernel<<<plan.grid_x, 128, 0, ctx->stream>>>(
+            gptq ? (const uint32_t *)(base + w.off_main) : nullptr,
+            (gptq && w.has_zeros) ? (const uint32_t *)(base + w.off_zeros) : nullptr,
+            gptq ? (const __half *)(base + w.off_scales) : nullptr, gptq ? nullptr : (const __half *)(base + w.off_main),
+            A, C, bias, M, w.N, w.K, w.pack_rows, gptq ? w.group : 8, w.zcols, act_dtype == WB_F16,
+            out_dtype == WB_F16, round_x);
+        ctx->launches++;
+        WB_CUDA(cudaGetLastError());
+        return WB_OK;
+    }
+    }
+    return fail(WB_ERR_BAD_ARG, "unknown kernel kind %d", plan.kernel);
+}
+
+}  // namespace wb
