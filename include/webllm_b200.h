@@ -162,6 +162,43 @@ WB_API int wb_plan_query(wb_context *ctx, wb_handle weight, int64_t M, int act_d
  * explicit S (src/tests/kernels.ts:1378-1400). */
 WB_API int wb_plan_override(wb_context *ctx, int kernel, int split_k);
 
+/* ---- Qwen2 forward. Replaces QwenGpt (src/model/qwen.ts:124-531) for the quantized-linear path and the
+ *      decode loop of generateQwen (src/infer/qwen-generate.ts:29-84). Weights are looked up by the
+ *      reference's names: "embed" (fp16 [V,C], tied lm_head), "finalNorm", and per layer i "L{i}.inNorm",
+ *      "L{i}.postNorm" (f32), "L{i}.qW/kW/vW/oW/gateW/upW/downW" (GPTQ or dense fp16), "L{i}.qB/kB/vB" (f32).
+ *      A layer may instead provide the fused projections "L{i}.qkvW" (+ "L{i}.qkvB") and "L{i}.gateUpW"
+ *      (output columns concatenated), which the reference already runs in shared passes
+ *      (src/model/qwen.ts:407-414,462-466). ---------------------------------------------------------- */
+typedef struct {
+    int32_t vocab_size, n_layer, n_head, n_kv_head, n_embd, intermediate; /* QwenConfig, src/model/qwen-config.ts:12-28 */
+    int32_t max_t;    /* context limit = KV cache rows (the reference's blockSize) */
+    int32_t kv_dtype; /* WB_F32 (the reference's cache, src/model/qwen.ts:200-205) or WB_F16 */
+    float rms_eps, rope_theta;
+} wb_qwen_config;
+
+WB_API int wb_qwen_create(wb_context *ctx, const wb_qwen_config *cfg, wb_qwen **out);
+WB_API int wb_qwen_destroy(wb_qwen *model);
+/* resetCache() */
+WB_API int wb_qwen_reset_cache(wb_qwen *model);
+WB_API int wb_qwen_cache_len(wb_qwen *model, int64_t *len);
+/* `exact` != 0: fp32-activation mode for every linear (see wb_linear). */
+WB_API int wb_qwen_set_exact(wb_qwen *model, int exact);
+/* forward(tokens, B, T): no KV cache, logits [B*T, V] f32 at *logits_offset in the activation arena
+ * (the arena is reset first, as runForward does, src/model/qwen.ts:359). */
+WB_API int wb_qwen_forward(wb_qwen *model, const uint32_t *tokens, int64_t B, int64_t T, uint64_t *logits_offset);
+/* prefill(tokens): fills the cache; last_only != 0 computes only the last row of logits ([1, V]),
+ * which is all generateQwen reads (src/infer/qwen-generate.ts:53-57); else [n, V]. */
+WB_API int wb_qwen_prefill(wb_qwen *model, const uint32_t *tokens, int64_t n, int last_only, uint64_t *logits_offset);
+/* decodeStep(token): logits [1, V]. */
+WB_API int wb_qwen_decode_step(wb_qwen *model, uint32_t token, uint64_t *logits_offset);
+/* Greedy decoding kept on the device: feeds `first_token`, then n_steps times (forward one token, argmax
+ * with the reference's first-strict-maximum rule, src/infer/sampler.ts:30-36, append). The step is captured
+ * in a CUDA graph on first use and replayed; out_tokens receives the n_steps sampled tokens. Replaces the
+ * per-token logits readback of generateQwen (src/infer/qwen-generate.ts:66-74). */
+WB_API int wb_qwen_decode_greedy(wb_qwen *model, uint32_t first_token, int64_t n_steps, uint32_t *out_tokens);
+/* Logits of the last step run by wb_qwen_decode_greedy, [V] f32, copied to the host. */
+WB_API int wb_qwen_last_logits(wb_qwen *model, float *out);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,128 @@
+"""GPU parity: the tcgen05 / TMEM GEMM (int4 unpack in shared memory, and dense fp16 weights) against
+gemmNTRef on the fp16 weights the reference keeps on the device, through the C ABI."""
+import numpy as np
+import pytest
+
+from helpers import assert_close, oracle_weight, register, run_linear
+from webllm_b200 import WebllmError, _lib, synthetic
+
+pytestmark = pytest.mark.gpu
+
+F16_RTOL = 1e-3
+
+_cache = {}
+
+
+def _weight(gpu, oracle, name, K, N, zeros="any"):
+    key = f"tc_{name}"
+    if key not in _cache:
+        t = synthetic.random_gptq(K, N, 128, seed=K * 3 + N, zeros=zeros)
+        h = register(gpu, key, t)
+        # the tensor-core path multiplies fp16 weights: f32ToF16Bits of the dequantised value
+        _cache[key] = (h, oracle.round_f16(oracle_weight(oracle, t)).reshape(N, K))
+    return _cache[key]
+
+
+def _ref_rows(oracle, x16, W16, rows, bias=None):
+    xs = x16[rows].astype(np.float32)
+    return oracle.gemm_nt_ref(xs, W16, len(rows), W16.shape[0], W16.shape[1], bias, threads=oracle.max_threads())
+
+
+@pytest.mark.parametrize("name,K,N", [("q", 896, 896), ("k", 896, 128), ("gate", 896, 4864), ("down", 4864, 896)])
+@pytest.mark.parametrize("M", [16, 17, 32, 64, 100, 128, 300])
+def test_gemm_tc_small_and_ragged_m(gpu, oracle, name, K, N, M):
+    """Every tile height (16, 32, 64, 128, 256) incl. token counts that do not fill the tile."""
+    h, W16 = _weight(gpu, oracle, name, K, N)
+    bias = np.random.default_rng(N).standard_normal(N).astype(np.float32)
+    try:
+        hb = gpu.weight(f"tcb_{name}")
+    except WebllmError:
+        hb = gpu.f32_upload(f"tcb_{name}", bias)
+    x16 = np.random.default_rng(M + K).standard_normal((M, K)).astype(np.float16)
+    gpu.plan_override(_lib.WB_KERNEL_GEMM_TC, 0)
+    try:
+        p = gpu.plan(h, M, "f16")
+        assert p["kernel_name"] == "gemm_tc" and p["tile_m"] >= min(M, 256) // 2
+        got = run_linear(gpu, h, x16, M, N, hb, act="f16")
+        ref = _ref_rows(oracle, x16, W16, list(range(M)), bias)
+        assert_close(oracle, got, ref, F16_RTOL, f"{name} M={M}")
+        gpu.synchronize()  # surfaces a device-side wait that gave up
+    finally:
+        gpu.plan_override(0, 0)
+
+
+@pytest.mark.parametrize("name,K,N", [(n, k, nn) for n, (k, nn) in synthetic.QWEN05B_SHAPES.items() if n in ("q", "k", "gate", "down")])
+def test_prefill_m2048(gpu, oracle, name, K, N):
+    """Prefill size, M = 2048: the planner picks the tensor-core kernel; 96 sampled rows are checked
+    against the oracle (a full 2048-row double-precision reference would take minutes on the host)."""
+    h, W16 = _weight(gpu, oracle, name, K, N)
+    M = 2048
+    x16 = np.random.default_rng(7).standard_normal((M, K)).astype(np.float16)
+    assert gpu.plan(h, M, "f16")["kernel_name"] == "gemm_tc"
+    got = run_linear(gpu, h, x16, M, N, None, act="f16")
+    rows = sorted(set(np.random.default_rng(1).integers(0, M, 94).tolist()) | {0, M - 1})
+    assert_close(oracle, got[rows], _ref_rows(oracle, x16, W16, rows), F16_RTOL, f"{name} M=2048")
+    # fp16 output: the f32 result rounded once
+    got16 = run_linear(gpu, h, x16, M, N, None, act="f16", out="f16")
+    assert np.array_equal(got16.astype(np.float16).view(np.uint16), got.astype(np.float16).view(np.uint16))
+    # f32 activations are rounded to fp16 first, like gemm_nt_f16_from_f32.wgsl:58-62
+    got32 = run_linear(gpu, h, x16.astype(np.float32) * np.float32(1.0002), M, N, None)
+    x_r = (x16.astype(np.float32) * np.float32(1.0002)).astype(np.float16)
+    assert_close(oracle, got32[rows], _ref_rows(oracle, x_r, W16, rows), F16_RTOL, f"{name} f32 activations")
+
+
+def test_linearity_at_full_size(gpu, oracle):
+    """Size-independent property at M = 2048 x (896 -> 4864): f(a) + f(b) == f(a + b) up to fp16/f32
+    rounding, with a and b chosen so that a + b is exact in fp16."""
+    h, _ = _weight(gpu, oracle, "gate", 896, 4864)
+    rng = np.random.default_rng(3)
+    a = (rng.integers(-64, 64, size=(2048, 896)) / 32).astype(np.float16)
+    b = (rng.integers(-64, 64, size=(2048, 896)) / 32).astype(np.float16)
+    fa = run_linear(gpu, h, a, 2048, 4864, None, act="f16")
+    fb = run_linear(gpu, h, b, 2048, 4864, None, act="f16")
+    fab = run_linear(gpu, h, (a + b).astype(np.float16), 2048, 4864, None, act="f16")
+    assert_close(oracle, fa + fb, fab, 1e-4, "linearity")
+
+
+def test_gemv_and_gemm_paths_agree(gpu, oracle):
+    """The switch between the streaming kernel and the tensor-core kernel (M = 16 / 17, and forced both ways
+    at M = 32) must not be visible beyond fp16-weight rounding."""
+    h, _ = _weight(gpu, oracle, "gate", 896, 4864)
+    x16 = np.random.default_rng(5).standard_normal((32, 896)).astype(np.float16)
+    outs = {}
+    for kind in (_lib.WB_KERNEL_GEMV_MMA, _lib.WB_KERNEL_GEMM_TC):
+        gpu.plan_override(kind, 0)
+        try:
+            outs[kind] = run_linear(gpu, h, x16, 32, 4864, None, act="f16")
+        finally:
+            gpu.plan_override(0, 0)
+    # the tensor-core path multiplies weights rounded to fp16 (2^-11), the streaming path exact ones
+    assert_close(oracle, outs[_lib.WB_KERNEL_GEMM_TC], outs[_lib.WB_KERNEL_GEMV_MMA], 4e-3, "paths")
+    assert gpu.plan(h, 16, "f16")["kernel_name"] == "gemv_mma"
+    assert gpu.plan(h, 33, "f16")["kernel_name"] == "gemm_tc"
+
+
+@pytest.mark.parametrize("M", [9, 64, 200])
+def test_dense_f16_gemm(gpu, oracle, M):
+    """Dense fp16 weight (the tied lm_head at prefill): both operands arrive by TMA."""
+    V, K = 1000, 896
+    if "dense" not in _cache:
+        W = np.random.default_rng(8).normal(0, 0.02, size=(V, K)).astype(np.float16)
+        h = gpu.f16_alloc("tc_dense", V, K)
+        gpu.f16_write_bits(h, 0, W)
+        _cache["dense"] = (h, W.astype(np.float32))
+    h, W = _cache["dense"]
+    x16 = np.random.default_rng(M).standard_normal((M, K)).astype(np.float16)
+    assert gpu.plan(h, M, "f16")["kernel_name"] == "gemm_tc"
+    got = run_linear(gpu, h, x16, M, V, None, act="f16")
+    assert_close(oracle, got, _ref_rows(oracle, x16, W, list(range(M))), F16_RTOL, f"dense M={M}")
+
+
+def test_7b_shapes(gpu, oracle):
+    for name, K, N, M in (("q7", 3584, 3584, 4096), ("kv7", 3584, 512, 4096), ("down7", 18944, 3584, 512)):
+        h, W16 = _weight(gpu, oracle, name, K, N, zeros="7or8")
+        x16 = np.random.default_rng(K).standard_normal((M, K)).astype(np.float16)
+        got = run_linear(gpu, h, x16, M, N, None, act="f16")
+        rows = sorted(set(np.random.default_rng(2).integers(0, M, 30).tolist()) | {0, M - 1})
+        assert_close(oracle, got[rows], _ref_rows(oracle, x16, W16, rows), F16_RTOL, f"{name} M={M}")
+    gpu.synchronize()

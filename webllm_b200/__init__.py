@@ -9,3 +9,6 @@ from ._lib import WebllmError, LIB_PATH  # noqa: F401
 from .buffer import ALIGN, Tensor, align_to  # noqa: F401
 from .device import Arena, Gpu  # noqa: F401
 from .quant import GptqInt4Params, dequantize_gptq_int4  # noqa: F401
+from .qwen import QwenGpt, concat_gptq  # noqa: F401,E402
+from .generate import SamplerOptions, generate_qwen, sample_token  # noqa: F401,E402
+from .plan import plan_gemv_split  # noqa: F401,E402

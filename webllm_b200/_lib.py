@@ -84,6 +84,16 @@ SIGNATURES = {
     "wb_linear": [_vp, C.c_int32, _u64, _u64, C.c_int32, _i64, _i32, _i32, _i32],
     "wb_plan_query": [_vp, C.c_int32, _i64, _i32, _i32, C.POINTER(Plan)],
     "wb_plan_override": [_vp, _i32, _i32],
+    "wb_qwen_create": [_vp, C.POINTER(QwenConfigC), C.POINTER(_vp)],
+    "wb_qwen_destroy": [_vp],
+    "wb_qwen_reset_cache": [_vp],
+    "wb_qwen_cache_len": [_vp, C.POINTER(_i64)],
+    "wb_qwen_set_exact": [_vp, _i32],
+    "wb_qwen_forward": [_vp, _vp, _i64, _i64, C.POINTER(_u64)],
+    "wb_qwen_prefill": [_vp, _vp, _i64, _i32, C.POINTER(_u64)],
+    "wb_qwen_decode_step": [_vp, C.c_uint32, C.POINTER(_u64)],
+    "wb_qwen_decode_greedy": [_vp, C.c_uint32, _i64, _vp],
+    "wb_qwen_last_logits": [_vp, _vp],
 }
 _RESTYPES = {"wb_last_error": C.c_char_p}
 

@@ -1,7 +1,461 @@
-// placeholder until the tcgen05 kernel lands
+// Prefill / batched linear on the 5th-generation tensor cores: C[M,N] = A[M,K] . W[N,K]^T (+bias) with
+// W either GPTQ int4 (unpacked inside the kernel) or dense fp16. Replaces gemm_nt_f16_from_f32.wgsl
+// (src/gpu/kernels/gemm/gemm_nt_f16_from_f32.wgsl:39-95), the tiled GEMM behind QwenGpt.gemm for M > 1
+// (src/model/qwen.ts:613-617).
+//
+// One CTA computes a 128 (output columns n) x MT (tokens m) tile of C^T: the weight tile is the 128-row
+// operand of tcgen05.mma, the activation tile its MT-column operand, the f32 accumulator lives in TMEM
+// (128 lanes x MT columns). Roles, 6 warps:
+//   warp 0      TMA producer: per 64-k block one box of activations [MT x 64] fp16 (128-byte swizzle) and
+//               one box of packed weights [8 packed rows x 128 columns] int32, into a 4-stage ring.
+//   warp 1      allocates TMEM, then one elected lane issues 4 x tcgen05.mma (K = 16 each) per block and
+//               commits the stage back to the producer.
+//   warps 2-5   unpack: thread n turns the 8 words of column n into 64 fp16 values w = (q - zero) * scale
+//               (exact integer in fp16, one rounding in the multiply: the fp16 weight the reference
+//               uploads, src/gpu/buffer.ts:103-120) and stores them as the K-major, 128-byte-swizzled
+//               operand tile; afterwards the same warps drain TMEM (tcgen05.ld), add the bias and store.
+// Every wait on an mbarrier is bounded: when a wait gives up it raises a CTA-wide abort flag, records a
+// code in the context's status word, and all roles fall through to the common exit where TMEM is freed.
+#include <cuda.h>
+
 #include "common.cuh"
+
 namespace wb {
-bool gemm_tc_supports(const Weight &, int64_t) { return false; }
-int plan_gemm_tc(wb_context *, const Weight &, int64_t, int, int, wb_plan *) { return fail(WB_ERR_UNSUPPORTED, "no tc"); }
-int launch_gemm_tc(wb_context *, const Weight &, const void *, void *, const float *, int64_t, int, int, int, const wb_plan &) { return fail(WB_ERR_UNSUPPORTED, "no tc"); }
+
+namespace tc {
+
+constexpr int BN = 128;       // output columns per CTA (UMMA M)
+constexpr int BK = 64;        // k per stage: one 128-byte swizzle atom of fp16
+constexpr int STAGES = 4;
+constexpr int THREADS = 192;
+constexpr uint32_t SPIN_LIMIT = 1u << 20;
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
 }
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint64_t *bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait. Returns false when it gave up or another role already aborted.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int *status, int code)
+{
+    for (uint32_t it = 0; it < SPIN_LIMIT; it++) {
+        if (mbar_try(bar, parity)) return true;
+        if ((it & 1023u) == 1023u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    if (status) *(volatile int *)status = code;
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int x, int y, uint64_t *bar)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_alloc(uint32_t *dst_smem, uint32_t cols)
+{
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols)
+{
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t *bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)[16])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major operand tile stored as 8-row x 128-byte swizzle atoms
+// (rows 128 bytes apart, atoms 1024 bytes apart): start address >> 4, leading byte offset 1 (unused with
+// a swizzle), stride byte offset 1024 >> 4, descriptor version 1 (sm_100), layout type 2 = 128-byte swizzle.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr)
+{
+    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+
+// Instruction descriptor, kind::f16: D = f32 (bits 4-5 = 1), A = B = fp16 (0), both K-major (bits 15, 16 = 0),
+// N >> 3 at bit 17, M >> 4 at bit 24.
+__host__ __device__ constexpr uint32_t idesc_f16(int m, int n)
+{
+    return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+struct Params {
+    const uint32_t *qz;   // nullable
+    const __half *sc;     // GPTQ scales; nullptr for a dense fp16 weight
+    void *out;
+    const float *bias;    // nullable
+    int *status;
+    int M, N, K;
+    int zcols, group_blocks;  // group / 64
+    int out_f16;
+};
+
+}  // namespace tc
+
+namespace tc {
+
+template <int MT, bool DENSE>
+struct Smem {
+    static constexpr int X_BYTES = MT * BK * 2;
+    static constexpr int WD_BYTES = BN * BK * 2;
+    static constexpr int WP_BYTES = DENSE ? 0 : 8 * BN * 4;
+    static constexpr int STAGE_BYTES = X_BYTES + WD_BYTES + WP_BYTES;  // every piece is a multiple of 1024
+    static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
+
+template <int MT, bool DENSE>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, const Params p)
+{
+    using S = Smem<MT, DENSE>;
+    constexpr uint32_t TMEM_COLS = MT < 32 ? 32 : MT;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t *bars = (uint64_t *)(smem + STAGES * S::STAGE_BYTES);
+    uint64_t *full = bars, *deq = bars + STAGES, *empty = bars + 2 * STAGES, *acc_full = bars + 3 * STAGES;
+    uint32_t *tmem_slot = (uint32_t *)(bars + 3 * STAGES + 1);
+    volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.x * MT, n0 = blockIdx.y * BN;
+    const int KB = p.K / BK;
+
+    auto xs = [&](int s) { return smem + s * S::STAGE_BYTES; };
+    auto wd = [&](int s) { return smem + s * S::STAGE_BYTES + S::X_BYTES; };
+    auto wp = [&](int s) { return (uint32_t *)(smem + s * S::STAGE_BYTES + S::X_BYTES + S::WD_BYTES); };
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&deq[s], 4);
+            mbar_init(&empty[s], 1);
+        }
+        mbar_init(acc_full, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            for (int kb = 0; kb < KB; kb++) {
+                const int s = kb % STAGES;
+                const uint32_t ph = (kb / STAGES) & 1;
+                if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 1)) break;
+                mbar_expect_tx(&full[s], S::X_BYTES + (DENSE ? S::WD_BYTES : S::WP_BYTES));
+                tma_load_2d(xs(s), &map_x, kb * BK, m0, &full[s]);
+                if constexpr (DENSE) tma_load_2d(wd(s), &map_w, kb * BK, n0, &full[s]);
+                else tma_load_2d(wp(s), &map_w, n0, kb * 8, &full[s]);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = idesc_f16(BN, MT);
+            bool ok = true;
+            for (int kb = 0; kb < KB && ok; kb++) {
+                const int s = kb % STAGES;
+                const uint32_t ph = (kb / STAGES) & 1;
+                ok = mbar_wait(&full[s], ph, abort_flag, p.status, 2);
+                if (ok && !DENSE) ok = mbar_wait(&deq[s], ph, abort_flag, p.status, 3);
+                if (!ok) break;
+                tc_fence_after();
+                const uint64_t a0 = smem_desc_sw128(smem_u32(wd(s)));
+                const uint64_t b0 = smem_desc_sw128(smem_u32(xs(s)));
+#pragma unroll
+                for (int k = 0; k < BK / 16; k++)  // 16 fp16 = 32 bytes = 2 descriptor units along K
+                    umma_f16(tmem_base, a0 + 2 * k, b0 + 2 * k, idesc, (kb | k) != 0);
+                umma_commit(&empty[s]);
+            }
+            if (ok) umma_commit(acc_full);
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------------ unpack, then epilogue
+        const int tn = threadIdx.x - 64;  // 0..127: column of the tile
+        bool ok = true;
+        if constexpr (!DENSE) {
+            const int n = n0 + tn;
+            const bool n_ok = n < p.N;
+            __half2 scale2 = __float2half2_rn(0.f), zsub = scale2, zfma = scale2;
+            const __half2 sixteenth = __float2half2_rn(0.0625f);
+            for (int kb = 0; kb < KB; kb++) {
+                const int s = kb % STAGES;
+                const uint32_t ph = (kb / STAGES) & 1;
+                if (kb % p.group_blocks == 0) {
+                    const int G = kb / p.group_blocks;
+                    float z = 8.f;
+                    if (n_ok) {
+                        scale2 = __half2half2(p.sc[(int64_t)G * p.N + n]);
+                        if (p.qz) z = (float)(((p.qz[(int64_t)G * p.zcols + (n >> 3)] >> ((n & 7) * 4)) & 15u) + 1u);
+                    }
+                    zsub = __float2half2_rn(1024.f + z);
+                    zfma = __float2half2_rn(-(64.f + z));
+                }
+                ok = mbar_wait(&full[s], ph, abort_flag, p.status, 4);
+                if (!ok) break;
+                const uint32_t *src = wp(s) + tn;
+                uint8_t *dst_row = wd(s) + tn * 128;
+#pragma unroll
+                for (int r = 0; r < 8; r++) {
+                    uint32_t w = src[r * BN];
+                    const uint32_t lo0 = (w & 0x000f000fu) | 0x64006400u;
+                    const uint32_t hi0 = (w & 0x00f000f0u) | 0x64006400u;
+                    w >>= 8;
+                    const uint32_t lo1 = (w & 0x000f000fu) | 0x64006400u;
+                    const uint32_t hi1 = (w & 0x00f000f0u) | 0x64006400u;
+                    const __half2 a = __hmul2(__hsub2(*(const __half2 *)&lo0, zsub), scale2);          // k0, k4
+                    const __half2 b = __hmul2(__hfma2(*(const __half2 *)&hi0, sixteenth, zfma), scale2);  // k1, k5
+                    const __half2 c = __hmul2(__hsub2(*(const __half2 *)&lo1, zsub), scale2);          // k2, k6
+                    const __half2 d = __hmul2(__hfma2(*(const __half2 *)&hi1, sixteenth, zfma), scale2);  // k3, k7
+                    const uint32_t ua = *(const uint32_t *)&a, ub = *(const uint32_t *)&b;
+                    const uint32_t uc = *(const uint32_t *)&c, ud = *(const uint32_t *)&d;
+                    uint4 o;
+                    o.x = __byte_perm(ua, ub, 0x5410);
+                    o.y = __byte_perm(uc, ud, 0x5410);
+                    o.z = __byte_perm(ua, ub, 0x7632);
+                    o.w = __byte_perm(uc, ud, 0x7632);
+                    // 16-byte chunk r of row tn, at its 128-byte-swizzle position
+                    *(uint4 *)(dst_row + ((r ^ (tn & 7)) << 4)) = o;
+                }
+                fence_async_smem();  // make the generic-proxy stores visible to the tensor core's reads
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&deq[s]);
+            }
+        }
+        // epilogue: warp w may touch TMEM lanes 32*(w%4) .. +31
+        if (ok) ok = mbar_wait(acc_full, 0, abort_flag, p.status, 5);
+        if (ok) {
+            tc_fence_after();
+            const int q = warp & 3;
+            const int n = n0 + q * 32 + lane;
+            const float bias = (p.bias && n < p.N) ? p.bias[n] : 0.f;
+#pragma unroll 1
+            for (int c = 0; c < MT; c += 16) {
+                uint32_t r[16];
+                tmem_ld_32x32b_x16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c, r);
+                tmem_ld_wait();
+                if (n < p.N) {
+#pragma unroll
+                    for (int j = 0; j < 16; j++) {
+                        const int m = m0 + c + j;
+                        if (m < p.M) {
+                            const float v = __uint_as_float(r[j]) + bias;
+                            if (p.out_f16) ((__half *)p.out)[(int64_t)m * p.N + n] = __float2half_rn(v);
+                            else ((float *)p.out)[(int64_t)m * p.N + n] = v;
+                        }
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+__global__ void cast_f32_to_f16_kernel(const float *__restrict__ in, __half *__restrict__ out, int64_t n)
+{
+    int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x * 4;
+    for (; i + 3 < n; i += stride) {
+        const float4 v = *reinterpret_cast<const float4 *>(in + i);
+        __half2 a = __floats2half2_rn(v.x, v.y), b = __floats2half2_rn(v.z, v.w);
+        uint2 o;
+        o.x = *reinterpret_cast<uint32_t *>(&a);
+        o.y = *reinterpret_cast<uint32_t *>(&b);
+        *reinterpret_cast<uint2 *>(out + i) = o;
+    }
+}
+
+}  // namespace tc
+
+// ----------------------------------------------------------------------------------------------------
+// host side
+// ----------------------------------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static int make_map_2d(wb_context *ctx, CUtensorMap *map, CUtensorMapDataType dt, int elem_bytes, const void *base,
+                       uint64_t inner, uint64_t outer, uint32_t box_inner, uint32_t box_outer, bool swizzle128)
+{
+    cuuint64_t dims[2] = {inner, outer};
+    cuuint64_t strides[1] = {inner * (uint64_t)elem_bytes};
+    cuuint32_t box[2] = {box_inner, box_outer};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = ((EncodeTiledFn)ctx->tmap_encode)(map, dt, 2, const_cast<void *>(base), dims, strides, box, estr,
+                                                   CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                                   swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                                                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(WB_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return WB_OK;
+}
+
+bool gemm_tc_supports(const Weight &w, int64_t M)
+{
+    if (M < 1 || w.K % 64 != 0) return false;
+    if (w.kind == WeightKind::Gptq) return w.N % 4 == 0 && w.group % 64 == 0;
+    return w.kind == WeightKind::DenseF16;
+}
+
+static int pick_mt(int64_t M, int64_t N, int sms)
+{
+    if (M <= 16) return 16;
+    if (M <= 32) return 32;
+    if (M <= 64) return 64;
+    if (M <= 128) return 128;
+    const int64_t n_tiles = (N + 127) / 128;
+    int best = 256;
+    int64_t best_cost = -1;
+    for (int mt : {256, 128}) {
+        const int64_t tiles = ((M + mt - 1) / mt) * n_tiles;
+        const int64_t waves = (tiles + sms - 1) / sms;
+        const int64_t cost = waves * (mt + 32);  // per-tile time grows with MT; 32 ~ fixed cost of a tile
+        if (best_cost < 0 || cost < best_cost) best = mt, best_cost = cost;
+    }
+    return best;
+}
+
+int plan_gemm_tc(wb_context *ctx, const Weight &w, int64_t M, int act_dtype, int exact, wb_plan *plan)
+{
+    (void)exact;
+    const int mt = pick_mt(M, w.N, ctx->sm_count);
+    plan->kernel = WB_KERNEL_GEMM_TC;
+    plan->split_k = 1;
+    plan->grid_x = (int)((M + mt - 1) / mt);
+    plan->grid_y = (int)((w.N + 127) / 128);
+    plan->grid_z = 1;
+    plan->block = tc::THREADS;
+    plan->tile_m = mt;
+    plan->tile_n = 128;
+    plan->launches = act_dtype == WB_F32 ? 2 : 1;
+    plan->scratch_bytes = act_dtype == WB_F32 ? (uint64_t)M * w.K * 2 : 0;
+    if (plan->scratch_bytes > kWorkspaceBytes)
+        return fail(WB_ERR_OOM, "fp16 staging of %lld x %lld activations exceeds the workspace; pass fp16 activations or split M",
+                    (long long)M, (long long)w.K);
+    return WB_OK;
+}
+
+template <int MT, bool DENSE>
+static cudaError_t launch_tc(const CUtensorMap &mx, const CUtensorMap &mw, const tc::Params &p, dim3 grid, cudaStream_t st)
+{
+    constexpr int smem = tc::Smem<MT, DENSE>::TOTAL;
+    cudaError_t e = cudaFuncSetAttribute(tc::gemm_tc_kernel<MT, DENSE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    tc::gemm_tc_kernel<MT, DENSE><<<grid, tc::THREADS, smem, st>>>(mx, mw, p);
+    return cudaGetLastError();
+}
+
+template <bool DENSE>
+static cudaError_t launch_tc_mt(int mt, const CUtensorMap &mx, const CUtensorMap &mw, const tc::Params &p, dim3 grid, cudaStream_t st)
+{
+    switch (mt) {
+    case 16: return launch_tc<16, DENSE>(mx, mw, p, grid, st);
+    case 32: return launch_tc<32, DENSE>(mx, mw, p, grid, st);
+    case 64: return launch_tc<64, DENSE>(mx, mw, p, grid, st);
+    case 128: return launch_tc<128, DENSE>(mx, mw, p, grid, st);
+    default: return launch_tc<256, DENSE>(mx, mw, p, grid, st);
+    }
+}
+
+int launch_gemm_tc(wb_context *ctx, const Weight &w, const void *A, void *C, const float *bias, int64_t M, int act_dtype,
+                   int out_dtype, int exact, const wb_plan &plan)
+{
+    (void)exact;
+    const char *base = ctx->arena[WB_ARENA_WEIGHTS].base;
+    const void *a16 = A;
+    if (act_dtype == WB_F32) {
+        // The reference rounds f32 activations to fp16 when it stages a tile (gemm_nt_f16_from_f32.wgsl:58-62).
+        const int64_t n = M * w.K;  // K % 64 == 0, so n % 4 == 0
+        int blocks = (int)((n / 4 + 255) / 256);
+        if (blocks > ctx->sm_count * 8) blocks = ctx->sm_count * 8;
+        tc::cast_f32_to_f16_kernel<<<blocks, 256, 0, ctx->stream>>>((const float *)A, (__half *)ctx->workspace, n);
+        ctx->launches++;
+        WB_CUDA(cudaGetLastError());
+        a16 = ctx->workspace;
+    }
+    const int mt = plan.tile_m;
+    CUtensorMap mx, mw;
+    WB_CHECK(make_map_2d(ctx, &mx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a16, (uint64_t)w.K, (uint64_t)M, tc::BK, (uint32_t)mt, true));
+    tc::Params p;
+    p.out = C, p.bias = bias, p.status = ctx->status_word;
+    p.M = (int)M, p.N = (int)w.N, p.K = (int)w.K;
+    p.out_f16 = out_dtype == WB_F16;
+    dim3 grid(plan.grid_x, plan.grid_y);
+    cudaError_t e;
+    if (w.kind == WeightKind::Gptq) {
+        WB_CHECK(make_map_2d(ctx, &mw, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, base + w.off_main, (uint64_t)w.N,
+                             (uint64_t)w.pack_rows, tc::BN, 8, false));
+        p.qz = w.has_zeros ? (const uint32_t *)(base + w.off_zeros) : nullptr;
+        p.sc = (const __half *)(base + w.off_scales);
+        p.zcols = (int)w.zcols;
+        p.group_blocks = (int)(w.group / 64);
+        e = launch_tc_mt<false>(mt, mx, mw, p, grid, ctx->stream);
+    } else {
+        WB_CHECK(make_map_2d(ctx, &mw, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, base + w.off_main, (uint64_t)w.K, (uint64_t)w.N,
+                             tc::BK, tc::BN, true));
+        p.qz = nullptr, p.sc = nullptr, p.zcols = 0, p.group_blocks = 1;
+        e = launch_tc_mt<true>(mt, mx, mw, p, grid, ctx->stream);
+    }
+    ctx->launches++;
+    WB_CUDA(e);
+    return WB_OK;
+}
+
+}  // namespace wb

@@ -414,10 +414,12 @@ int launch_gemm_tc(wb_context *ctx, const Weight &w, const void *A, void *C, con
 int plan_gemm_tc(wb_context *ctx, const Weight &w, int64_t M, int act_dtype, int exact, wb_plan *plan);
 bool gemm_tc_supports(const Weight &w, int64_t M);
 
-static bool gemv_mma_supports(const Weight &w, int64_t M)
+static bool gemv_mma_shape_ok(const Weight &w)
 {
-    return w.kind == WeightKind::Gptq && M <= 32 && w.K % 8 == 0 && w.N % 4 == 0 && w.group % 128 == 0;
+    return w.kind == WeightKind::Gptq && w.K % 8 == 0 && w.N % 4 == 0 && w.group % 128 == 0;
 }
+
+static bool gemv_mma_supports(const Weight &w, int64_t M) { return M <= 32 && gemv_mma_shape_ok(w); }
 
 static bool dense_gemv_supports(const Weight &w, int64_t M)
 {
@@ -476,8 +478,8 @@ int plan_linear(wb_context *ctx, const Weight &w, int64_t M, int act_dtype, int 
     if (kind == 0) {
         if (gemv_mma_supports(w, M) && (M <= 16 || !gemm_tc_supports(w, M))) kind = WB_KERNEL_GEMV_MMA;
         else if (dense_gemv_supports(w, M)) kind = WB_KERNEL_DENSE_GEMV;
-        else if (gemm_tc_supports(w, M)) kind = WB_KERNEL_GEMM_TC;
-        else kind = WB_KERNEL_GENERIC;
+        else if (gemm_tc_supports(w, M) && !(exact && act_dtype == WB_F32)) kind = WB_KERNEL_GEMM_TC;
+        else kind = WB_KERNEL_GENERIC;  // incl. exact f32 activations at large M: k-ascending double sums
     }
     switch (kind) {
     case WB_KERNEL_GEMV_MMA:

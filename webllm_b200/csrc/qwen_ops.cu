@@ -1,0 +1,324 @@
+// The non-linear steps either side of each projection in the Qwen2 forward pass. They replace the WGSL
+// kernels embedding_f16, rmsnorm, rope_half, kv_store, attention_gqa(_cache), silu_mul and vec_add that
+// QwenGpt.runForward dispatches between its gemm() calls (src/model/qwen.ts:391-489). All activations
+// are f32, as in the reference; the KV cache is fp16 or f32.
+#include "qwen_ops.cuh"
+
+namespace wb {
+
+// embedding_f16.wgsl: x[m, :] = f32(embed[token[m], :])
+__global__ void embed_f16_kernel(const __half *__restrict__ table, const uint32_t *__restrict__ tokens,
+                                 float *__restrict__ x, int M, int C, int vocab)
+{
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (int64_t)M * C) return;
+    const int m = (int)(idx / C), c = (int)(idx - (int64_t)m * C);
+    uint32_t tok = tokens[m];
+    if (tok >= (uint32_t)vocab) tok = 0;  // ids are validated on the host; never read out of bounds
+    x[idx] = __half2float(table[(int64_t)tok * C + c]);
+}
+
+__device__ __forceinline__ float block_sum(float v, float *red)
+{
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float t = 0.f;
+    for (int i = 0; i < nw; i++) t += red[i];  // same order in every thread: deterministic
+    __syncthreads();
+    return t;
+}
+
+// rmsnorm.wgsl / rmsNormRef (src/reference/qwen-ref.ts:12-29): y = x / sqrt(mean(x^2) + eps) * w,
+// optionally fused with the residual add that precedes it: x_out = x + delta (vec_add.wgsl).
+__global__ void __launch_bounds__(256) rmsnorm_kernel(const float *__restrict__ x, const float *__restrict__ delta,
+                                                      float *__restrict__ x_out, const float *__restrict__ w,
+                                                      float *__restrict__ y, int D, float eps)
+{
+    __shared__ float red[8];
+    const int64_t base = (int64_t)blockIdx.x * D;
+    float ss = 0.f;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float v = x[base + d];
+        if (delta) {
+            v += delta[base + d];
+            x_out[base + d] = v;
+        }
+        ss = fmaf(v, v, ss);
+    }
+    const float rstd = rsqrtf(block_sum(ss, red) / (float)D + eps);
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        const float v = delta ? x_out[base + d] : x[base + d];
+        y[base + d] = v * rstd * w[d];
+    }
+}
+
+// vec_add.wgsl
+__global__ void add_kernel(const float *__restrict__ a, const float *__restrict__ b, float *__restrict__ out, int64_t n)
+{
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = a[i] + b[i];
+}
+
+// silu_mul.wgsl / siluMulRef (src/reference/qwen-ref.ts:119-123): out = gate / (1 + exp(-gate)) * up.
+// gate and up may be two column halves of one [M, 2I] tensor (fused gate_up projection): ld = row pitch.
+__global__ void silu_mul_kernel(const float *__restrict__ gate, const float *__restrict__ up, float *__restrict__ out,
+                                int M, int I, int ld)
+{
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (int64_t)M * I) return;
+    const int m = (int)(idx / I), i = (int)(idx - (int64_t)m * I);
+    const float g = gate[(int64_t)m * ld + i], u = up[(int64_t)m * ld + i];
+    out[idx] = g / (1.f + expf(-g)) * u;
+}
+
+// rope_half.wgsl + kv_store.wgsl (ropeHalfRef, src/reference/qwen-ref.ts:35-64): HF rotate-half with
+// pos = row % T + pos_offset; cos/sin come from a table computed in double on the host. q is rotated in
+// place; k is rotated and, with v, appended to the cache rows [cache_row0 + row] (or written back in
+// place when there is no cache).
+template <typename KV>
+__global__ void rope_kv_kernel(float *__restrict__ q, float *__restrict__ k, const float *__restrict__ v,
+                               KV *__restrict__ k_cache, KV *__restrict__ v_cache, const float *__restrict__ cs_table,
+                               int M, int H, int KVH, int D, int T, const int *__restrict__ pos_offset_ptr,
+                               int pos_offset_imm, int ldq, int ldk, int ldv)
+{
+    const int half = D >> 1;
+    const int per_row = (H + 2 * KVH) * half;
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (int64_t)M * per_row) return;
+    const int row = (int)(idx / per_row);
+    int rem = (int)(idx - (int64_t)row * per_row);
+    const int pos_offset = pos_offset_ptr ? *pos_offset_ptr : pos_offset_imm;
+    const int pos = row % T + pos_offset;
+    const int hh = rem / half, i = rem - hh * half;
+    const float c = cs_table[((int64_t)pos * half + i) * 2], s = cs_table[((int64_t)pos * half + i) * 2 + 1];
+    if (hh < H) {
+        float *p = q + (int64_t)row * ldq + hh * D;
+        const float x0 = p[i], x1 = p[i + half];
+        p[i] = x0 * c - x1 * s;
+        p[i + half] = x0 * s + x1 * c;
+    } else if (hh < H + KVH) {
+        const int kh = hh - H;
+        float *p = k + (int64_t)row * ldk + kh * D;
+        const float x0 = p[i], x1 = p[i + half];
+        const float r0 = x0 * c - x1 * s, r1 = x0 * s + x1 * c;
+        if (k_cache) {
+            KV *dst = k_cache + ((int64_t)(pos_offset + row) * KVH + kh) * D;
+            dst[i] = (KV)r0;
+            dst[i + half] = (KV)r1;
+        } else {
+            p[i] = r0;
+            p[i + half] = r1;
+        }
+    } else if (v_cache) {
+        const int vh = hh - H - KVH;
+        const float *p = v + (int64_t)row * ldv + vh * D;
+        KV *dst = v_cache + ((int64_t)(pos_offset + row) * KVH + vh) * D;
+        dst[i] = (KV)p[i];
+        dst[i + half] = (KV)p[i + half];
+    }
+}
+
+__device__ __forceinline__ float kv_load(const float *p) { return *p; }
+__device__ __forceinline__ float kv_load(const __half *p) { return __half2float(*p); }
+
+// attention_gqa_cache.wgsl / attention_gqa.wgsl (attentionGqaRef, src/reference/qwen-ref.ts:67-116): one
+// block per (query row, head). Keys/values are rows of `kmem`/`vmem` with pitch kv_ld: the KV cache, or
+// the current k/v tensors when there is no cache. Row r sees keys [key_row0(r), key_row0(r) + n_keys(r)):
+//   cache:    key_row0 = 0,           n_keys = past + r + 1
+//   no cache: key_row0 = (r / T) * T, n_keys = r % T + 1
+// Unlike the reference kernel there is no 512-key cap: scores live in dynamic shared memory.
+template <typename KV>
+__global__ void __launch_bounds__(128) attention_kernel(const float *__restrict__ q, const KV *__restrict__ kmem,
+                                                        const KV *__restrict__ vmem, float *__restrict__ out, int H,
+                                                        int KVH, int D, int T, const int *__restrict__ past_ptr,
+                                                        int past_imm, int use_cache, int ldq, int kv_ld, float scale)
+{
+    extern __shared__ float sm[];  // [D] query, [n_keys] scores
+    __shared__ float red[4];
+    const int row = blockIdx.x, h = blockIdx.y, kvh = h / (H / KVH);
+    const int past = past_ptr ? *past_ptr : past_imm;
+    const int key_row0 = use_cache ? 0 : (row / T) * T;
+    const int n_keys = use_cache ? past + row + 1 : row % T + 1;
+    float *qs = sm, *sc = sm + D;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) qs[d] = q[(int64_t)row * ldq + h * D + d];
+    __syncthreads();
+
+    // scores: one warp per key, lanes stride the head dimension
+    float lmax = -INFINITY;
+    for (int s = warp; s < n_keys; s += nw) {
+        const KV *kp = kmem + (int64_t)(key_row0 + s) * kv_ld + kvh * D;
+        float dot = 0.f;
+        for (int d = lane; d < D; d += 32) dot = fmaf(qs[d], kv_load(kp + d), dot);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+        dot *= scale;
+        if (lane == 0) sc[s] = dot;
+        lmax = fmaxf(lmax, dot);
+    }
+    if (lane == 0) red[warp] = lmax;
+    __syncthreads();
+    float mx = red[0];
+    for (int i = 1; i < nw; i++) mx = fmaxf(mx, red[i]);
+    __syncthreads();
+    float lsum = 0.f;
+    for (int s = threadIdx.x; s < n_keys; s += blockDim.x) {
+        const float e = expf(sc[s] - mx);
+        sc[s] = e;
+        lsum += e;
+    }
+    const float total = block_sum(lsum, red);
+    const float inv = 1.f / total;
+    // out[d] = sum_s p[s] v[s, d]: threads own d (coalesced across the value row), keys in order
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float acc = 0.f;
+        const KV *vp = vmem + (int64_t)key_row0 * kv_ld + kvh * D + d;
+        for (int s = 0; s < n_keys; s++) acc = fmaf(sc[s] * inv, kv_load(vp + (int64_t)s * kv_ld), acc);
+        out[(int64_t)row * (H * D) + h * D + d] = acc;
+    }
+}
+
+// Greedy sampling (sampleToken with temperature <= 0, src/infer/sampler.ts:30-36): index of the first
+// strict maximum. Stage 1: per-block (value, index) candidates; stage 2: one block reduces them.
+__global__ void __launch_bounds__(256) argmax_stage1(const float *__restrict__ logits, int V, float *__restrict__ bval,
+                                                     int *__restrict__ bidx)
+{
+    __shared__ float sv[256];
+    __shared__ int si[256];
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < V; i += gridDim.x * blockDim.x) {
+        const float v = logits[i];
+        if (v > best || (v == best && i < bi)) best = v, bi = i;
+    }
+    sv[threadIdx.x] = best, si[threadIdx.x] = bi;
+    __syncthreads();
+    for (int o = 128; o > 0; o >>= 1) {
+        if (threadIdx.x < o) {
+            const float v = sv[threadIdx.x + o];
+            const int i = si[threadIdx.x + o];
+            if (v > sv[threadIdx.x] || (v == sv[threadIdx.x] && i < si[threadIdx.x])) sv[threadIdx.x] = v, si[threadIdx.x] = i;
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) bval[blockIdx.x] = sv[0], bidx[blockIdx.x] = si[0];
+}
+
+// Stage 2 also advances the decode state on the device: next token -> token buffer and output ring,
+// cache length += 1, so that a captured graph can be replayed step after step with no host round trip.
+__global__ void __launch_bounds__(256) argmax_stage2(const float *__restrict__ bval, const int *__restrict__ bidx, int nb,
+                                                     uint32_t *__restrict__ token_out, uint32_t *__restrict__ history,
+                                                     int *__restrict__ step_counter, int *__restrict__ cache_len)
+{
+    __shared__ float sv[256];
+    __shared__ int si[256];
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < nb; i += blockDim.x) {
+        const float v = bval[i];
+        const int ix = bidx[i];
+        if (v > best || (v == best && ix < bi)) best = v, bi = ix;
+    }
+    sv[threadIdx.x] = best, si[threadIdx.x] = bi;
+    __syncthreads();
+    for (int o = 128; o > 0; o >>= 1) {
+        if (threadIdx.x < o) {
+            const float v = sv[threadIdx.x + o];
+            const int i = si[threadIdx.x + o];
+            if (v > sv[threadIdx.x] || (v == sv[threadIdx.x] && i < si[threadIdx.x])) sv[threadIdx.x] = v, si[threadIdx.x] = i;
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        const uint32_t tok = si[0] == 0x7fffffff ? 0u : (uint32_t)si[0];  // all-NaN logits: JS returns index 0
+        *token_out = tok;
+        if (history) {
+            history[*step_counter] = tok;
+            *step_counter += 1;
+        }
+        if (cache_len) *cache_len += 1;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------
+
+#define LAUNCH_OK(ctx)                \
+    do {                              \
+        (ctx)->launches++;            \
+        WB_CUDA(cudaGetLastError());  \
+        return WB_OK;                 \
+    } while (0)
+
+int op_embed(wb_context *ctx, const __half *table, const uint32_t *tokens, float *x, int M, int C, int vocab)
+{
+    const int64_t n = (int64_t)M * C;
+    embed_f16_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(table, tokens, x, M, C, vocab);
+    LAUNCH_OK(ctx);
+}
+
+int op_rmsnorm(wb_context *ctx, const float *x, const float *delta, float *x_out, const float *w, float *y, int M, int D, float eps)
+{
+    rmsnorm_kernel<<<M, 256, 0, ctx->stream>>>(x, delta, x_out, w, y, D, eps);
+    LAUNCH_OK(ctx);
+}
+
+int op_add(wb_context *ctx, const float *a, const float *b, float *out, int64_t n)
+{
+    add_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(a, b, out, n);
+    LAUNCH_OK(ctx);
+}
+
+int op_silu_mul(wb_context *ctx, const float *gate, const float *up, float *out, int M, int I, int ld)
+{
+    const int64_t n = (int64_t)M * I;
+    silu_mul_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(gate, up, out, M, I, ld);
+    LAUNCH_OK(ctx);
+}
+
+int op_rope_kv(wb_context *ctx, float *q, float *k, const float *v, void *k_cache, void *v_cache, int kv_f16,
+               const float *cs_table, int M, int H, int KVH, int D, int T, const int *pos_ptr, int pos_imm, int ldq,
+               int ldk, int ldv)
+{
+    const int64_t n = (int64_t)M * (H + 2 * KVH) * (D / 2);
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    if (kv_f16)
+        rope_kv_kernel<__half><<<blocks, 256, 0, ctx->stream>>>(q, k, v, (__half *)k_cache, (__half *)v_cache, cs_table, M, H,
+                                                                 KVH, D, T, pos_ptr, pos_imm, ldq, ldk, ldv);
+    else
+        rope_kv_kernel<float><<<blocks, 256, 0, ctx->stream>>>(q, k, v, (float *)k_cache, (float *)v_cache, cs_table, M, H, KVH,
+                                                                D, T, pos_ptr, pos_imm, ldq, ldk, ldv);
+    LAUNCH_OK(ctx);
+}
+
+int op_attention(wb_context *ctx, const float *q, const void *kmem, const void *vmem, int kv_f16, float *out, int M, int H,
+                 int KVH, int D, int T, const int *past_ptr, int past_imm, int use_cache, int max_keys, int ldq, int kv_ld)
+{
+    const size_t smem = (size_t)(D + max_keys) * sizeof(float);
+    const float scale = 1.0f / sqrtf((float)D);
+    dim3 grid(M, H);
+    if (kv_f16) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(attention_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        attention_kernel<__half><<<grid, 128, smem, ctx->stream>>>(q, (const __half *)kmem, (const __half *)vmem, out, H, KVH, D, T,
+                                                                    past_ptr, past_imm, use_cache, ldq, kv_ld, scale);
+    } else {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(attention_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        attention_kernel<float><<<grid, 128, smem, ctx->stream>>>(q, (const float *)kmem, (const float *)vmem, out, H, KVH, D, T,
+                                                                   past_ptr, past_imm, use_cache, ldq, kv_ld, scale);
+    }
+    LAUNCH_OK(ctx);
+}
+
+int op_argmax(wb_context *ctx, const float *logits, int V, float *bval, int *bidx, uint32_t *token_out, uint32_t *history,
+              int *step_counter, int *cache_len)
+{
+    const int nb = 128;
+    argmax_stage1<<<nb, 256, 0, ctx->stream>>>(logits, V, bval, bidx);
+    ctx->launches++;
+    argmax_stage2<<<1, 256, 0, ctx->stream>>>(bval, bidx, nb, token_out, history, step_counter, cache_len);
+    LAUNCH_OK(ctx);
+}
+
+}  // namespace wb

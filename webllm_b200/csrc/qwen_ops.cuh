@@ -1,0 +1,22 @@
+// Host entry points of the non-linear Qwen2 forward steps (qwen_ops.cu).
+#pragma once
+#include "common.cuh"
+
+namespace wb {
+
+int op_embed(wb_context *ctx, const __half *table, const uint32_t *tokens, float *x, int M, int C, int vocab);
+// y = rmsnorm(x + delta) * w; when delta != nullptr the sum is also stored to x_out (residual stream).
+int op_rmsnorm(wb_context *ctx, const float *x, const float *delta, float *x_out, const float *w, float *y, int M, int D, float eps);
+int op_add(wb_context *ctx, const float *a, const float *b, float *out, int64_t n);
+int op_silu_mul(wb_context *ctx, const float *gate, const float *up, float *out, int M, int I, int ld);
+// Rotates q in place and k (into the cache when k_cache != nullptr, else in place); copies v to the cache.
+// The position offset is read from pos_ptr when it is not null (graph replay), else pos_imm.
+int op_rope_kv(wb_context *ctx, float *q, float *k, const float *v, void *k_cache, void *v_cache, int kv_f16,
+               const float *cs_table, int M, int H, int KVH, int D, int T, const int *pos_ptr, int pos_imm, int ldq,
+               int ldk, int ldv);
+int op_attention(wb_context *ctx, const float *q, const void *kmem, const void *vmem, int kv_f16, float *out, int M, int H,
+                 int KVH, int D, int T, const int *past_ptr, int past_imm, int use_cache, int max_keys, int ldq, int kv_ld);
+int op_argmax(wb_context *ctx, const float *logits, int V, float *bval, int *bidx, uint32_t *token_out, uint32_t *history,
+              int *step_counter, int *cache_len);
+
+}  // namespace wb
