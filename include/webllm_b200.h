@@ -31,6 +31,7 @@ extern "C" {
 
 typedef struct wb_context wb_context;
 typedef struct wb_qwen wb_qwen;
+typedef struct wb_batch wb_batch;
 typedef int32_t wb_handle; /* index of a registered weight; < 0 = none */
 
 typedef enum {
@@ -161,6 +162,15 @@ WB_API int wb_plan_query(wb_context *ctx, wb_handle weight, int64_t M, int act_d
  * Used by tests to cover every path at every shape, as the reference's tests drive the split kernel with
  * explicit S (src/tests/kernels.ts:1378-1400). */
 WB_API int wb_plan_override(wb_context *ctx, int kernel, int split_k);
+
+/* ---- command batches. Replaces CommandBatch (src/gpu/pipeline.ts:55-117): every wb_linear /
+ *      wb_gptq_dequant call between begin and end is recorded instead of run; wb_batch_submit enqueues
+ *      the whole recording in one go and may be repeated. Transfers and wb_synchronize are not allowed
+ *      while recording. Offsets and handles are baked in: keep the tensors alive while the batch is. ---- */
+WB_API int wb_batch_begin(wb_context *ctx);
+WB_API int wb_batch_end(wb_context *ctx, wb_batch **out);
+WB_API int wb_batch_submit(wb_batch *batch);
+WB_API int wb_batch_destroy(wb_batch *batch);
 
 /* ---- Qwen2 forward. Replaces QwenGpt (src/model/qwen.ts:124-531) for the quantized-linear path and the
  *      decode loop of generateQwen (src/infer/qwen-generate.ts:29-84). Weights are looked up by the

@@ -84,6 +84,10 @@ SIGNATURES = {
     "wb_linear": [_vp, C.c_int32, _u64, _u64, C.c_int32, _i64, _i32, _i32, _i32],
     "wb_plan_query": [_vp, C.c_int32, _i64, _i32, _i32, C.POINTER(Plan)],
     "wb_plan_override": [_vp, _i32, _i32],
+    "wb_batch_begin": [_vp],
+    "wb_batch_end": [_vp, C.POINTER(_vp)],
+    "wb_batch_submit": [_vp],
+    "wb_batch_destroy": [_vp],
     "wb_qwen_create": [_vp, C.POINTER(QwenConfigC), C.POINTER(_vp)],
     "wb_qwen_destroy": [_vp],
     "wb_qwen_reset_cache": [_vp],

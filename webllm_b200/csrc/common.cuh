@@ -80,6 +80,8 @@ struct wb_context {
     uint64_t launches = 0;
     int force_kernel = 0, force_split = 0;
     void *tmap_encode = nullptr;     // cuTensorMapEncodeTiled, resolved at context creation
+    bool capturing = false;          // a command batch is being recorded (batch.cu)
+    uint64_t launches_at_capture = 0;
 };
 
 namespace wb {

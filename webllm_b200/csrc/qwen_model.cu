@@ -40,7 +40,8 @@ struct wb_qwen {
     // device-resident decode state and M = 1 buffers (stable addresses for the captured graph)
     Bufs dec{};
     int *d_cache_len = nullptr, *d_step = nullptr, *d_bidx = nullptr;
-    float *d_bval = nullptr;
+    float *d_bval = nullptr, *att_scratch = nullptr;
+    unsigned *att_counters = nullptr;
     uint32_t *d_history = nullptr;
     int64_t history_cap = 0;
     cudaGraphExec_t graph = nullptr;
@@ -155,6 +156,10 @@ int forward_impl(wb_qwen *m, const Bufs &b, int64_t M, int64_t B, int64_t T, int
                             b.ldq, b.ldk, b.ldv));
         if (use_cache) {
             const int max_keys = past_ptr ? m->cfg.max_t : (int)(past + M);
+            if (M == 1 && D % 8 == 0 && D <= 128 && (size_t)(5 * D + max_keys / 8 + 1) * 4 <= 48 * 1024) {
+                WB_CHECK(op_attention_decode(ctx, b.q, kc, vc, kv16, b.att, m->att_scratch, m->att_counters, H, KVH, D, past_ptr,
+                                             (int)past, max_keys, KV));
+            } else
             WB_CHECK(op_attention(ctx, b.q, kc, vc, kv16, b.att, (int)M, H, KVH, D, (int)T, past_ptr, (int)past, 1, max_keys,
                                   b.ldq, KV));
         } else {
@@ -279,6 +284,9 @@ int wb_qwen_create(wb_context *ctx, const wb_qwen_config *cfg, wb_qwen **out)
     WB_CHECK(carve_t(ctx, WB_ARENA_WEIGHTS, 128, &m->d_bval));
     WB_CHECK(carve_t(ctx, WB_ARENA_WEIGHTS, 128, &m->d_bidx));
     WB_CUDA(cudaMemsetAsync(m->d_cache_len, 0, 64 * sizeof(int), ctx->stream));
+    WB_CHECK(carve_t(ctx, WB_ARENA_WEIGHTS, (uint64_t)op_attention_decode_scratch_floats(m->H, m->D), &m->att_scratch));
+    WB_CHECK(carve_t(ctx, WB_ARENA_WEIGHTS, (uint64_t)m->H, &m->att_counters));
+    WB_CUDA(cudaMemsetAsync(m->att_counters, 0, (size_t)m->H * sizeof(unsigned), ctx->stream));
     WB_CUDA(cudaStreamSynchronize(ctx->stream));
     *out = m.release();
     return WB_OK;

@@ -181,6 +181,124 @@ __global__ void __launch_bounds__(128) attention_kernel(const float *__restrict_
     }
 }
 
+// Decode-time attention (one query row against the whole cache), attention_gqa_cache.wgsl for M = 1. The
+// reference gives one workgroup per head the whole key range; here the keys are also split over
+// ATT_SPLITS CTAs per head so that 14 heads x 8 slices fill the GPU, each slice keeps an online-softmax
+// triple (max, sum, weighted values), and the last slice to arrive for a head (arrival counter, no
+// waiting) merges the triples in slice order.
+constexpr int ATT_SPLITS = 8;
+
+template <typename KV>
+__device__ __forceinline__ float dot_row(const float *qs, const KV *kp, int D);
+
+template <>
+__device__ __forceinline__ float dot_row<__half>(const float *qs, const __half *kp, int D)
+{
+    float dot = 0.f;
+    for (int d = 0; d < D; d += 8) {
+        const uint4 raw = *reinterpret_cast<const uint4 *>(kp + d);
+        const __half2 *h = reinterpret_cast<const __half2 *>(&raw);
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const float2 f = __half22float2(h[j]);
+            dot = fmaf(qs[d + 2 * j], f.x, dot);
+            dot = fmaf(qs[d + 2 * j + 1], f.y, dot);
+        }
+    }
+    return dot;
+}
+
+template <>
+__device__ __forceinline__ float dot_row<float>(const float *qs, const float *kp, int D)
+{
+    float dot = 0.f;
+    for (int d = 0; d < D; d += 4) {
+        const float4 f = *reinterpret_cast<const float4 *>(kp + d);
+        dot = fmaf(qs[d], f.x, dot), dot = fmaf(qs[d + 1], f.y, dot);
+        dot = fmaf(qs[d + 2], f.z, dot), dot = fmaf(qs[d + 3], f.w, dot);
+    }
+    return dot;
+}
+
+template <typename KV>
+__global__ void __launch_bounds__(128) attention_decode_kernel(const float *__restrict__ q, const KV *__restrict__ kmem,
+                                                               const KV *__restrict__ vmem, float *__restrict__ out,
+                                                               float *__restrict__ scratch, unsigned *__restrict__ counters,
+                                                               int H, int KVH, int D, const int *__restrict__ past_ptr,
+                                                               int past_imm, int kv_ld, float scale)
+{
+    extern __shared__ float sm[];  // [D] query (pre-scaled), [chunk] scores, [4][D] per-warp value sums
+    __shared__ float red[4];
+    __shared__ int is_last;
+    const int h = blockIdx.x, s = blockIdx.y, kvh = h / (H / KVH);
+    const int n_keys = (past_ptr ? *past_ptr : past_imm) + 1;
+    const int chunk = (n_keys + ATT_SPLITS - 1) / ATT_SPLITS;
+    const int k0 = s * chunk, k1 = min(n_keys, k0 + chunk), nk = max(0, k1 - k0);
+    float *qs = sm, *sc = sm + D, *wacc = sm + D + chunk;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    for (int d = tid; d < D; d += blockDim.x) qs[d] = q[h * D + d] * scale;
+    __syncthreads();
+
+    float lmax = -INFINITY;
+    for (int j = tid; j < nk; j += blockDim.x) {
+        const float dot = dot_row<KV>(qs, kmem + (int64_t)(k0 + j) * kv_ld + kvh * D, D);
+        sc[j] = dot;
+        lmax = fmaxf(lmax, dot);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) lmax = fmaxf(lmax, __shfl_xor_sync(0xffffffffu, lmax, o));
+    if (lane == 0) red[warp] = lmax;
+    __syncthreads();
+    const float mx = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+    __syncthreads();
+    float lsum = 0.f;
+    for (int j = tid; j < nk; j += blockDim.x) {
+        const float e = expf(sc[j] - mx);
+        sc[j] = e;
+        lsum += e;
+    }
+    const float total = block_sum(lsum, red);  // also orders the sc[] writes before the reads below
+    // weighted values: warp w takes keys w, w+4, ...; lane owns dims 2*lane, 2*lane+1 (and +64 for D = 128)
+    for (int d0 = 0; d0 < D; d0 += 64) {
+        float a0 = 0.f, a1 = 0.f;
+        const int d = d0 + 2 * lane;
+        if (d < D)
+            for (int j = warp; j < nk; j += 4) {
+                const KV *vp = vmem + (int64_t)(k0 + j) * kv_ld + kvh * D + d;
+                a0 = fmaf(sc[j], kv_load(vp), a0);
+                a1 = fmaf(sc[j], kv_load(vp + 1), a1);
+            }
+        if (d < D) wacc[warp * D + d] = a0, wacc[warp * D + d + 1] = a1;
+    }
+    __syncthreads();
+    float *slot = scratch + ((int64_t)h * ATT_SPLITS + s) * (D + 2);
+    for (int d = tid; d < D; d += blockDim.x) slot[2 + d] = wacc[d] + wacc[D + d] + wacc[2 * D + d] + wacc[3 * D + d];
+    if (tid == 0) slot[0] = mx, slot[1] = total;
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) is_last = (atomicAdd(&counters[h], 1u) == (unsigned)(ATT_SPLITS - 1));
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    const float *base = scratch + (int64_t)h * ATT_SPLITS * (D + 2);
+    float M = -INFINITY;
+    for (int i = 0; i < ATT_SPLITS; i++) M = fmaxf(M, __ldcg(base + i * (D + 2)));
+    float Lsum = 0.f;
+    for (int i = 0; i < ATT_SPLITS; i++) {
+        const float mi = __ldcg(base + i * (D + 2)), li = __ldcg(base + i * (D + 2) + 1);
+        if (li > 0.f) Lsum += li * expf(mi - M);
+    }
+    for (int d = tid; d < D; d += blockDim.x) {
+        float acc = 0.f;
+        for (int i = 0; i < ATT_SPLITS; i++) {
+            const float mi = __ldcg(base + i * (D + 2)), li = __ldcg(base + i * (D + 2) + 1);
+            if (li > 0.f) acc = fmaf(__ldcg(base + i * (D + 2) + 2 + d), expf(mi - M), acc);
+        }
+        out[h * D + d] = acc / Lsum;
+    }
+    if (tid == 0) counters[h] = 0u;
+}
+
 // Greedy sampling (sampleToken with temperature <= 0, src/infer/sampler.ts:30-36): index of the first
 // strict maximum. Stage 1: per-block (value, index) candidates; stage 2: one block reduces them.
 __global__ void __launch_bounds__(256) argmax_stage1(const float *__restrict__ logits, int V, float *__restrict__ bval,
@@ -310,6 +428,26 @@ int op_attention(wb_context *ctx, const float *q, const void *kmem, const void *
     }
     LAUNCH_OK(ctx);
 }
+
+int op_attention_decode(wb_context *ctx, const float *q, const void *kmem, const void *vmem, int kv_f16, float *out,
+                        float *scratch, unsigned *counters, int H, int KVH, int D, const int *past_ptr, int past_imm,
+                        int max_keys, int kv_ld)
+{
+    const int chunk = (max_keys + ATT_SPLITS - 1) / ATT_SPLITS;
+    const size_t smem = (size_t)(5 * D + chunk) * sizeof(float);
+    const float scale = 1.0f / sqrtf((float)D);
+    dim3 grid(H, ATT_SPLITS);
+    if (kv_f16)
+        attention_decode_kernel<__half><<<grid, 128, smem, ctx->stream>>>(q, (const __half *)kmem, (const __half *)vmem, out,
+                                                                           scratch, counters, H, KVH, D, past_ptr, past_imm,
+                                                                           kv_ld, scale);
+    else
+        attention_decode_kernel<float><<<grid, 128, smem, ctx->stream>>>(q, (const float *)kmem, (const float *)vmem, out, scratch,
+                                                                          counters, H, KVH, D, past_ptr, past_imm, kv_ld, scale);
+    LAUNCH_OK(ctx);
+}
+
+int op_attention_decode_scratch_floats(int H, int D) { return H * ATT_SPLITS * (D + 2); }
 
 int op_argmax(wb_context *ctx, const float *logits, int V, float *bval, int *bidx, uint32_t *token_out, uint32_t *history,
               int *step_counter, int *cache_len)

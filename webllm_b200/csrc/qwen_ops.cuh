@@ -16,6 +16,12 @@ int op_rope_kv(wb_context *ctx, float *q, float *k, const float *v, void *k_cach
                int ldk, int ldv);
 int op_attention(wb_context *ctx, const float *q, const void *kmem, const void *vmem, int kv_f16, float *out, int M, int H,
                  int KVH, int D, int T, const int *past_ptr, int past_imm, int use_cache, int max_keys, int ldq, int kv_ld);
+// One query row against the cache, keys split over several CTAs per head; scratch holds the per-slice
+// softmax state (op_attention_decode_scratch_floats floats), counters one zeroed word per head.
+int op_attention_decode(wb_context *ctx, const float *q, const void *kmem, const void *vmem, int kv_f16, float *out,
+                        float *scratch, unsigned *counters, int H, int KVH, int D, const int *past_ptr, int past_imm,
+                        int max_keys, int kv_ld);
+int op_attention_decode_scratch_floats(int H, int D);
 int op_argmax(wb_context *ctx, const float *logits, int V, float *bval, int *bidx, uint32_t *token_out, uint32_t *history,
               int *step_counter, int *cache_len);
 

@@ -168,8 +168,37 @@ class Gpu:
                                         1 if exact else 0, C.byref(p)))
         return p.as_dict()
 
+    def batch(self) -> "CommandBatch":
+        return CommandBatch(self)
+
     def plan_override(self, kernel: int = 0, split_k: int = 0) -> None:
         L.check(self._lib.wb_plan_override(self._ctx, kernel, split_k))
+
+
+class CommandBatch:
+    """``CommandBatch`` (src/gpu/pipeline.ts:55-117): ``with gpu.batch() as b: gpu.linear(...)`` records the
+    calls; ``b.submit()`` enqueues the whole recording at once and can be repeated."""
+
+    def __init__(self, gpu: "Gpu"):
+        self._gpu, self._handle = gpu, C.c_void_p()
+
+    def __enter__(self):
+        L.check(self._gpu._lib.wb_batch_begin(self._gpu.ctx))
+        return self
+
+    def __exit__(self, exc_type, exc, tb):
+        rc = self._gpu._lib.wb_batch_end(self._gpu.ctx, C.byref(self._handle))
+        if exc_type is None:
+            L.check(rc)
+        return False
+
+    def submit(self) -> None:
+        L.check(self._gpu._lib.wb_batch_submit(self._handle))
+
+    def destroy(self) -> None:
+        if self._handle:
+            self._gpu._lib.wb_batch_destroy(self._handle)
+            self._handle = C.c_void_p()
 
 
 class Arena:
