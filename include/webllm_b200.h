@@ -209,6 +209,28 @@ WB_API int wb_qwen_decode_greedy(wb_qwen *model, uint32_t first_token, int64_t n
 /* Logits of the last step run by wb_qwen_decode_greedy, [V] f32, copied to the host. */
 WB_API int wb_qwen_last_logits(wb_qwen *model, float *out);
 
+/* ---- allocation-free GEMV. No counterpart in the reference (its split-K scratch comes from the arena,
+ *      src/model/qwen.ts:584); added for hosts that may not allocate device memory where they run the
+ *      kernel: a real-time loop or driver callback where the allocator is off limits, a sandboxed plugin
+ *      that was handed its buffers up front, an application that owns every byte of the GPU and passes a
+ *      plugin only input and output pointers. It needs no context and calls no cudaMalloc / cudaFree or
+ *      any allocating routine: the split-K partial sums and arrival counters live in a 4 MiB + 16 KiB
+ *      array inside the library image (held by every GPU that loads the library until the process exits).
+ *
+ *      y[M,N] = x[M,K] . W[N,K]^T (+ bias) for one GPTQ linear given as raw DEVICE pointers in the
+ *      checkpoint layout (see wb_gptq_register; qzeros and bias may be NULL), on the current device and the
+ *      given cudaStream_t (NULL = default stream). split_k <= 0 picks a split automatically.
+ *      Limits: M <= 32, K % 8 == 0, N % 4 == 0, group % 128 == 0, N <= 131072 * (1, 2 or 4 for M <= 2, 4, 32),
+ *      and split_k * M * N * 4 bytes <= 4 MiB; anything beyond is refused with WB_ERR_UNSUPPORTED and a
+ *      message, never truncated.
+ *      The first call on a device looks up the array's device address (cudaGetSymbolAddress): make that
+ *      call before any stream capture. All calls on a device share the array, which keeps the previous
+ *      call's contents; each call re-zeroes the counters it uses on its stream, so calls that run one after
+ *      another are safe, while calls that overlap on the GPU (different streams) race on it. ------------ */
+WB_API int wb_gptq_gemv_static(const void *qweight, const void *qzeros, const void *scales_f16, const void *x, void *y,
+                               const float *bias, int64_t in_features, int64_t out_features, int64_t group_size,
+                               int64_t M, int act_dtype, int out_dtype, int split_k, void *cuda_stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -2,6 +2,8 @@
 // lm_head) and the shape-agnostic kernel for ragged sizes. Together with gemm_tc.cu they replace the four
 // WGSL kernels behind QwenGpt.gemm (src/model/qwen.ts:568-618): gemm_gemv_f16.wgsl,
 // gemm_gemv_split_f16.wgsl, gemm_gemv_split_reduce.wgsl and gemm_nt_f16_from_f32.wgsl.
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace wb {
@@ -607,3 +609,105 @@ int launch_linear(wb_context *ctx, const Weight &w, const void *A, void *C, cons
 }
 
 }  // namespace wb
+
+// =====================================================================================================
+// wb_gptq_gemv_static: the split-K int4 GEMV for callers that must not allocate device memory.
+//
+// Some hosts cannot call cudaMalloc where they run this kernel: code inside a region where the allocator
+// is off limits (a real-time audio/control loop, a driver callback, a sandboxed plugin that was handed
+// its buffers up front), or an embedding application that owns every byte of the GPU and gives a plugin
+// only input and output pointers. The regular path needs a context, and creating one allocates the
+// workspace where split-K slices park their partial sums. Here that workspace is a fixed array inside the
+// library image instead; every GPU that loads the library carries it until the process exits.
+// =====================================================================================================
+namespace {
+
+constexpr size_t kStaticCounterWords = 4096;                 // one arrival counter per column tile
+constexpr size_t kStaticPartialBytes = 4u << 20;             // split-K partial sums
+constexpr size_t kStaticScratchBytes = kStaticCounterWords * sizeof(unsigned) + kStaticPartialBytes;
+
+// Counters first (they must be zero when a call starts), partial sums after them.
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+void *g_static_scratch_addr[kMaxDevices] = {};  // device address of g_static_scratch, per device ordinal
+
+}  // namespace
+
+extern "C" int wb_gptq_gemv_static(const void *qweight, const void *qzeros, const void *scales_f16, const void *x,
+                                   void *y, const float *bias, int64_t in_features, int64_t out_features,
+                                   int64_t group_size, int64_t M, int act_dtype, int out_dtype, int split_k,
+                                   void *cuda_stream)
+{
+    using namespace wb;
+    if (!qweight || !scales_f16 || !x || !y) return fail(WB_ERR_BAD_ARG, "wb_gptq_gemv_static: NULL device pointer");
+    if ((act_dtype != WB_F32 && act_dtype != WB_F16) || (out_dtype != WB_F32 && out_dtype != WB_F16))
+        return fail(WB_ERR_BAD_ARG, "wb_gptq_gemv_static: dtype must be WB_F32 or WB_F16");
+    const int64_t K = in_features, N = out_features;
+    if (K <= 0 || N <= 0 || M <= 0) return fail(WB_ERR_BAD_ARG, "wb_gptq_gemv_static: sizes must be positive");
+    if (M > 32 || K % 8 != 0 || N % 4 != 0 || group_size <= 0 || group_size % 128 != 0)
+        return fail(WB_ERR_UNSUPPORTED, "wb_gptq_gemv_static needs M <= 32, K %% 8 == 0, N %% 4 == 0, group %% 128 == 0");
+    int device = 0;
+    WB_CUDA(cudaGetDevice(&device));
+    if (device < 0 || device >= kMaxDevices) return fail(WB_ERR_UNSUPPORTED, "device ordinal %d is beyond %d", device, kMaxDevices);
+    if (!g_static_scratch_addr[device]) {
+        // In host code the array's name is only a handle; its device address has to be asked for, once per
+        // device, with that device current. This is the set-up the first call on a device performs.
+        void *p = nullptr;
+        WB_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
+        g_static_scratch_addr[device] = p;
+    }
+    unsigned *counters = (unsigned *)g_static_scratch_addr[device];
+    float *partial = (float *)((unsigned char *)g_static_scratch_addr[device] + kStaticCounterWords * sizeof(unsigned));
+
+    // launch shape: the regular planner's layout for M, the caller's (or a simple automatic) split
+    const int pack_rows = (int)(K / 8), chunks = (pack_rows + 15) / 16, col_tiles = (int)((N + 31) / 32);
+    int wn = M <= 2 ? 1 : (M <= 4 ? 2 : 4);
+    while (wn > 1 && col_tiles < wn) wn >>= 1;
+    int wk = wn == 4 ? 4 : 8;
+    if (wk > chunks) wk = chunks;
+    const int ctas_n = (col_tiles + wn - 1) / wn;
+    int S = split_k;
+    if (S <= 0) {
+        int sms = 148;
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+        const int per_warp = (chunks + wk - 1) / wk;
+        S = (ctas_n < 2 * sms && per_warp > 2) ? std::min((per_warp + 1) / 2, (2 * sms + ctas_n - 1) / ctas_n) : 1;
+    }
+    if (S > chunks) S = chunks;
+    const int cps = (chunks + S - 1) / S;
+    S = (chunks + cps - 1) / cps;
+    const bool two_halves = act_dtype == WB_F32;
+    const int MB = M <= 8 ? 1 : (M <= 16 ? 2 : 4);
+    const int xs_stride = cps * 16 + 4;
+    const size_t xs_bytes = (size_t)M * xs_stride * 16 * (two_halves ? 2 : 1);
+    const size_t red_bytes = (size_t)wn * wk * MB * 8 * 32 * 4;
+    const size_t smem = xs_bytes > red_bytes ? xs_bytes : red_bytes;
+    if (smem > (size_t)kGemvSmemLimit)
+        return fail(WB_ERR_UNSUPPORTED, "wb_gptq_gemv_static: %lld x %lld activations per slice do not fit shared memory; raise split_k",
+                    (long long)M, (long long)(cps * 128));
+    if ((size_t)ctas_n > kStaticCounterWords)
+        return fail(WB_ERR_UNSUPPORTED, "wb_gptq_gemv_static: N = %lld needs %d column-tile counters, the static scratch holds %zu",
+                    (long long)N, ctas_n, kStaticCounterWords);
+    if (S > 1 && (size_t)S * M * N * sizeof(float) > kStaticPartialBytes)
+        return fail(WB_ERR_UNSUPPORTED,
+                    "wb_gptq_gemv_static: split_k * M * N * 4 = %zu bytes of partial sums exceed the static scratch of %zu bytes",
+                    (size_t)S * M * N * sizeof(float), kStaticPartialBytes);
+
+    cudaStream_t st = (cudaStream_t)cuda_stream;
+    // The array keeps whatever the previous call left; the counters must start at zero.
+    if (S > 1) WB_CUDA(cudaMemsetAsync(counters, 0, (size_t)ctas_n * sizeof(unsigned), st));
+    GemvParams p;
+    p.qw = (const uint32_t *)qweight, p.qz = (const uint32_t *)qzeros, p.sc = (const __half *)scales_f16;
+    p.x = x, p.out = y, p.bias = bias, p.partial = partial, p.counters = counters;
+    p.M = (int)M, p.N = (int)N, p.K = (int)K, p.pack_rows = pack_rows, p.zcols = (int)((N + 7) / 8);
+    p.chunks = chunks, p.chunks_per_split = cps, p.group_chunks = (int)(group_size / 128), p.S = S;
+    p.wn = wn, p.wk = wk, p.x_f16 = act_dtype == WB_F16, p.out_f16 = out_dtype == WB_F16, p.xs_stride = xs_stride;
+    dim3 grid(ctas_n, S);
+    const int block = wn * wk * 32;
+    cudaError_t e = MB == 1   ? launch_gemv_mb<1>(p, grid, block, smem, two_halves, st)
+                    : MB == 2 ? launch_gemv_mb<2>(p, grid, block, smem, two_halves, st)
+                              : launch_gemv_mb<4>(p, grid, block, smem, two_halves, st);
+    WB_CUDA(e);
+    return WB_OK;
+}
