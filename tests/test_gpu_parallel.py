@@ -1,0 +1,95 @@
+"""GPU tests of the output-column-sharded linear: device-side slicing (wb_gptq_register_cols) on one GPU, and the
+NCCL all-gather across ranks when at least two GPUs are visible."""
+import os
+import socket
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from helpers import assert_close, oracle_weight, run_linear
+from webllm_b200 import WebllmError, parallel, synthetic
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+
+@pytest.mark.parametrize("M", [1, 64])
+def test_column_slices_reassemble_to_the_full_product(gpu, oracle, M):
+    """Four column shards of a 7B-class k/v projection (3584 -> 512) registered with wb_gptq_register_cols on one
+    GPU; their outputs side by side equal the unsharded product (streaming kernel at M=1, tensor cores at M=64)."""
+    K, N, G = 3584, 512, 4
+    t = synthetic.random_gptq(K, N, 128, seed=21, zeros="any")
+    W = oracle_weight(oracle, t)
+    x = np.random.default_rng(M).standard_normal((M, K)).astype(np.float16)
+    parts = []
+    for r in range(G):
+        sh = parallel.column_shard(N, r, G)
+        name = f"shard{r}_of{G}"
+        try:
+            h = gpu.weight(name)
+        except WebllmError:
+            h = gpu.gptq_register(name, t.qweight, t.qzeros, t.scales, K, N, 128, 4, cols=(sh.begin, sh.count))
+        parts.append(run_linear(gpu, h, x, M, sh.count, None, act="f16"))
+    got = np.concatenate(parts, axis=1)
+    Wref = oracle.round_f16(W).reshape(N, K) if M > 16 else W
+    ref = oracle.gemm_nt_ref(x.astype(np.float32), Wref, M, N, K, threads=oracle.max_threads())
+    assert_close(oracle, got, ref, 1e-3, f"sharded M={M}")
+    with pytest.raises(WebllmError, match="multiple of 8"):
+        gpu.gptq_register("bad_slice", t.qweight, t.qzeros, t.scales, K, N, 128, 4, cols=(4, 64))
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _nccl_rank(rank, world, port, tmp):
+    sys.path.insert(0, str(ROOT))
+    sys.path.insert(0, str(ROOT / "tests"))
+    import torch
+    import torch.distributed as dist
+    from oracle import oracle
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device(f"cuda:{rank}"))
+    host = parallel.TorchSlabGpu(rank, weight_bytes=256 << 20, act_bytes=256 << 20)
+    try:
+        K, N = 3584, 3584
+        t = synthetic.random_gptq(K, N, 128, seed=5, zeros="any")
+        bias = np.random.default_rng(2).standard_normal(N).astype(np.float32)
+        lin = parallel.ColumnShardedLinear(host, "q7", t, bias)
+        W = oracle.dequantize_gptq_int4(t.qweight, t.qzeros, oracle.f16_bits_to_f32(t.scales.view(np.uint16)), K, N, 128)
+        for M in (1, 48):
+            host.gpu.arena.reset()
+            A = host.gpu.arena.alloc(M * K, [M, K], "f16")
+            Cl = host.gpu.arena.alloc(M * lin.shard.count, [M, lin.shard.count], "f32")
+            x = np.random.default_rng(10 + M).standard_normal((M, K)).astype(np.float16)  # same on every rank
+            host.gpu.write(A, x)
+            y = lin.forward(A, Cl, M)
+            torch.cuda.synchronize()
+            got = y.cpu().numpy()
+            Wref = oracle.round_f16(W).reshape(N, K) if M > 16 else W
+            ref = oracle.gemm_nt_ref(x.astype(np.float32), Wref, M, N, K, bias, threads=4)
+            rms = float(np.sqrt(np.mean(ref.astype(np.float64) ** 2)))
+            r = oracle.check_tolerance(got, ref, 1e-3 * rms, 1e-3)
+            assert got.shape == (M, N) and r.ok, (rank, M, r)
+        Path(tmp, f"ok{rank}").write_text("ok")
+    finally:
+        host.close()
+        dist.destroy_process_group()
+
+
+def test_column_sharded_linear_over_nccl(tmp_path, built_lib, oracle):
+    """7B-class 3584 -> 3584 projection split over every visible GPU (2, 4 or 8), decode (M=1) and a batch that
+    takes the tensor-core kernel; every rank must end with the same full [M, N] as the unsharded oracle."""
+    import torch
+    world = torch.cuda.device_count()
+    world = 8 if world >= 8 else 4 if world >= 4 else 2 if world >= 2 else 1
+    if world < 2:
+        pytest.skip("needs at least two GPUs")
+    import torch.multiprocessing as mp
+    mp.spawn(_nccl_rank, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    assert all((tmp_path / f"ok{r}").exists() for r in range(world))
