@@ -70,7 +70,7 @@ def test_static_scratch_limits_are_refused_not_truncated(built_lib):
     buf = torch.zeros(1 << 20, dtype=torch.int32, device="cuda")
     p = buf.data_ptr()
     # split_k * M * N * 4 beyond the 4 MiB of static partial sums
-    rc = lib.wb_gptq_gemv_static(p, None, p, p, p, None, 18944, 16384, 128, 32, _lib.WB_F16, _lib.WB_F32, 8, None)
+    rc = lib.wb_gptq_gemv_static(p, None, p, p, p, None, 3584, 16384, 128, 32, _lib.WB_F16, _lib.WB_F32, 8, None)
     assert rc == _lib.WB_ERR_UNSUPPORTED and b"exceed the static scratch" in lib.wb_last_error()
     rc = lib.wb_gptq_gemv_static(p, None, p, p, p, None, 896, 4864, 128, 33, _lib.WB_F16, _lib.WB_F32, 0, None)
     assert rc == _lib.WB_ERR_UNSUPPORTED and b"M <= 32" in lib.wb_last_error()

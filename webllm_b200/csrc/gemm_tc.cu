@@ -5,12 +5,12 @@
 //
 // One CTA computes a 128 (output columns n) x MT (tokens m) tile of C^T: the weight tile is the 128-row
 // operand of tcgen05.mma, the activation tile its MT-column operand, the f32 accumulator lives in TMEM
-// (128 lanes x MT columns). Roles, 6 warps:
+// (128 lanes x MT columns). Roles, 10 warps:
 //   warp 0      TMA producer: per 64-k block one box of activations [MT x 64] fp16 (128-byte swizzle) and
 //               one box of packed weights [8 packed rows x 128 columns] int32, into a 4-stage ring.
 //   warp 1      allocates TMEM, then one elected lane issues 4 x tcgen05.mma (K = 16 each) per block and
 //               commits the stage back to the producer.
-//   warps 2-5   unpack: thread n turns the 8 words of column n into 64 fp16 values w = (q - zero) * scale
+//   warps 2-9   unpack: two threads per column n, each turns 4 of its 8 words into 32 fp16 values w = (q - zero) * scale
 //               (exact integer in fp16, one rounding in the multiply: the fp16 weight the reference
 //               uploads, src/gpu/buffer.ts:103-120) and stores them as the K-major, 128-byte-swizzled
 //               operand tile; afterwards the same warps drain TMEM (tcgen05.ld), add the bias and store.
@@ -27,7 +27,7 @@ namespace tc {
 constexpr int BN = 128;       // output columns per CTA (UMMA M)
 constexpr int BK = 64;        // k per stage: one 128-byte swizzle atom of fp16
 constexpr int STAGES = 4;
-constexpr int THREADS = 192;
+constexpr int THREADS = 320;
 constexpr uint32_t SPIN_LIMIT = 1u << 20;
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -176,7 +176,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
             mbar_init(&full[s], 1);
-            mbar_init(&deq[s], 4);
+            mbar_init(&deq[s], 8);
             mbar_init(&empty[s], 1);
         }
         mbar_init(acc_full, 1);
@@ -226,7 +226,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         __syncwarp();
     } else {
         // ------------------------------------------------------------------ unpack, then epilogue
-        const int tn = threadIdx.x - 64;  // 0..127: column of the tile
+        const int tn = (threadIdx.x - 64) & 127;   // column of the tile
+        const int rhalf = (threadIdx.x - 64) >> 7;  // which 4 of the 8 packed rows of a k-block
         bool ok = true;
         if constexpr (!DENSE) {
             const int n = n0 + tn;
@@ -251,7 +252,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 const uint32_t *src = wp(s) + tn;
                 uint8_t *dst_row = wd(s) + tn * 128;
 #pragma unroll
-                for (int r = 0; r < 8; r++) {
+                for (int rr = 0; rr < 4; rr++) {
+                    const int r = rhalf * 4 + rr;
                     uint32_t w = src[r * BN];
                     const uint32_t lo0 = (w & 0x000f000fu) | 0x64006400u;
                     const uint32_t hi0 = (w & 0x00f000f0u) | 0x64006400u;
@@ -285,7 +287,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             const int n = n0 + q * 32 + lane;
             const float bias = (p.bias && n < p.N) ? p.bias[n] : 0.f;
 #pragma unroll 1
-            for (int c = 0; c < MT; c += 16) {
+            // the two warps that share a TMEM lane quarter split the columns
+            constexpr int CSPAN = MT >= 32 ? MT / 2 : MT;
+            const int c_begin = MT >= 32 ? ((warp - 2) >> 2) * CSPAN : 0;
+            const int c_end = (MT >= 32 || warp < 6) ? c_begin + CSPAN : 0;
+            for (int c = c_begin; c < c_end; c += 16) {
                 uint32_t r[16];
                 tmem_ld_32x32b_x16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c, r);
                 tmem_ld_wait();
@@ -366,7 +372,9 @@ static int pick_mt(int64_t M, int64_t N, int sms)
     for (int mt : {256, 128}) {
         const int64_t tiles = ((M + mt - 1) / mt) * n_tiles;
         const int64_t waves = (tiles + sms - 1) / sms;
-        const int64_t cost = waves * (mt + 32);  // per-tile time grows with MT; 32 ~ fixed cost of a tile
+        // measured: a 128-token tile is bound by the unpack of its weight tile and takes ~0.85 of the time of a
+        // 256-token tile, so the taller tile wins whenever it does not add waves
+        const int64_t cost = waves * (mt == 256 ? 100 : 85);
         if (best_cost < 0 || cost < best_cost) best = mt, best_cost = cost;
     }
     return best;

@@ -51,6 +51,9 @@ struct GemvParams {
     int wn, wk;         // warps across columns / across k
     int x_f16, out_f16;
     int xs_stride;      // uint4 per staged activation row
+    int stages;         // depth of the per-thread cp.async ring
+    int ring_off;       // byte offset of the ring in dynamic shared memory
+    int red_off;        // byte offset of the cross-warp reduction buffer
 };
 
 __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -65,23 +68,14 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a
 __device__ __forceinline__ uint32_t h2_as_u32(__half2 h) { return *reinterpret_cast<uint32_t *>(&h); }
 __device__ __forceinline__ __half2 u32_as_h2(uint32_t u) { return *reinterpret_cast<__half2 *>(&u); }
 
-// 8 nibbles of `w` -> h[0]=(q0,q4) h[1]=(q1,q5) h[2]=(q2,q6) h[3]=(q3,q7), each minus the zero point.
-__device__ __forceinline__ void unpack_word(uint32_t w, __half2 zsub, __half2 zfma, uint32_t (&h)[4])
-{
-    const __half2 sixteenth = __float2half2_rn(0.0625f);
-    const uint32_t lo0 = (w & 0x000f000fu) | 0x64006400u;
-    const uint32_t hi0 = (w & 0x00f000f0u) | 0x64006400u;
-    w >>= 8;
-    const uint32_t lo1 = (w & 0x000f000fu) | 0x64006400u;
-    const uint32_t hi1 = (w & 0x00f000f0u) | 0x64006400u;
-    h[0] = h2_as_u32(__hsub2(u32_as_h2(lo0), zsub));
-    h[1] = h2_as_u32(__hfma2(u32_as_h2(hi0), sixteenth, zfma));
-    h[2] = h2_as_u32(__hsub2(u32_as_h2(lo1), zsub));
-    h[3] = h2_as_u32(__hfma2(u32_as_h2(hi1), sixteenth, zfma));
-}
+}  // namespace wb
+
+#include "gemv_core.cuh"
+
+namespace wb {
 
 template <int MB, bool EXACT>
-__global__ void __launch_bounds__(512) gptq_gemv_mma_kernel(const GemvParams p)
+__global__ void __launch_bounds__(MB == 1 ? 256 : 512, MB == 1 ? 3 : 1) gptq_gemv_mma_kernel(const GemvParams p)
 {
     extern __shared__ uint4 smem_u4[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -95,14 +89,49 @@ __global__ void __launch_bounds__(512) gptq_gemv_mma_kernel(const GemvParams p)
     const int rows_cta = max(0, min(p.pack_rows, ch_end * 16) - row_begin);
 
     uint4 *xs_hi = smem_u4;
-    uint4 *xs_lo = smem_u4 + (size_t)p.M * p.xs_stride;  // EXACT only
+    // rows 0..M-1 are the activations, row M is all zeros: lanes whose batch row does not exist read it
+    uint4 *xs_lo = smem_u4 + (size_t)(p.M + 1) * p.xs_stride;                           // EXACT only
+    float *xsum = reinterpret_cast<float *>(smem_u4 + (size_t)(p.M + 1) * p.xs_stride * (EXACT ? 2 : 1));
+    const int chunks_cta = ch_end - ch_begin;
 
-    // ---- stage this slice of the activations, permuted to the MMA's k-slot order ----
-    for (int idx = tid; idx < p.M * rows_cta; idx += nthreads) {
-        const int m = idx / rows_cta, rl = idx - m * rows_cta;
+    // Work of this CTA: column tiles blockIdx.x, blockIdx.x + gridDim.x, ... (wn * 32 columns each) of its k-slice.
+    // Within a tile a warp owns 32 columns and every wk-th chunk; a thread owns columns c .. c+3 (N % 4 == 0: in
+    // or out of the matrix together). The grid is sized to what is resident at once, so no partial second wave.
+    const int n_tiles = (p.N + p.wn * 32 - 1) / (p.wn * 32);
+    const int tiles_cta = (int)blockIdx.x < n_tiles ? (n_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+    const int n_i = ch_end > ch_begin + wk ? (ch_end - ch_begin - wk + p.wk - 1) / p.wk : 0;  // this warp's chunks per tile
+    auto col_of = [&](int j) { return (((int)blockIdx.x + j * (int)gridDim.x) * p.wn + wn) * 32 + 4 * g; };
+    // cp.async ring over the flattened (tile, chunk) sequence of this warp: `stages` slots per thread,
+    // stages - 1 chunks requested before the activations are staged and one more per iteration, so that
+    // several chunks per thread are always in flight, also across tile boundaries.
+    unsigned char *ring = reinterpret_cast<unsigned char *>(smem_u4) + p.ring_off + (size_t)tid * kSlotBytes;
+    const size_t stage_stride = (size_t)nthreads * kSlotBytes;
+    int rq_tile = 0, rq_i = 0;
+    auto request = [&](int slot) {
+        if (rq_tile < tiles_cta && n_i > 0) {
+            const int cc = col_of(rq_tile);
+            fetch_chunk_async(p, ch_begin + wk + rq_i * p.wk, t, cc, cc < p.N, ring + slot * stage_stride);
+            if (++rq_i == n_i) rq_i = 0, rq_tile++;
+        }
+        cp_async_commit();
+    };
+    for (int s = 0; s < p.stages - 1; s++) request(s);
+
+    // ---- stage this slice of the activations in the MMA's k-slot order: (x0,x4)(x2,x6)(x1,x5)(x3,x7) per packed
+    // row, zeros for the rows of a last partial chunk, plus the per-chunk sums used for the zero-point term ----
+    const int rows_pad = chunks_cta * 16;
+    for (int rl = tid; rl < rows_pad; rl += nthreads) {
+        xs_hi[p.M * p.xs_stride + rl] = make_uint4(0, 0, 0, 0);
+        if constexpr (EXACT) xs_lo[p.M * p.xs_stride + rl] = make_uint4(0, 0, 0, 0);
+    }
+    for (int idx = tid; idx < p.M * rows_pad; idx += nthreads) {
+        const int m = idx / rows_pad, rl = idx - m * rows_pad;
         const int64_t k0 = (int64_t)(row_begin + rl) * 8;
         float v[8];
-        if (p.x_f16) {
+        if (rl >= rows_cta) {
+#pragma unroll
+            for (int j = 0; j < 8; j++) v[j] = 0.f;
+        } else if (p.x_f16) {
             const uint4 raw = *reinterpret_cast<const uint4 *>((const __half *)p.x + (int64_t)m * p.K + k0);
             const __half2 *h = reinterpret_cast<const __half2 *>(&raw);
 #pragma unroll
@@ -121,8 +150,8 @@ __global__ void __launch_bounds__(512) gptq_gemv_mma_kernel(const GemvParams p)
         for (int j = 0; j < 8; j++) hi[j] = __float2half_rn(v[j]);
         uint4 o;
         o.x = h2_as_u32(__halves2half2(hi[0], hi[4]));
-        o.y = h2_as_u32(__halves2half2(hi[1], hi[5]));
-        o.z = h2_as_u32(__halves2half2(hi[2], hi[6]));
+        o.y = h2_as_u32(__halves2half2(hi[2], hi[6]));
+        o.z = h2_as_u32(__halves2half2(hi[1], hi[5]));
         o.w = h2_as_u32(__halves2half2(hi[3], hi[7]));
         xs_hi[m * p.xs_stride + rl] = o;
         if constexpr (EXACT) {
@@ -130,160 +159,114 @@ __global__ void __launch_bounds__(512) gptq_gemv_mma_kernel(const GemvParams p)
 #pragma unroll
             for (int j = 0; j < 8; j++) lo[j] = __float2half_rn(v[j] - __half2float(hi[j]));
             o.x = h2_as_u32(__halves2half2(lo[0], lo[4]));
-            o.y = h2_as_u32(__halves2half2(lo[1], lo[5]));
-            o.z = h2_as_u32(__halves2half2(lo[2], lo[6]));
+            o.y = h2_as_u32(__halves2half2(lo[2], lo[6]));
+            o.z = h2_as_u32(__halves2half2(lo[1], lo[5]));
             o.w = h2_as_u32(__halves2half2(lo[3], lo[7]));
             xs_lo[m * p.xs_stride + rl] = o;
         }
     }
     __syncthreads();
+    // per (row m, chunk): sum of the staged operand values (hi + lo), 16 threads per sum, fixed order
+    for (int idx = tid; idx < p.M * chunks_cta * 16; idx += nthreads) {
+        const int task = idx >> 4, rr = idx & 15;
+        const int m = task / chunks_cta, cl = task - m * chunks_cta;
+        auto sum8 = [](const uint4 &o) {
+            const float2 a = __half22float2(u32_as_h2(o.x)), b = __half22float2(u32_as_h2(o.y));
+            const float2 cc = __half22float2(u32_as_h2(o.z)), d = __half22float2(u32_as_h2(o.w));
+            return ((a.x + a.y) + (b.x + b.y)) + ((cc.x + cc.y) + (d.x + d.y));
+        };
+        float sx = sum8(xs_hi[m * p.xs_stride + cl * 16 + rr]);
+        if constexpr (EXACT) sx += sum8(xs_lo[m * p.xs_stride + cl * 16 + rr]);
+        // 16 consecutive lanes share a sum; a half-warp is either wholly inside this loop or wholly outside
+        const unsigned half_mask = (lane & 16) ? 0xffff0000u : 0x0000ffffu;
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) sx += __shfl_xor_sync(half_mask, sx, o);
+        if (rr == 0) xsum[task] = sx;
+    }
+    __syncthreads();
 
-    // ---- main loop: this warp owns columns [c0w, c0w+32), this thread columns c .. c+3 ----
-    const int c0w = (blockIdx.x * p.wn + wn) * 32;
-    const int c = c0w + 4 * g;
-    const bool col_ok = c < p.N;  // N % 4 == 0: a thread's four columns are in or out together
-
-    float tot[MB][2][4];
-#pragma unroll
-    for (int mb = 0; mb < MB; mb++)
-#pragma unroll
-        for (int s = 0; s < 2; s++)
-#pragma unroll
-            for (int i = 0; i < 4; i++) tot[mb][s][i] = 0.f;
-
-    const uint4 zero4 = make_uint4(0, 0, 0, 0);
-    for (int ch = ch_begin + wk; ch < ch_end; ch += p.wk) {
-        // issue the chunk's four 128-bit loads first
-        uint4 wq[4];
-#pragma unroll
-        for (int st = 0; st < 4; st++) {
-            const int r = ch * 16 + st * 4 + t;
-            wq[st] = (col_ok && r < p.pack_rows) ? ldg_stream_v4(p.qw + (int64_t)r * p.N + c) : zero4;
-        }
-        const int G = ch / p.group_chunks;
-        float scale[4] = {0.f, 0.f, 0.f, 0.f};
-        __half2 zsub[4], zfma[4];
-        {
-            uint32_t znib = 0x7777u;  // stored zero 7 -> zero point 8 when the checkpoint has no qzeros
-            if (col_ok) {
-                const uint2 sraw = *reinterpret_cast<const uint2 *>(p.sc + (int64_t)G * p.N + c);
-                const float2 s01 = __half22float2(u32_as_h2(sraw.x)), s23 = __half22float2(u32_as_h2(sraw.y));
-                scale[0] = s01.x, scale[1] = s01.y, scale[2] = s23.x, scale[3] = s23.y;
-                if (p.qz) znib = p.qz[(int64_t)G * p.zcols + (c >> 3)] >> ((c & 7) * 4);
-            }
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-                const float z = (float)(((znib >> (4 * j)) & 15u) + 1u);
-                zsub[j] = __float2half2_rn(1024.f + z);
-                zfma[j] = __float2half2_rn(-(64.f + z));
-            }
-        }
-
-        float acc[MB][2][4];
+    // ---- main loop over this CTA's column tiles ----
+    float *red = reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(smem_u4) + p.red_off);  // [wk][wn][MB*8][32]
+    __shared__ int is_last;
+    constexpr int J = MB * 8;
+    const int tile_cols = p.wn * 32;
+    const bool direct = p.S == 1;
+    int slot_use = 0, slot_req = p.stages - 1;
+    for (int tj = 0; tj < tiles_cta; tj++) {
+        const int tile = (int)blockIdx.x + tj * (int)gridDim.x;
+        const int c = col_of(tj);
+        float tot[MB][2][4];
 #pragma unroll
         for (int mb = 0; mb < MB; mb++)
 #pragma unroll
             for (int s = 0; s < 2; s++)
 #pragma unroll
-                for (int i = 0; i < 4; i++) acc[mb][s][i] = 0.f;
-
-#pragma unroll
-        for (int st = 0; st < 4; st++) {
-            const int rl = ch * 16 + st * 4 + t - row_begin;
-            const bool row_ok = rl < rows_cta;
-            uint32_t h0[4], h1[4], h2[4], h3[4];
-            unpack_word(wq[st].x, zsub[0], zfma[0], h0);
-            unpack_word(wq[st].y, zsub[1], zfma[1], h1);
-            unpack_word(wq[st].z, zsub[2], zfma[2], h2);
-            unpack_word(wq[st].w, zsub[3], zfma[3], h3);
-#pragma unroll
-            for (int mb = 0; mb < MB; mb++) {
-                const int m = mb * 8 + g;
-                const bool ok = row_ok && m < p.M;
-                const uint4 xb = ok ? xs_hi[m * p.xs_stride + rl] : zero4;
-                mma_16816(acc[mb][0], h0[0], h1[0], h0[1], h1[1], xb.x, xb.y);
-                mma_16816(acc[mb][0], h0[2], h1[2], h0[3], h1[3], xb.z, xb.w);
-                mma_16816(acc[mb][1], h2[0], h3[0], h2[1], h3[1], xb.x, xb.y);
-                mma_16816(acc[mb][1], h2[2], h3[2], h2[3], h3[3], xb.z, xb.w);
-                if constexpr (EXACT) {
-                    const uint4 xl = ok ? xs_lo[m * p.xs_stride + rl] : zero4;
-                    mma_16816(acc[mb][0], h0[0], h1[0], h0[1], h1[1], xl.x, xl.y);
-                    mma_16816(acc[mb][0], h0[2], h1[2], h0[3], h1[3], xl.z, xl.w);
-                    mma_16816(acc[mb][1], h2[0], h3[0], h2[1], h3[1], xl.x, xl.y);
-                    mma_16816(acc[mb][1], h2[2], h3[2], h2[3], h3[3], xl.z, xl.w);
-                }
-            }
+                for (int i = 0; i < 4; i++) tot[mb][s][i] = 0.f;
+        for (int i = 0; i < n_i; i++) {
+            request(slot_req);
+            slot_req = slot_req + 1 == p.stages ? 0 : slot_req + 1;
+            cp_async_wait(p.stages - 1);  // everything but the newest stages - 1 groups has landed
+            ChunkRegs ra;
+            read_slot(ring + slot_use * stage_stride, c, ra);
+            slot_use = slot_use + 1 == p.stages ? 0 : slot_use + 1;
+            const int chunk = ch_begin + wk + i * p.wk;
+            const int rl0 = chunk * 16 + t - row_begin;
+            compute_chunk<MB, EXACT>(p, ra, rl0, g, t, xs_hi, xs_lo, xsum, chunk - ch_begin, chunks_cta, tot);
         }
-        // accumulator rows g / g+8 of set s are columns c+2s / c+2s+1
+
+        // reduce over the wk warps that share the column tile (fixed order), then write / split-K
 #pragma unroll
         for (int mb = 0; mb < MB; mb++)
 #pragma unroll
-            for (int s = 0; s < 2; s++) {
-                tot[mb][s][0] = fmaf(scale[2 * s], acc[mb][s][0], tot[mb][s][0]);
-                tot[mb][s][1] = fmaf(scale[2 * s], acc[mb][s][1], tot[mb][s][1]);
-                tot[mb][s][2] = fmaf(scale[2 * s + 1], acc[mb][s][2], tot[mb][s][2]);
-                tot[mb][s][3] = fmaf(scale[2 * s + 1], acc[mb][s][3], tot[mb][s][3]);
+            for (int s = 0; s < 2; s++)
+#pragma unroll
+                for (int i = 0; i < 4; i++)
+                    red[((wk * p.wn + wn) * J + (mb * 2 + s) * 4 + i) * 32 + lane] = tot[mb][s][i];
+        __syncthreads();
+        const int n_base = tile * tile_cols;
+        const int outputs = p.M * tile_cols;
+        for (int idx = tid; idx < outputs; idx += nthreads) {
+            const int m = idx / tile_cols, cl_all = idx - m * tile_cols;
+            const int n = n_base + cl_all;
+            if (n >= p.N) continue;
+            const int w_n = cl_all >> 5, cl = cl_all & 31;
+            const int gg = cl >> 2, s = (cl & 3) >> 1, hi = cl & 1;
+            const int mb = m >> 3, tt = (m & 7) >> 1, i = hi * 2 + (m & 1);
+            const int src_lane = gg * 4 + tt, j = (mb * 2 + s) * 4 + i;
+            float v = 0.f;
+            for (int k = 0; k < p.wk; k++) v += red[((k * p.wn + w_n) * J + j) * 32 + src_lane];
+            if (direct) {
+                if (p.bias) v += p.bias[n];
+                if (p.out_f16) ((__half *)p.out)[(int64_t)m * p.N + n] = __float2half_rn(v);
+                else ((float *)p.out)[(int64_t)m * p.N + n] = v;
+            } else {
+                p.partial[((int64_t)blockIdx.y * p.M + m) * p.N + n] = v;
             }
-    }
-
-    // ---- reduce over the wk warps that share a column tile (fixed order), then write / split-K ----
-    __syncthreads();  // xs is dead; reuse shared memory as float red[wk][wn][MB*8][32]
-    float *red = reinterpret_cast<float *>(smem_u4);
-    constexpr int J = MB * 8;
-#pragma unroll
-    for (int mb = 0; mb < MB; mb++)
-#pragma unroll
-        for (int s = 0; s < 2; s++)
-#pragma unroll
-            for (int i = 0; i < 4; i++)
-                red[((wk * p.wn + wn) * J + (mb * 2 + s) * 4 + i) * 32 + lane] = tot[mb][s][i];
-    __syncthreads();
-
-    const int tile_cols = p.wn * 32;
-    const int n_base = blockIdx.x * tile_cols;
-    const int outputs = p.M * tile_cols;
-    const bool direct = p.S == 1;
-    for (int idx = tid; idx < outputs; idx += nthreads) {
-        const int m = idx / tile_cols, cl_all = idx - m * tile_cols;
-        const int n = n_base + cl_all;
-        if (n >= p.N) continue;
-        const int w_n = cl_all >> 5, cl = cl_all & 31;
-        const int gg = cl >> 2, s = (cl & 3) >> 1, hi = cl & 1;
-        const int mb = m >> 3, tt = (m & 7) >> 1, i = hi * 2 + (m & 1);
-        const int src_lane = gg * 4 + tt, j = (mb * 2 + s) * 4 + i;
-        float v = 0.f;
-        for (int k = 0; k < p.wk; k++) v += red[((k * p.wn + w_n) * J + j) * 32 + src_lane];
-        if (direct) {
-            if (p.bias) v += p.bias[n];
-            if (p.out_f16) ((__half *)p.out)[(int64_t)m * p.N + n] = __float2half_rn(v);
-            else ((float *)p.out)[(int64_t)m * p.N + n] = v;
-        } else {
-            p.partial[((int64_t)blockIdx.y * p.M + m) * p.N + n] = v;
         }
+        if (!direct) {
+            // the last slice to arrive for this tile adds the slices in slice order and the bias once
+            __threadfence();
+            __syncthreads();
+            if (tid == 0) is_last = (atomicAdd(&p.counters[tile], 1u) == (unsigned)(p.S - 1));
+            __syncthreads();
+            if (is_last) {
+                __threadfence();
+                for (int idx = tid; idx < outputs; idx += nthreads) {
+                    const int m = idx / tile_cols;
+                    const int n = n_base + (idx - m * tile_cols);
+                    if (n >= p.N) continue;
+                    float v = 0.f;
+                    for (int s = 0; s < p.S; s++) v += __ldcg(&p.partial[((int64_t)s * p.M + m) * p.N + n]);
+                    if (p.bias) v += p.bias[n];
+                    if (p.out_f16) ((__half *)p.out)[(int64_t)m * p.N + n] = __float2half_rn(v);
+                    else ((float *)p.out)[(int64_t)m * p.N + n] = v;
+                }
+                if (tid == 0) p.counters[tile] = 0u;  // leave the counters clean for the next call
+            }
+        }
+        __syncthreads();  // red and is_last are reused by the next tile
     }
-    if (direct) return;
-
-    __shared__ int is_last;
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) {
-        const unsigned prev = atomicAdd(&p.counters[blockIdx.x], 1u);
-        is_last = (prev == (unsigned)(p.S - 1));
-    }
-    __syncthreads();
-    if (!is_last) return;
-    __threadfence();
-    for (int idx = tid; idx < outputs; idx += nthreads) {
-        const int m = idx / tile_cols;
-        const int n = n_base + (idx - m * tile_cols);
-        if (n >= p.N) continue;
-        float v = 0.f;
-        for (int s = 0; s < p.S; s++) v += __ldcg(&p.partial[((int64_t)s * p.M + m) * p.N + n]);
-        if (p.bias) v += p.bias[n];
-        if (p.out_f16) ((__half *)p.out)[(int64_t)m * p.N + n] = __float2half_rn(v);
-        else ((float *)p.out)[(int64_t)m * p.N + n] = v;
-    }
-    if (tid == 0) p.counters[blockIdx.x] = 0u;  // leave the counters clean for the next call
+    cp_async_wait(0);
 }
 
 // =====================================================================================================
@@ -430,13 +413,55 @@ static bool dense_gemv_supports(const Weight &w, int64_t M)
 
 constexpr int kGemvSmemLimit = 200 * 1024;
 
+// Dynamic shared memory of one GEMV CTA: staged activations (16 bytes per row per packed row, twice for f32
+// activations; plus the per-chunk sums otherwise), then the cp.async ring (80 bytes per thread per stage).
+// The cross-warp reduction reuses the front of the buffer. Returns the total; 0 stages = size without a ring.
+static size_t gemv_smem_bytes(int64_t M, int cps, bool two_halves, int wn, int wk, int stages, int *ring_off,
+                              int *red_off = nullptr)
+{
+    const int MB = M <= 8 ? 1 : (M <= 16 ? 2 : 4);
+    size_t xs = (size_t)(M + 1) * (cps * 16 + 4) * 16 * (two_halves ? 2 : 1) + (size_t)M * cps * 4;
+    xs = (xs + 15) / 16 * 16;
+    const size_t ring = (size_t)stages * wn * wk * 32 * 80;
+    const size_t red = (size_t)wn * wk * MB * 8 * 32 * 4;
+    if (ring_off) *ring_off = (int)xs;
+    if (red_off) *red_off = (int)(xs + ring);
+    return xs + ring + red;
+}
+
+// Grid width: as many column tiles as are resident at once, evened out so that every CTA gets the same number
+// of tiles (a partial second wave would otherwise double the time of a kernel that lasts one wave).
+static int gemv_grid_x(int sm_count, int ctas_n, int S, int block, size_t smem)
+{
+    int per_sm = (int)((220 * 1024) / (smem + 1024));
+    const int by_threads = 2048 / block, by_regs = block <= 256 ? 3 : 1;
+    if (per_sm > by_threads) per_sm = by_threads;
+    if (per_sm > by_regs) per_sm = by_regs;
+    if (per_sm < 1) per_sm = 1;
+    int capacity = sm_count * per_sm / (S > 0 ? S : 1);
+    if (capacity < 1) capacity = 1;
+    const int waves = (ctas_n + capacity - 1) / capacity;
+    return (ctas_n + waves - 1) / waves;
+}
+
+// Ring depth: 3 chunks ahead keeps ~3 x 64 bytes per thread in flight; fewer when a warp has fewer chunks or
+// when the activations leave no room.
+static int gemv_pick_stages(int64_t M, int cps, bool two_halves, int wn, int wk)
+{
+    int stages = (cps + wk - 1) / wk;
+    if (stages > 2) stages = 2;
+    if (stages < 1) stages = 1;
+    while (stages > 1 && gemv_smem_bytes(M, cps, two_halves, wn, wk, stages, nullptr) > (size_t)kGemvSmemLimit) stages--;
+    return stages;
+}
+
 static void plan_gemv_mma(wb_context *ctx, const Weight &w, int64_t M, int two_halves, wb_plan *plan)
 {
     const int chunks = (int)((w.pack_rows + 15) / 16);
     const int col_tiles = (int)((w.N + 31) / 32);
     int wn = M <= 2 ? 1 : (M <= 4 ? 2 : 4);
     while (wn > 1 && col_tiles < wn) wn >>= 1;
-    int wk = wn == 1 ? 8 : (wn == 2 ? 8 : 4);
+    int wk = M <= 8 ? 8 / wn : 4;  // 256 threads up to 8 rows (3 CTAs per SM), 512 beyond
     if (wk > chunks) wk = chunks;
     const int ctas_n = (col_tiles + wn - 1) / wn;
     const int target = 2 * ctx->sm_count;
@@ -448,13 +473,7 @@ static void plan_gemv_mma(wb_context *ctx, const Weight &w, int64_t M, int two_h
         S = by_work < by_fill ? by_work : by_fill;
     }
     // shared memory: staged activations (16 bytes per row per packed row, twice in exact mode)
-    auto smem_for = [&](int s) {
-        const int cps = (chunks + s - 1) / s;
-        const uint64_t xs = (uint64_t)M * (cps * 16 + 4) * 16 * (two_halves ? 2 : 1);
-        const int MB = M <= 8 ? 1 : (M <= 16 ? 2 : 4);
-        const uint64_t red = (uint64_t)wn * wk * MB * 8 * 32 * 4;
-        return xs > red ? xs : red;
-    };
+    auto smem_for = [&](int s) { return (uint64_t)gemv_smem_bytes(M, (chunks + s - 1) / s, two_halves, wn, wk, 1, nullptr); };
     while (smem_for(S) > (uint64_t)kGemvSmemLimit && S < chunks) S++;
     if (ctx->force_split > 0) S = ctx->force_split;
     if (S > chunks) S = chunks;
@@ -559,11 +578,11 @@ int launch_linear(wb_context *ctx, const Weight &w, const void *A, void *C, cons
         p.x_f16 = act_dtype == WB_F16, p.out_f16 = out_dtype == WB_F16;
         p.xs_stride = p.chunks_per_split * 16 + 4;
         const int MB = M <= 8 ? 1 : (M <= 16 ? 2 : 4);
-        const size_t xs_bytes = (size_t)M * p.xs_stride * 16 * (ex_gemv ? 2 : 1);
-        const size_t red_bytes = (size_t)p.wn * p.wk * MB * 8 * 32 * 4;
-        const size_t smem = xs_bytes > red_bytes ? xs_bytes : red_bytes;
+        p.stages = gemv_pick_stages(M, p.chunks_per_split, ex_gemv, p.wn, p.wk);
+        const size_t smem = gemv_smem_bytes(M, p.chunks_per_split, ex_gemv, p.wn, p.wk, p.stages, &p.ring_off, &p.red_off);
         if (smem > (size_t)kGemvSmemLimit) return fail(WB_ERR_UNSUPPORTED, "GEMV_MMA: activations do not fit shared memory");
-        dim3 grid(plan.grid_x, plan.grid_y);
+        // plan.grid_x counts column tiles; the launch covers them with one evenly loaded wave of CTAs
+        dim3 grid(gemv_grid_x(ctx->sm_count, plan.grid_x, plan.grid_y, plan.block, smem), plan.grid_y);
         cudaError_t e = MB == 1   ? launch_gemv_mb<1>(p, grid, plan.block, smem, ex_gemv, ctx->stream)
                         : MB == 2 ? launch_gemv_mb<2>(p, grid, plan.block, smem, ex_gemv, ctx->stream)
                                   : launch_gemv_mb<4>(p, grid, plan.block, smem, ex_gemv, ctx->stream);
@@ -664,7 +683,7 @@ extern "C" int wb_gptq_gemv_static(const void *qweight, const void *qzeros, cons
     const int pack_rows = (int)(K / 8), chunks = (pack_rows + 15) / 16, col_tiles = (int)((N + 31) / 32);
     int wn = M <= 2 ? 1 : (M <= 4 ? 2 : 4);
     while (wn > 1 && col_tiles < wn) wn >>= 1;
-    int wk = wn == 4 ? 4 : 8;
+    int wk = M <= 8 ? 8 / wn : 4;
     if (wk > chunks) wk = chunks;
     const int ctas_n = (col_tiles + wn - 1) / wn;
     int S = split_k;
@@ -680,9 +699,10 @@ extern "C" int wb_gptq_gemv_static(const void *qweight, const void *qzeros, cons
     const bool two_halves = act_dtype == WB_F32;
     const int MB = M <= 8 ? 1 : (M <= 16 ? 2 : 4);
     const int xs_stride = cps * 16 + 4;
-    const size_t xs_bytes = (size_t)M * xs_stride * 16 * (two_halves ? 2 : 1);
-    const size_t red_bytes = (size_t)wn * wk * MB * 8 * 32 * 4;
-    const size_t smem = xs_bytes > red_bytes ? xs_bytes : red_bytes;
+    const int stages = gemv_pick_stages(M, cps, two_halves, wn, wk);
+    int ring_off = 0;
+    int red_off = 0;
+    const size_t smem = gemv_smem_bytes(M, cps, two_halves, wn, wk, stages, &ring_off, &red_off);
     if (smem > (size_t)kGemvSmemLimit)
         return fail(WB_ERR_UNSUPPORTED, "wb_gptq_gemv_static: %lld x %lld activations per slice do not fit shared memory; raise split_k",
                     (long long)M, (long long)(cps * 128));
@@ -703,7 +723,10 @@ extern "C" int wb_gptq_gemv_static(const void *qweight, const void *qzeros, cons
     p.M = (int)M, p.N = (int)N, p.K = (int)K, p.pack_rows = pack_rows, p.zcols = (int)((N + 7) / 8);
     p.chunks = chunks, p.chunks_per_split = cps, p.group_chunks = (int)(group_size / 128), p.S = S;
     p.wn = wn, p.wk = wk, p.x_f16 = act_dtype == WB_F16, p.out_f16 = out_dtype == WB_F16, p.xs_stride = xs_stride;
-    dim3 grid(ctas_n, S);
+    p.stages = stages, p.ring_off = ring_off, p.red_off = red_off;
+    int sms = 148;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    dim3 grid(gemv_grid_x(sms, ctas_n, S, wn * wk * 32, smem), S);
     const int block = wn * wk * 32;
     cudaError_t e = MB == 1   ? launch_gemv_mb<1>(p, grid, block, smem, two_halves, st)
                     : MB == 2 ? launch_gemv_mb<2>(p, grid, block, smem, two_halves, st)
