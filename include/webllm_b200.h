@@ -206,6 +206,11 @@ WB_API int wb_qwen_decode_step(wb_qwen *model, uint32_t token, uint64_t *logits_
  * in a CUDA graph on first use and replayed; out_tokens receives the n_steps sampled tokens. Replaces the
  * per-token logits readback of generateQwen (src/infer/qwen-generate.ts:66-74). */
 WB_API int wb_qwen_decode_greedy(wb_qwen *model, uint32_t first_token, int64_t n_steps, uint32_t *out_tokens);
+/* How wb_qwen_decode_greedy runs a step: 0 = automatic (currently 1), 1 = one kernel per operation replayed as a
+ * CUDA graph (the CommandBatch form of the reference, src/gpu/pipeline.ts:55-117), 2 = one persistent cooperative
+ * kernel per step with grid-wide barriers between its phases (needs the fused GPTQ projections). Both give the
+ * same tokens. */
+WB_API int wb_qwen_set_decode_mode(wb_qwen *model, int mode);
 /* Logits of the last step run by wb_qwen_decode_greedy, [V] f32, copied to the host. */
 WB_API int wb_qwen_last_logits(wb_qwen *model, float *out);
 

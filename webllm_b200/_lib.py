@@ -97,6 +97,7 @@ SIGNATURES = {
     "wb_qwen_prefill": [_vp, _vp, _i64, _i32, C.POINTER(_u64)],
     "wb_qwen_decode_step": [_vp, C.c_uint32, C.POINTER(_u64)],
     "wb_qwen_decode_greedy": [_vp, C.c_uint32, _i64, _vp],
+    "wb_qwen_set_decode_mode": [_vp, _i32],
     "wb_qwen_last_logits": [_vp, _vp],
     "wb_gptq_gemv_static": [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i32, _i32, _i32, _vp],
 }

@@ -4,7 +4,47 @@
 // ~47 ns per SM sub-partition, so the loop has to stay within a few dozen issue slots per load; see compute_chunk.
 #pragma once
 
+#include <cuda_fp16.h>
+#include <stdint.h>
+
 namespace wb {
+
+// Launch parameters of the streaming GEMV; the chunk functions below read the weight pointers and sizes.
+struct GemvParams {
+    const uint32_t *qw;
+    const uint32_t *qz;  // nullable
+    const __half *sc;
+    const void *x;
+    void *out;
+    const float *bias;  // nullable
+    float *partial;
+    unsigned *counters;
+    int M, N, K;
+    int pack_rows, zcols;
+    int chunks;         // ceil(pack_rows / 16)
+    int chunks_per_split;
+    int group_chunks;   // group / 128
+    int S;
+    int wn, wk;         // warps across columns / across k
+    int x_f16, out_f16;
+    int xs_stride;      // uint4 per staged activation row
+    int stages;         // depth of the per-thread cp.async ring
+    int ring_off;       // byte offset of the ring in dynamic shared memory
+    int red_off;        // byte offset of the cross-warp reduction buffer
+};
+
+__device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                          uint32_t b0, uint32_t b1)
+{
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t h2_as_u32(__half2 h) { return *reinterpret_cast<uint32_t *>(&h); }
+__device__ __forceinline__ __half2 u32_as_h2(uint32_t u) { return *reinterpret_cast<__half2 *>(&u); }
+
 
 struct ChunkRegs {
     uint4 w[4];     // packed words: rows 4*st + t of the chunk, columns c .. c+3

@@ -5,49 +5,12 @@
 
 #include <memory>
 
-#include "qwen_ops.cuh"
+#include "qwen_internal.cuh"
 
 using namespace wb;
 
-namespace {
-
-struct LayerW {
-    int in_norm = -1, post_norm = -1;
-    int q = -1, k = -1, v = -1, o = -1, gate = -1, up = -1, down = -1;
-    int qb = -1, kb = -1, vb = -1;
-    int qkv = -1, qkvb = -1, gate_up = -1;  // fused variants
-};
-
-// Activation buffers of one forward call (all f32).
-struct Bufs {
-    uint32_t *tokens;
-    float *x, *xa, *n, *q, *k, *v, *att, *proj, *gu, *act, *logits;
-    int ldq, ldk, ldv, ld_gu;
-};
-
-}  // namespace
-
-struct wb_qwen {
-    wb_context *ctx = nullptr;
-    wb_qwen_config cfg{};
-    int C = 0, H = 0, KVH = 0, D = 0, KV = 0, I = 0, V = 0;
-    int embed = -1, final_norm = -1;
-    std::vector<LayerW> layers;
-    char *k_cache = nullptr, *v_cache = nullptr;  // [n_layer][max_t][KV] of kv_dtype
-    float *cs_table = nullptr;                    // [max_t][D/2][2] cos, sin
-    int64_t cache_len = 0;
-    int exact = 0;
-    // device-resident decode state and M = 1 buffers (stable addresses for the captured graph)
-    Bufs dec{};
-    int *d_cache_len = nullptr, *d_step = nullptr, *d_bidx = nullptr;
-    float *d_bval = nullptr, *att_scratch = nullptr;
-    unsigned *att_counters = nullptr;
-    uint32_t *d_history = nullptr;
-    int64_t history_cap = 0;
-    cudaGraphExec_t graph = nullptr;
-    cudaStream_t graph_stream = nullptr;
-    int graph_exact = -1;
-};
+using wbq::Bufs;
+using wbq::LayerW;
 
 namespace {
 
@@ -298,6 +261,7 @@ int wb_qwen_destroy(wb_qwen *m)
     cudaSetDevice(m->ctx->device);
     cudaStreamSynchronize(m->ctx->stream);
     drop_graph(m);
+    wbq::mega_destroy(m);
     delete m;
     return WB_OK;
 }
@@ -392,6 +356,16 @@ int wb_qwen_decode_greedy(wb_qwen *m, uint32_t first_token, int64_t n_steps, uin
     const int state[2] = {(int)m->cache_len, 0};
     WB_CUDA(cudaMemcpyAsync(m->d_cache_len, state, sizeof state, cudaMemcpyHostToDevice, ctx->stream));
     WB_CUDA(cudaMemcpyAsync(m->dec.tokens, &first_token, 4, cudaMemcpyHostToDevice, ctx->stream));
+    // One kernel per operation replayed as a CUDA graph (the automatic choice: it measured faster), or, when
+    // asked for and the model qualifies (fused GPTQ projections), a single persistent kernel per step.
+    if (m->decode_mode == 2 && wbq::mega_supported(m)) {
+        WB_CHECK(wbq::mega_decode(m, n_steps));
+        WB_CUDA(cudaMemcpyAsync(out_tokens, m->d_history, (size_t)n_steps * 4, cudaMemcpyDeviceToHost, ctx->stream));
+        WB_CHECK(wb_synchronize(ctx));
+        m->cache_len += n_steps;
+        return WB_OK;
+    }
+    if (m->decode_mode == 2) return fail(WB_ERR_UNSUPPORTED, "the single-kernel decode step needs fused GPTQ projections (qkvW, gateUpW) with group % 128 == 0");
     if (m->graph && (m->graph_stream != ctx->stream || m->graph_exact != m->exact)) drop_graph(m);
     if (!m->graph) {
         // Warm-up step outside capture (sets kernel attributes), then restore the state it advanced.
@@ -428,6 +402,14 @@ int wb_qwen_decode_greedy(wb_qwen *m, uint32_t first_token, int64_t n_steps, uin
     WB_CUDA(cudaMemcpyAsync(out_tokens, m->d_history, (size_t)n_steps * 4, cudaMemcpyDeviceToHost, ctx->stream));
     WB_CHECK(wb_synchronize(ctx));
     m->cache_len += n_steps;
+    return WB_OK;
+}
+
+int wb_qwen_set_decode_mode(wb_qwen *m, int mode)
+{
+    WB_MODEL(m);
+    if (mode < 0 || mode > 2) return fail(WB_ERR_BAD_ARG, "decode mode must be 0 (automatic), 1 (graph of kernels) or 2 (single kernel)");
+    m->decode_mode = mode;
     return WB_OK;
 }
 
