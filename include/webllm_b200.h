@@ -162,6 +162,12 @@ WB_API int wb_plan_query(wb_context *ctx, wb_handle weight, int64_t M, int act_d
  * Used by tests to cover every path at every shape, as the reference's tests drive the split kernel with
  * explicit S (src/tests/kernels.ts:1378-1400). */
 WB_API int wb_plan_override(wb_context *ctx, int kernel, int split_k);
+/* Tells the next wb_linear call which weight a LATER call will stream (< 0 = none): a decode-size call (the int4
+ * GEMV) then also asks the L2 to fetch that weight (up to 32 MiB of it) while it runs, so the later call finds its
+ * first chunks in L2 instead of paying the HBM latency on its critical path. The hint is consumed by the next
+ * wb_linear whatever kernel it picks; results never depend on it. No counterpart in the reference (WebGPU offers
+ * no cache control); the Qwen decode step sets it for its own sequence of projections. */
+WB_API int wb_linear_hint_next(wb_context *ctx, wb_handle next_weight);
 
 /* ---- command batches. Replaces CommandBatch (src/gpu/pipeline.ts:55-117): every wb_linear /
  *      wb_gptq_dequant call between begin and end is recorded instead of run; wb_batch_submit enqueues

@@ -84,6 +84,7 @@ SIGNATURES = {
     "wb_linear": [_vp, C.c_int32, _u64, _u64, C.c_int32, _i64, _i32, _i32, _i32],
     "wb_plan_query": [_vp, C.c_int32, _i64, _i32, _i32, C.POINTER(Plan)],
     "wb_plan_override": [_vp, _i32, _i32],
+    "wb_linear_hint_next": [_vp, _i32],
     "wb_batch_begin": [_vp],
     "wb_batch_end": [_vp, C.POINTER(_vp)],
     "wb_batch_submit": [_vp],

@@ -4,6 +4,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #include <string>
 #include <unordered_map>
@@ -79,6 +80,7 @@ struct wb_context {
     int *status_host = nullptr;
     uint64_t launches = 0;
     int force_kernel = 0, force_split = 0;
+    int prefetch_weight = -1;        // index of the weight the next linear should pull into L2 (-1: none)
     void *tmap_encode = nullptr;     // cuTensorMapEncodeTiled, resolved at context creation
     bool capturing = false;          // a command batch is being recorded (batch.cu)
     uint64_t launches_at_capture = 0;
@@ -94,8 +96,21 @@ int get_weight(wb_context *ctx, wb_handle h, Weight **out);
 int launch_dequant(wb_context *ctx, const Weight &w, void *out, bool f16);
 int launch_f32_to_f16_ref(wb_context *ctx, const float *in, __half *out, int64_t n);
 int plan_linear(wb_context *ctx, const Weight &w, int64_t M, int act_dtype, int exact, wb_plan *plan);
+// Work a decode-size int4 projection can do on its input while staging it (see GemvPrologue in gemv_core.cuh):
+// kind 1 = rmsnorm(x + delta) * norm_w with x + delta stored to x_out, kind 2 = silu(x) * up with row pitch ld.
+struct LinearFusion {
+    int kind = 0;
+    const float *delta = nullptr;
+    float *x_out = nullptr;
+    const float *norm_w = nullptr;
+    float eps = 0.f;
+    const float *up = nullptr;
+    int ld = 0;
+};
+// True when launch_linear would run this weight at M rows of f32 activations through the kernel that fuses.
+bool linear_fusion_supported(wb_context *ctx, const Weight &w, int64_t M);
 int launch_linear(wb_context *ctx, const Weight &w, const void *A, void *C, const float *bias, int64_t M,
-                  int act_dtype, int out_dtype, int exact);
+                  int act_dtype, int out_dtype, int exact, const LinearFusion *fusion = nullptr);
 
 // ---------------------------------------------------------------- device helpers
 #ifdef __CUDACC__
@@ -117,6 +132,42 @@ __device__ __forceinline__ uint4 ldg_stream_v4(const void *p)
                  : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
                  : "l"(p));
     return v;
+}
+
+// ---- programmatic dependent launch -------------------------------------------------------------------------
+// Kernels of the decode step are launched so that the next one may become resident while the previous one is
+// still running. A kernel first does whatever touches only constant data (index arithmetic, requesting its
+// first weight chunks), then calls pdl_sync(): it lets ITS successor start the same way, and blocks until
+// every kernel before it in the stream has completed and its writes are visible. Nothing that an earlier
+// kernel writes or reads may be touched before pdl_sync(). Without the launch attribute both instructions
+// return at once.
+__device__ __forceinline__ void pdl_sync()
+{
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+// WEBLLM_B200_NO_PDL=1 in the environment launches every kernel fully serialised (for A/B timing).
+inline bool pdl_enabled()
+{
+    static const bool on = [] {
+        const char *e = getenv("WEBLLM_B200_NO_PDL");
+        return !(e && e[0] == '1');
+    }();
+    return on;
+}
+
+template <typename... P, typename... A>
+inline cudaError_t launch_pdl(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, A &&...args)
+{
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid, cfg.blockDim = block, cfg.dynamicSmemBytes = smem, cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, P(args)...);
 }
 
 #endif  // __CUDACC__

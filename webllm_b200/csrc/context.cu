@@ -571,4 +571,17 @@ int wb_plan_override(wb_context *ctx, int kernel, int split_k)
     return WB_OK;
 }
 
+int wb_linear_hint_next(wb_context *ctx, wb_handle next_weight)
+{
+    WB_CTX(ctx);
+    if (next_weight < 0) {
+        ctx->prefetch_weight = -1;
+        return WB_OK;
+    }
+    Weight *w = nullptr;
+    WB_CHECK(get_weight(ctx, next_weight, &w));
+    ctx->prefetch_weight = (int)(w - ctx->weights.data());
+    return WB_OK;
+}
+
 }  // extern "C"

@@ -39,10 +39,30 @@ namespace wb {
 
 namespace wb {
 
+
+#ifdef WB_GEMV_TRACE
+__device__ unsigned long long g_gemv_trace[64 * 8];
+__device__ unsigned g_gemv_trace_n;
+#define GT_INIT() __shared__ unsigned gt_slot; if (blockIdx.x == gridDim.x / 2 && blockIdx.y == 0 && threadIdx.x == 0) gt_slot = atomicAdd(&g_gemv_trace_n, 1u) & 63u
+#define GT(i) do { if (blockIdx.x == gridDim.x / 2 && blockIdx.y == 0 && threadIdx.x == 0) { unsigned long long _t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(_t)); g_gemv_trace[gt_slot * 8 + (i)] = _t; } } while (0)
+extern "C" int wb_debug_gemv_trace(unsigned long long *out, unsigned *n)
+{
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(out, g_gemv_trace, sizeof(unsigned long long) * 512);
+    cudaMemcpyFromSymbol(n, g_gemv_trace_n, 4);
+    return 0;
+}
+#else
+#define GT_INIT()
+#define GT(i)
+#endif
+
 template <int MB, bool EXACT>
 __global__ void __launch_bounds__(MB == 1 ? 256 : 512, MB == 1 ? 3 : 1) gptq_gemv_mma_kernel(const GemvParams p)
 {
     extern __shared__ uint4 smem_u4[];
+    GT_INIT();
+    GT(0);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int wn = warp % p.wn, wk = warp / p.wn;
@@ -81,6 +101,51 @@ __global__ void __launch_bounds__(MB == 1 ? 256 : 512, MB == 1 ? 3 : 1) gptq_gem
         cp_async_commit();
     };
     for (int s = 0; s < p.stages - 1; s++) request(s);
+    if (p.pf_bytes && tid == 0) {
+        // L2 prefetch of the weight that a following call will stream: each CTA asks for one slice, so the whole
+        // matrix is on its way while this kernel (and the small kernels after it) run, and that call finds its
+        // first chunks in L2 instead of paying the HBM and page-walk latency on its critical path.
+        const unsigned ncta = gridDim.x * gridDim.y, id = blockIdx.y * gridDim.x + blockIdx.x;
+        const unsigned slice = ((p.pf_bytes + ncta - 1) / ncta + 15u) & ~15u;
+        const unsigned long long off = (unsigned long long)id * slice;
+        if (off < p.pf_bytes) {
+            const unsigned n = min(slice, (unsigned)(p.pf_bytes - off));
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.pf_ptr + off), "r"(n) : "memory");
+        }
+    }
+    GT(1);
+    pdl_sync();  // weights are constant: their first chunks are requested while the previous kernel still runs
+    GT(2);
+
+    // ---- fused rmsnorm: the row statistic over the whole of K (not only this CTA's slice), fixed summation order
+    __shared__ float pro_red[16];
+    __shared__ float pro_rstd[8];
+    if (p.prologue == kPrologueRmsNorm) {
+        const bool writer = p.x_out != nullptr && blockIdx.x == 0 && blockIdx.y == 0;
+        for (int m = 0; m < p.M; m++) {
+            const float *xr = (const float *)p.x + (int64_t)m * p.K;
+            float ss = 0.f;
+            for (int k = tid * 4; k < p.K; k += nthreads * 4) {
+                float4 a = *reinterpret_cast<const float4 *>(xr + k);
+                if (p.delta) {
+                    const float4 d = *reinterpret_cast<const float4 *>(p.delta + (int64_t)m * p.K + k);
+                    a.x += d.x, a.y += d.y, a.z += d.z, a.w += d.w;
+                    if (writer) *reinterpret_cast<float4 *>(p.x_out + (int64_t)m * p.K + k) = a;
+                }
+                ss = fmaf(a.x, a.x, ss), ss = fmaf(a.y, a.y, ss), ss = fmaf(a.z, a.z, ss), ss = fmaf(a.w, a.w, ss);
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            if (lane == 0) pro_red[warp] = ss;
+            __syncthreads();
+            if (tid == 0) {
+                float tsum = 0.f;
+                for (int i = 0; i < (nthreads >> 5); i++) tsum += pro_red[i];
+                pro_rstd[m] = rsqrtf(tsum / (float)p.K + p.eps);
+            }
+            __syncthreads();
+        }
+    }
 
     // ---- stage this slice of the activations in the MMA's k-slot order: (x0,x4)(x2,x6)(x1,x5)(x3,x7) per packed
     // row, zeros for the rows of a last partial chunk, plus the per-chunk sums used for the zero-point term ----
@@ -93,9 +158,31 @@ __global__ void __launch_bounds__(MB == 1 ? 256 : 512, MB == 1 ? 3 : 1) gptq_gem
         const int m = idx / rows_pad, rl = idx - m * rows_pad;
         const int64_t k0 = (int64_t)(row_begin + rl) * 8;
         float v[8];
+        auto load8 = [&](const float *src) {
+            const float4 a = *reinterpret_cast<const float4 *>(src), b = *reinterpret_cast<const float4 *>(src + 4);
+            v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
+        };
         if (rl >= rows_cta) {
 #pragma unroll
             for (int j = 0; j < 8; j++) v[j] = 0.f;
+        } else if (p.prologue == kPrologueRmsNorm) {
+            load8((const float *)p.x + (int64_t)m * p.K + k0);
+            if (p.delta) {
+                const float4 a = *reinterpret_cast<const float4 *>(p.delta + (int64_t)m * p.K + k0);
+                const float4 b = *reinterpret_cast<const float4 *>(p.delta + (int64_t)m * p.K + k0 + 4);
+                v[0] += a.x, v[1] += a.y, v[2] += a.z, v[3] += a.w, v[4] += b.x, v[5] += b.y, v[6] += b.z, v[7] += b.w;
+            }
+            const float rstd = pro_rstd[m];
+#pragma unroll
+            for (int j = 0; j < 8; j++) v[j] = v[j] * rstd * p.norm_w[k0 + j];
+        } else if (p.prologue == kPrologueSiluMul) {
+            float u[8];
+            load8(p.up + (int64_t)m * p.ld_x + k0);
+#pragma unroll
+            for (int j = 0; j < 8; j++) u[j] = v[j];
+            load8((const float *)p.x + (int64_t)m * p.ld_x + k0);
+#pragma unroll
+            for (int j = 0; j < 8; j++) v[j] = v[j] / (1.f + expf(-v[j])) * u[j];
         } else if (p.x_f16) {
             const uint4 raw = *reinterpret_cast<const uint4 *>((const __half *)p.x + (int64_t)m * p.K + k0);
             const __half2 *h = reinterpret_cast<const __half2 *>(&raw);
@@ -106,9 +193,7 @@ __global__ void __launch_bounds__(MB == 1 ? 256 : 512, MB == 1 ? 3 : 1) gptq_gem
                 v[2 * j + 1] = f.y;
             }
         } else {
-            const float4 a = *reinterpret_cast<const float4 *>((const float *)p.x + (int64_t)m * p.K + k0);
-            const float4 b = *reinterpret_cast<const float4 *>((const float *)p.x + (int64_t)m * p.K + k0 + 4);
-            v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
+            load8((const float *)p.x + (int64_t)m * p.K + k0);
         }
         __half hi[8];
 #pragma unroll
@@ -150,6 +235,7 @@ __global__ void __launch_bounds__(MB == 1 ? 256 : 512, MB == 1 ? 3 : 1) gptq_gem
     }
     __syncthreads();
 
+    GT(3);
     // ---- main loop over this CTA's column tiles ----
     float *red = reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(smem_u4) + p.red_off);  // [wk][wn][MB*8][32]
     __shared__ int is_last;
@@ -171,6 +257,7 @@ __global__ void __launch_bounds__(MB == 1 ? 256 : 512, MB == 1 ? 3 : 1) gptq_gem
             request(slot_req);
             slot_req = slot_req + 1 == p.stages ? 0 : slot_req + 1;
             cp_async_wait(p.stages - 1);  // everything but the newest stages - 1 groups has landed
+            if (tj == 0 && i == 0) GT(4);
             ChunkRegs ra;
             read_slot(ring + slot_use * stage_stride, c, ra);
             slot_use = slot_use + 1 == p.stages ? 0 : slot_use + 1;
@@ -179,6 +266,7 @@ __global__ void __launch_bounds__(MB == 1 ? 256 : 512, MB == 1 ? 3 : 1) gptq_gem
             compute_chunk<MB, EXACT>(p, ra, rl0, g, t, xs_hi, xs_lo, xsum, chunk - ch_begin, chunks_cta, tot);
         }
 
+        if (tj == 0) GT(5);
         // reduce over the wk warps that share the column tile (fixed order), then write / split-K
 #pragma unroll
         for (int mb = 0; mb < MB; mb++)
@@ -232,6 +320,7 @@ __global__ void __launch_bounds__(MB == 1 ? 256 : 512, MB == 1 ? 3 : 1) gptq_gem
         __syncthreads();  // red and is_last are reused by the next tile
     }
     cp_async_wait(0);
+    GT(6);
 }
 
 // =====================================================================================================
@@ -246,6 +335,7 @@ __global__ void __launch_bounds__(256) dense_gemv_f16_kernel(const __half *__res
 {
     extern __shared__ float xsf[];  // [M][K]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    pdl_sync();
     for (int idx = tid; idx < M * K; idx += blockDim.x)
         xsf[idx] = x_f16 ? __half2float(((const __half *)x)[idx]) : ((const float *)x)[idx];
     __syncthreads();
@@ -325,6 +415,7 @@ __global__ void __launch_bounds__(128) linear_generic_kernel(const uint32_t *__r
                                                              int64_t K, int64_t pack_rows, int64_t group,
                                                              int64_t zcols, int x_f16, int out_f16, int round_x_f16)
 {
+    pdl_sync();
     const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= M * N) return;
     const int64_t m = idx / N, n = idx - m * N;
@@ -500,26 +591,36 @@ int plan_linear(wb_context *ctx, const Weight &w, int64_t M, int act_dtype, int 
     return fail(WB_ERR_BAD_ARG, "unknown kernel kind %d", kind);
 }
 
+// Most of a later weight that one call asks the L2 to fetch (a fraction of the 126 MB L2).
+constexpr uint64_t kPrefetchLimit = 32ull << 20;
+
 template <int MB>
 static cudaError_t launch_gemv_mb(const GemvParams &p, dim3 grid, int block, size_t smem, bool exact, cudaStream_t st)
 {
     if (exact) {
         cudaFuncSetAttribute(gptq_gemv_mma_kernel<MB, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemvSmemLimit);
-        gptq_gemv_mma_kernel<MB, true><<<grid, block, smem, st>>>(p);
+        return launch_pdl(gptq_gemv_mma_kernel<MB, true>, grid, dim3(block), smem, st, p);
     } else {
         cudaFuncSetAttribute(gptq_gemv_mma_kernel<MB, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemvSmemLimit);
-        gptq_gemv_mma_kernel<MB, false><<<grid, block, smem, st>>>(p);
+        return launch_pdl(gptq_gemv_mma_kernel<MB, false>, grid, dim3(block), smem, st, p);
     }
-    return cudaGetLastError();
+}
+
+bool linear_fusion_supported(wb_context *ctx, const Weight &w, int64_t M)
+{
+    if (M < 1 || M > 8 || ctx->force_kernel != 0) return false;
+    return gemv_mma_supports(w, M);  // what plan_linear picks first for M <= 16
 }
 
 int launch_linear(wb_context *ctx, const Weight &w, const void *A, void *C, const float *bias, int64_t M,
-                  int act_dtype, int out_dtype, int exact)
+                  int act_dtype, int out_dtype, int exact, const LinearFusion *fusion)
 {
     wb_plan plan;
     // exact mode only changes anything for f32 activations
     const int ex = (exact && act_dtype == WB_F32) ? 1 : 0;
     WB_CHECK(plan_linear(ctx, w, M, act_dtype, ex, &plan));
+    if (fusion && fusion->kind != 0 && (plan.kernel != WB_KERNEL_GEMV_MMA || M > 8 || act_dtype != WB_F32))
+        return fail(WB_ERR_UNSUPPORTED, "a fused prologue needs the int4 GEMV kernel, M <= 8 and f32 activations");
     // The streaming kernel always keeps f32 activations at ~22 bits (hi + lo halves): the reference's
     // GEMV reads A as f32 (gemm_gemv_f16.wgsl:45-58) and the extra MMAs are free in an HBM-bound kernel.
     const int ex_gemv = act_dtype == WB_F32 ? 1 : 0;
@@ -542,6 +643,20 @@ int launch_linear(wb_context *ctx, const Weight &w, const void *A, void *C, cons
         p.wn = plan.tile_m, p.wk = plan.tile_n;
         p.x_f16 = act_dtype == WB_F16, p.out_f16 = out_dtype == WB_F16;
         p.xs_stride = p.chunks_per_split * 16 + 4;
+        p.prologue = kPrologueNone, p.delta = nullptr, p.x_out = nullptr, p.norm_w = nullptr, p.eps = 0.f, p.up = nullptr;
+        p.ld_x = (int)w.K;
+        if (fusion && fusion->kind != 0) {
+            p.prologue = fusion->kind, p.delta = fusion->delta, p.x_out = fusion->x_out, p.norm_w = fusion->norm_w;
+            p.eps = fusion->eps, p.up = fusion->up;
+            if (fusion->kind == kPrologueSiluMul) p.ld_x = fusion->ld;
+        }
+        p.pf_ptr = nullptr, p.pf_bytes = 0;
+        if (ctx->prefetch_weight >= 0 && ctx->prefetch_weight < (int)ctx->weights.size()) {
+            const Weight &nx = ctx->weights[ctx->prefetch_weight];
+            p.pf_ptr = base + nx.off_main;  // qweight, scales and zeros of one registration are contiguous
+            p.pf_bytes = (unsigned)std::min<uint64_t>(nx.bytes, kPrefetchLimit);
+        }
+        ctx->prefetch_weight = -1;
         const int MB = M <= 8 ? 1 : (M <= 16 ? 2 : 4);
         p.stages = gemv_pick_stages(M, p.chunks_per_split, ex_gemv, p.wn, p.wk);
         const size_t smem = gemv_smem_bytes(M, p.chunks_per_split, ex_gemv, p.wn, p.wk, p.stages, &p.ring_off, &p.red_off);
@@ -560,15 +675,13 @@ int launch_linear(wb_context *ctx, const Weight &w, const void *A, void *C, cons
         const size_t smem = (size_t)M * w.K * 4;
         auto go = [&](auto kern) {
             cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
-            kern<<<plan.grid_x, 256, smem, ctx->stream>>>(W, A, C, bias, (int)M, (int)w.N, (int)w.K,
-                                                           act_dtype == WB_F16, out_dtype == WB_F16);
+            return launch_pdl(kern, dim3(plan.grid_x), dim3(256), smem, ctx->stream, W, A, C, bias, (int)M, (int)w.N, (int)w.K,
+                              (int)(act_dtype == WB_F16), (int)(out_dtype == WB_F16));
         };
-        if (M == 1) go(dense_gemv_f16_kernel<1>);
-        else if (M == 2) go(dense_gemv_f16_kernel<2>);
-        else if (M <= 4) go(dense_gemv_f16_kernel<4>);
-        else go(dense_gemv_f16_kernel<8>);
+        const cudaError_t e = M == 1 ? go(dense_gemv_f16_kernel<1>) : M == 2 ? go(dense_gemv_f16_kernel<2>)
+                              : M <= 4 ? go(dense_gemv_f16_kernel<4>) : go(dense_gemv_f16_kernel<8>);
         ctx->launches++;
-        WB_CUDA(cudaGetLastError());
+        WB_CUDA(e);
         return WB_OK;
     }
     case WB_KERNEL_GEMM_TC:
@@ -578,14 +691,14 @@ int launch_linear(wb_context *ctx, const Weight &w, const void *A, void *C, cons
         // f32 activations are rounded to fp16 for M > 1 unless exact mode is on, as the reference's
         // tiled GEMM does when it stages A (gemm_nt_f16_from_f32.wgsl:58-62); its GEMV keeps f32.
         const int round_x = (act_dtype == WB_F32 && !ex && M > 1) ? 1 : 0;
-        linear_generic_kernel<<<plan.grid_x, 128, 0, ctx->stream>>>(
+        const cudaError_t e = launch_pdl(linear_generic_kernel, dim3(plan.grid_x), dim3(128), 0, ctx->stream,
             gptq ? (const uint32_t *)(base + w.off_main) : nullptr,
             (gptq && w.has_zeros) ? (const uint32_t *)(base + w.off_zeros) : nullptr,
             gptq ? (const __half *)(base + w.off_scales) : nullptr, gptq ? nullptr : (const __half *)(base + w.off_main),
-            A, C, bias, M, w.N, w.K, w.pack_rows, gptq ? w.group : 8, w.zcols, act_dtype == WB_F16,
-            out_dtype == WB_F16, round_x);
+            A, C, bias, M, w.N, w.K, w.pack_rows, gptq ? w.group : 8, w.zcols, (int)(act_dtype == WB_F16),
+            (int)(out_dtype == WB_F16), round_x);
         ctx->launches++;
-        WB_CUDA(cudaGetLastError());
+        WB_CUDA(e);
         return WB_OK;
     }
     }
@@ -689,6 +802,8 @@ extern "C" int wb_gptq_gemv_static(const void *qweight, const void *qzeros, cons
     p.chunks = chunks, p.chunks_per_split = cps, p.group_chunks = (int)(group_size / 128), p.S = S;
     p.wn = wn, p.wk = wk, p.x_f16 = act_dtype == WB_F16, p.out_f16 = out_dtype == WB_F16, p.xs_stride = xs_stride;
     p.stages = stages, p.ring_off = ring_off, p.red_off = red_off;
+    p.pf_ptr = nullptr, p.pf_bytes = 0;
+    p.prologue = kPrologueNone, p.delta = nullptr, p.x_out = nullptr, p.norm_w = nullptr, p.eps = 0.f, p.up = nullptr, p.ld_x = (int)K;
     int sms = 148;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
     dim3 grid(gemv_grid_x(sms, ctas_n, S, wn * wk * 32, smem), S);

@@ -31,7 +31,24 @@ struct GemvParams {
     int stages;         // depth of the per-thread cp.async ring
     int ring_off;       // byte offset of the ring in dynamic shared memory
     int red_off;        // byte offset of the cross-warp reduction buffer
+    const char *pf_ptr;   // weight of a later call to pull into L2 while this one runs (nullable)
+    unsigned pf_bytes;    // multiple of 16
+    // Optional work fused in front of the projection (f32 activations, M <= 8); see GemvPrologue.
+    int prologue;
+    const float *delta;   // RmsNorm: x_in = x + delta (nullable)
+    float *x_out;         // RmsNorm with delta: where CTA (0, 0) stores x_in, [M, K]
+    const float *norm_w;  // RmsNorm: weight [K]
+    float eps;
+    const float *up;      // SiluMul: the second factor; rows of x and up are `ld_x` floats apart
+    int ld_x;
 };
+
+// What the GEMV does to its input while staging it:
+//   RmsNorm  the operand is rmsnorm(x + delta) * norm_w (rmsNormRef, src/reference/qwen-ref.ts:12-29, after the
+//            residual add of vec_add.wgsl); every CTA needs the whole row for the mean square, so K is not split
+//            for the statistic, only for the staging.
+//   SiluMul  the operand is silu(x) * up (siluMulRef, src/reference/qwen-ref.ts:119-123).
+enum GemvPrologue : int { kPrologueNone = 0, kPrologueRmsNorm = 1, kPrologueSiluMul = 2 };
 
 __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                           uint32_t b0, uint32_t b1)

@@ -42,6 +42,7 @@ struct wb_qwen {
     cudaGraphExec_t graph = nullptr;
     cudaStream_t graph_stream = nullptr;
     int graph_exact = -1;
+    uint64_t graph_launches = 0;    // kernels in one captured decode step
     int decode_mode = 0;            // 0 = automatic, 1 = one kernel per operation (CUDA graph), 2 = single persistent kernel
     wbq::Mega *mega = nullptr;
 };

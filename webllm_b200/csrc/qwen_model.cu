@@ -78,12 +78,16 @@ int alloc_bufs(wb_qwen *m, int arena, int64_t M, int64_t logit_rows, Bufs *b)
     return WB_OK;
 }
 
-int linear(wb_qwen *m, int wh, const float *A, float *Cout, int bias, int64_t M)
+// `next` (optional): the weight of the linear that follows in the forward pass; a decode step (M == 1) asks the
+// L2 for it while this projection runs.
+int linear(wb_qwen *m, int wh, const float *A, float *Cout, int bias, int64_t M, int next = -1,
+           const LinearFusion *fusion = nullptr)
 {
     wb_context *ctx = m->ctx;
+    ctx->prefetch_weight = M == 1 ? next : -1;
     const Weight &w = ctx->weights[wh];
     const float *bp = bias >= 0 ? (const float *)(ctx->arena[WB_ARENA_WEIGHTS].base + ctx->weights[bias].off_main) : nullptr;
-    return launch_linear(ctx, w, A, Cout, bp, M, WB_F32, WB_F32, m->exact);
+    return launch_linear(ctx, w, A, Cout, bp, M, WB_F32, WB_F32, m->exact, fusion);
 }
 
 // One forward pass over rows [0, M). past_ptr != nullptr: positions come from device memory (graph replay).
@@ -100,26 +104,54 @@ int forward_impl(wb_qwen *m, const Bufs &b, int64_t M, int64_t B, int64_t T, int
     WB_CHECK(op_embed(ctx, (const __half *)(wbase + ctx->weights[m->embed].off_main), b.tokens, b.x, (int)M, C, m->V));
     const float *delta = nullptr;  // pending residual contribution, folded into the next rmsnorm
     float *x = b.x;                // residual stream before `delta` is added
+    // A decode step over fused int4 projections runs five kernels per layer: the norms, silu * up and the rotary
+    // embedding + cache append ride inside the projections and the attention kernel (see GemvPrologue).
+    const LayerW &L0 = m->layers[0];
+    const bool fused_step = M == 1 && use_cache && L0.qkv >= 0 && L0.gate_up >= 0 && D % 8 == 0 && D <= 128 &&
+                            (size_t)(7 * D + m->cfg.max_t / 8 + 1) * 4 <= 48 * 1024 &&
+                            linear_fusion_supported(ctx, ctx->weights[L0.qkv], 1) &&
+                            linear_fusion_supported(ctx, ctx->weights[L0.gate_up], 1) &&
+                            linear_fusion_supported(ctx, ctx->weights[L0.down], 1);
     for (int i = 0; i < m->cfg.n_layer; i++) {
         const LayerW &L = m->layers[i];
+        char *kc = use_cache ? m->k_cache + i * layer_stride : nullptr;
+        char *vc = use_cache ? m->v_cache + i * layer_stride : nullptr;
+        if (fused_step) {
+            const int max_keys = past_ptr ? m->cfg.max_t : (int)(past + M);
+            float *x_in = (delta ? (x == b.x ? b.xa : b.x) : x);
+            LinearFusion f{};
+            f.kind = 1, f.delta = delta, f.x_out = delta ? x_in : nullptr, f.norm_w = f32w(L.in_norm), f.eps = m->cfg.rms_eps;
+            WB_CHECK(linear(m, L.qkv, x, b.q, L.qkvb, 1, L.o, &f));
+            x = x_in;
+            WB_CHECK(op_attention_decode(ctx, b.q, kc, vc, kv16, b.att, m->att_scratch, m->att_counters, H, KVH, D, past_ptr,
+                                         (int)past, max_keys, KV, b.k, b.v, m->cs_table));
+            WB_CHECK(linear(m, L.o, b.att, b.proj, -1, 1, L.gate_up));
+            float *xa = (x == b.x ? b.xa : b.x);
+            f.delta = b.proj, f.x_out = xa, f.norm_w = f32w(L.post_norm);
+            WB_CHECK(linear(m, L.gate_up, x, b.gu, -1, 1, L.down, &f));
+            x = xa;
+            LinearFusion g{};
+            g.kind = 2, g.up = b.gu + I, g.ld = 2 * I;
+            WB_CHECK(linear(m, L.down, b.gu, b.proj, -1, 1, i + 1 < m->cfg.n_layer ? m->layers[i + 1].qkv : -1, &g));
+            delta = b.proj;
+            continue;
+        }
         // --- attention sub-layer
         float *x_in = (delta ? (x == b.x ? b.xa : b.x) : x);
         WB_CHECK(op_rmsnorm(ctx, x, delta, x_in, f32w(L.in_norm), b.n, (int)M, C, m->cfg.rms_eps));
         x = x_in;
         if (L.qkv >= 0) {
-            WB_CHECK(linear(m, L.qkv, b.n, b.q, L.qkvb, M));
+            WB_CHECK(linear(m, L.qkv, b.n, b.q, L.qkvb, M, L.o));
         } else {
             WB_CHECK(linear(m, L.q, b.n, b.q, L.qb, M));
             WB_CHECK(linear(m, L.k, b.n, b.k, L.kb, M));
             WB_CHECK(linear(m, L.v, b.n, b.v, L.vb, M));
         }
-        char *kc = use_cache ? m->k_cache + i * layer_stride : nullptr;
-        char *vc = use_cache ? m->v_cache + i * layer_stride : nullptr;
         WB_CHECK(op_rope_kv(ctx, b.q, b.k, b.v, kc, vc, kv16, m->cs_table, (int)M, H, KVH, D, (int)T, past_ptr, (int)past,
                             b.ldq, b.ldk, b.ldv));
         if (use_cache) {
             const int max_keys = past_ptr ? m->cfg.max_t : (int)(past + M);
-            if (M == 1 && D % 8 == 0 && D <= 128 && (size_t)(5 * D + max_keys / 8 + 1) * 4 <= 48 * 1024) {
+            if (M == 1 && D % 8 == 0 && D <= 128 && (size_t)(7 * D + max_keys / 8 + 1) * 4 <= 48 * 1024) {
                 WB_CHECK(op_attention_decode(ctx, b.q, kc, vc, kv16, b.att, m->att_scratch, m->att_counters, H, KVH, D, past_ptr,
                                              (int)past, max_keys, KV));
             } else
@@ -128,20 +160,20 @@ int forward_impl(wb_qwen *m, const Bufs &b, int64_t M, int64_t B, int64_t T, int
         } else {
             WB_CHECK(op_attention(ctx, b.q, b.k, b.v, 0, b.att, (int)M, H, KVH, D, (int)T, nullptr, 0, 0, (int)T, b.ldq, b.ldk));
         }
-        WB_CHECK(linear(m, L.o, b.att, b.proj, -1, M));
+        WB_CHECK(linear(m, L.o, b.att, b.proj, -1, M, L.gate_up));
         // --- MLP sub-layer: xa = x + proj; n = rmsnorm(xa)
         float *xa = (x == b.x ? b.xa : b.x);
         WB_CHECK(op_rmsnorm(ctx, x, b.proj, xa, f32w(L.post_norm), b.n, (int)M, C, m->cfg.rms_eps));
         x = xa;
         if (L.gate_up >= 0) {
-            WB_CHECK(linear(m, L.gate_up, b.n, b.gu, -1, M));
+            WB_CHECK(linear(m, L.gate_up, b.n, b.gu, -1, M, L.down));
             WB_CHECK(op_silu_mul(ctx, b.gu, b.gu + I, b.act, (int)M, I, 2 * I));
         } else {
             WB_CHECK(linear(m, L.gate, b.n, b.gu, -1, M));
             WB_CHECK(linear(m, L.up, b.n, b.gu + M * I, -1, M));
             WB_CHECK(op_silu_mul(ctx, b.gu, b.gu + M * I, b.act, (int)M, I, I));
         }
-        WB_CHECK(linear(m, L.down, b.act, b.proj, -1, M));
+        WB_CHECK(linear(m, L.down, b.act, b.proj, -1, M, i + 1 < m->cfg.n_layer ? m->layers[i + 1].qkv : -1));
         delta = b.proj;
     }
     // final norm (+ the last residual add), then the tied lm_head
@@ -368,8 +400,11 @@ int wb_qwen_decode_greedy(wb_qwen *m, uint32_t first_token, int64_t n_steps, uin
     if (m->decode_mode == 2) return fail(WB_ERR_UNSUPPORTED, "the single-kernel decode step needs fused GPTQ projections (qkvW, gateUpW) with group % 128 == 0");
     if (m->graph && (m->graph_stream != ctx->stream || m->graph_exact != m->exact)) drop_graph(m);
     if (!m->graph) {
-        // Warm-up step outside capture (sets kernel attributes), then restore the state it advanced.
+        // Warm-up step outside capture (sets kernel attributes, counts the step's kernels), then restore the
+        // state it advanced.
+        const uint64_t launches_warm = ctx->launches;
         WB_CHECK(enqueue_graph_step(m));
+        m->graph_launches = ctx->launches - launches_warm;
         WB_CUDA(cudaMemcpyAsync(m->d_cache_len, state, sizeof state, cudaMemcpyHostToDevice, ctx->stream));
         WB_CUDA(cudaMemcpyAsync(m->dec.tokens, &first_token, 4, cudaMemcpyHostToDevice, ctx->stream));
         WB_CUDA(cudaStreamSynchronize(ctx->stream));
@@ -390,13 +425,7 @@ int wb_qwen_decode_greedy(wb_qwen *m, uint32_t first_token, int64_t n_steps, uin
         m->graph_stream = ctx->stream;
         m->graph_exact = m->exact;
     }
-    uint64_t per_step = 0;
-    {
-        // kernels per replayed step, for wb_launch_count
-        const LayerW &L = m->layers[0];
-        const uint64_t linears = (L.qkv >= 0 ? 1 : 3) + 1 + (L.gate_up >= 0 ? 1 : 2) + 1;
-        per_step = 1 + (uint64_t)m->cfg.n_layer * (linears + 5) + 2 + 2;
-    }
+    const uint64_t per_step = m->graph_launches;  // kernels per replayed step, for wb_launch_count
     for (int64_t s = 0; s < n_steps; s++) WB_CUDA(cudaGraphLaunch(m->graph, ctx->stream));
     ctx->launches += per_step * (uint64_t)n_steps;
     WB_CUDA(cudaMemcpyAsync(out_tokens, m->d_history, (size_t)n_steps * 4, cudaMemcpyDeviceToHost, ctx->stream));

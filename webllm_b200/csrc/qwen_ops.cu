@@ -10,6 +10,7 @@ namespace wb {
 __global__ void embed_f16_kernel(const __half *__restrict__ table, const uint32_t *__restrict__ tokens,
                                  float *__restrict__ x, int M, int C, int vocab)
 {
+    pdl_sync();
     const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (int64_t)M * C) return;
     const int m = (int)(idx / C), c = (int)(idx - (int64_t)m * C);
@@ -37,6 +38,7 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const float *__restrict__ 
                                                       float *__restrict__ x_out, const float *__restrict__ w,
                                                       float *__restrict__ y, int D, float eps)
 {
+    pdl_sync();
     __shared__ float red[8];
     const int64_t base = (int64_t)blockIdx.x * D;
     float ss = 0.f;
@@ -58,6 +60,7 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const float *__restrict__ 
 // vec_add.wgsl
 __global__ void add_kernel(const float *__restrict__ a, const float *__restrict__ b, float *__restrict__ out, int64_t n)
 {
+    pdl_sync();
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) out[i] = a[i] + b[i];
 }
@@ -67,6 +70,7 @@ __global__ void add_kernel(const float *__restrict__ a, const float *__restrict_
 __global__ void silu_mul_kernel(const float *__restrict__ gate, const float *__restrict__ up, float *__restrict__ out,
                                 int M, int I, int ld)
 {
+    pdl_sync();
     const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (int64_t)M * I) return;
     const int m = (int)(idx / I), i = (int)(idx - (int64_t)m * I);
@@ -84,6 +88,7 @@ __global__ void rope_kv_kernel(float *__restrict__ q, float *__restrict__ k, con
                                int M, int H, int KVH, int D, int T, const int *__restrict__ pos_offset_ptr,
                                int pos_offset_imm, int ldq, int ldk, int ldv)
 {
+    pdl_sync();
     const int half = D >> 1;
     const int per_row = (H + 2 * KVH) * half;
     const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -136,6 +141,7 @@ __global__ void __launch_bounds__(128) attention_kernel(const float *__restrict_
                                                         int KVH, int D, int T, const int *__restrict__ past_ptr,
                                                         int past_imm, int use_cache, int ldq, int kv_ld, float scale)
 {
+    pdl_sync();
     extern __shared__ float sm[];  // [D] query, [n_keys] scores
     __shared__ float red[4];
     const int row = blockIdx.x, h = blockIdx.y, kvh = h / (H / KVH);
@@ -220,29 +226,65 @@ __device__ __forceinline__ float dot_row<float>(const float *qs, const float *kp
     return dot;
 }
 
+// With k_raw != nullptr the kernel also does the work of rope_half.wgsl + kv_store.wgsl for the new position
+// (ropeHalfRef, src/reference/qwen-ref.ts:35-64): q, k_raw, v_raw are the projection outputs; q is rotated while it is
+// staged; the split that owns the newest key rotates k itself (rounded to the cache type, as a later step will read
+// it) instead of reading the cache row, and the first head of each KV group stores k and v to the cache.
 template <typename KV>
-__global__ void __launch_bounds__(128) attention_decode_kernel(const float *__restrict__ q, const KV *__restrict__ kmem,
-                                                               const KV *__restrict__ vmem, float *__restrict__ out,
+__global__ void __launch_bounds__(128) attention_decode_kernel(const float *__restrict__ q, KV *__restrict__ kmem,
+                                                               KV *__restrict__ vmem, float *__restrict__ out,
                                                                float *__restrict__ scratch, unsigned *__restrict__ counters,
                                                                int H, int KVH, int D, const int *__restrict__ past_ptr,
-                                                               int past_imm, int kv_ld, float scale)
+                                                               int past_imm, int kv_ld, float scale,
+                                                               const float *__restrict__ k_raw, const float *__restrict__ v_raw,
+                                                               const float *__restrict__ cs_table)
 {
-    extern __shared__ float sm[];  // [D] query (pre-scaled), [chunk] scores, [4][D] per-warp value sums
+    pdl_sync();
+    extern __shared__ float sm[];  // [D] query (pre-scaled), [2][D] new k, v (16-byte aligned: read as float4), [chunk] scores, [4][D] per-warp value sums
     __shared__ float red[4];
     __shared__ int is_last;
     const int h = blockIdx.x, s = blockIdx.y, kvh = h / (H / KVH);
-    const int n_keys = (past_ptr ? *past_ptr : past_imm) + 1;
+    const int pos = past_ptr ? *past_ptr : past_imm;
+    const int n_keys = pos + 1;
     const int chunk = (n_keys + ATT_SPLITS - 1) / ATT_SPLITS;
     const int k0 = s * chunk, k1 = min(n_keys, k0 + chunk), nk = max(0, k1 - k0);
-    float *qs = sm, *sc = sm + D, *wacc = sm + D + chunk;
+    float *qs = sm, *knew = sm + D, *vnew = sm + 2 * D, *sc = sm + 3 * D, *wacc = sc + chunk;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    for (int d = tid; d < D; d += blockDim.x) qs[d] = q[h * D + d] * scale;
+    const bool fused = k_raw != nullptr;
+    const bool own_new = fused && k1 == n_keys && nk > 0;  // this split holds the newest key
+    if (!fused) {
+        for (int d = tid; d < D; d += blockDim.x) qs[d] = q[h * D + d] * scale;
+    } else {
+        const int half = D >> 1;
+        for (int i = tid; i < half; i += blockDim.x) {
+            const float c = cs_table[((int64_t)pos * half + i) * 2], sn = cs_table[((int64_t)pos * half + i) * 2 + 1];
+            const float q0 = q[h * D + i], q1 = q[h * D + i + half];
+            qs[i] = (q0 * c - q1 * sn) * scale;
+            qs[i + half] = (q0 * sn + q1 * c) * scale;
+            if (own_new) {
+                const float x0 = k_raw[kvh * D + i], x1 = k_raw[kvh * D + i + half];
+                const KV r0 = (KV)(x0 * c - x1 * sn), r1 = (KV)(x0 * sn + x1 * c);
+                const KV v0 = (KV)v_raw[kvh * D + i], v1 = (KV)v_raw[kvh * D + i + half];
+                knew[i] = (float)r0, knew[i + half] = (float)r1, vnew[i] = (float)v0, vnew[i + half] = (float)v1;
+                if (h == kvh * (H / KVH)) {
+                    KV *kd = kmem + (int64_t)pos * kv_ld + kvh * D, *vd = vmem + (int64_t)pos * kv_ld + kvh * D;
+                    kd[i] = r0, kd[i + half] = r1, vd[i] = v0, vd[i + half] = v1;
+                }
+            }
+        }
+    }
     __syncthreads();
+    const int nk_mem = own_new ? nk - 1 : nk;  // keys of this split that are read from memory
 
     float lmax = -INFINITY;
-    for (int j = tid; j < nk; j += blockDim.x) {
+    for (int j = tid; j < nk_mem; j += blockDim.x) {
         const float dot = dot_row<KV>(qs, kmem + (int64_t)(k0 + j) * kv_ld + kvh * D, D);
         sc[j] = dot;
+        lmax = fmaxf(lmax, dot);
+    }
+    if (own_new && tid == (nk_mem & 127)) {  // the thread whose turn index nk - 1 would have been
+        const float dot = dot_row<float>(qs, knew, D);
+        sc[nk_mem] = dot;
         lmax = fmaxf(lmax, dot);
     }
 #pragma unroll
@@ -262,12 +304,14 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const float *__re
     for (int d0 = 0; d0 < D; d0 += 64) {
         float a0 = 0.f, a1 = 0.f;
         const int d = d0 + 2 * lane;
-        if (d < D)
-            for (int j = warp; j < nk; j += 4) {
+        if (d < D) {
+            for (int j = warp; j < nk_mem; j += 4) {
                 const KV *vp = vmem + (int64_t)(k0 + j) * kv_ld + kvh * D + d;
                 a0 = fmaf(sc[j], kv_load(vp), a0);
                 a1 = fmaf(sc[j], kv_load(vp + 1), a1);
             }
+            if (own_new && warp == (nk_mem & 3)) a0 = fmaf(sc[nk_mem], vnew[d], a0), a1 = fmaf(sc[nk_mem], vnew[d + 1], a1);
+        }
         if (d < D) wacc[warp * D + d] = a0, wacc[warp * D + d + 1] = a1;
     }
     __syncthreads();
@@ -304,6 +348,7 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const float *__re
 __global__ void __launch_bounds__(256) argmax_stage1(const float *__restrict__ logits, int V, float *__restrict__ bval,
                                                      int *__restrict__ bidx)
 {
+    pdl_sync();
     __shared__ float sv[256];
     __shared__ int si[256];
     float best = -INFINITY;
@@ -331,6 +376,7 @@ __global__ void __launch_bounds__(256) argmax_stage2(const float *__restrict__ b
                                                      uint32_t *__restrict__ token_out, uint32_t *__restrict__ history,
                                                      int *__restrict__ step_counter, int *__restrict__ cache_len)
 {
+    pdl_sync();
     __shared__ float sv[256];
     __shared__ int si[256];
     float best = -INFINITY;
@@ -373,26 +419,26 @@ __global__ void __launch_bounds__(256) argmax_stage2(const float *__restrict__ b
 int op_embed(wb_context *ctx, const __half *table, const uint32_t *tokens, float *x, int M, int C, int vocab)
 {
     const int64_t n = (int64_t)M * C;
-    embed_f16_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(table, tokens, x, M, C, vocab);
+    WB_CUDA(launch_pdl(embed_f16_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, ctx->stream, table, tokens, x, M, C, vocab));
     LAUNCH_OK(ctx);
 }
 
 int op_rmsnorm(wb_context *ctx, const float *x, const float *delta, float *x_out, const float *w, float *y, int M, int D, float eps)
 {
-    rmsnorm_kernel<<<M, 256, 0, ctx->stream>>>(x, delta, x_out, w, y, D, eps);
+    WB_CUDA(launch_pdl(rmsnorm_kernel, dim3(M), dim3(256), 0, ctx->stream, x, delta, x_out, w, y, D, eps));
     LAUNCH_OK(ctx);
 }
 
 int op_add(wb_context *ctx, const float *a, const float *b, float *out, int64_t n)
 {
-    add_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(a, b, out, n);
+    WB_CUDA(launch_pdl(add_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, ctx->stream, a, b, out, n));
     LAUNCH_OK(ctx);
 }
 
 int op_silu_mul(wb_context *ctx, const float *gate, const float *up, float *out, int M, int I, int ld)
 {
     const int64_t n = (int64_t)M * I;
-    silu_mul_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(gate, up, out, M, I, ld);
+    WB_CUDA(launch_pdl(silu_mul_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, ctx->stream, gate, up, out, M, I, ld));
     LAUNCH_OK(ctx);
 }
 
@@ -403,11 +449,11 @@ int op_rope_kv(wb_context *ctx, float *q, float *k, const float *v, void *k_cach
     const int64_t n = (int64_t)M * (H + 2 * KVH) * (D / 2);
     const unsigned blocks = (unsigned)((n + 255) / 256);
     if (kv_f16)
-        rope_kv_kernel<__half><<<blocks, 256, 0, ctx->stream>>>(q, k, v, (__half *)k_cache, (__half *)v_cache, cs_table, M, H,
-                                                                 KVH, D, T, pos_ptr, pos_imm, ldq, ldk, ldv);
+        WB_CUDA(launch_pdl(rope_kv_kernel<__half>, dim3(blocks), dim3(256), 0, ctx->stream, q, k, v, (__half *)k_cache, (__half *)v_cache, cs_table, M, H,
+                                                                 KVH, D, T, pos_ptr, pos_imm, ldq, ldk, ldv));
     else
-        rope_kv_kernel<float><<<blocks, 256, 0, ctx->stream>>>(q, k, v, (float *)k_cache, (float *)v_cache, cs_table, M, H, KVH,
-                                                                D, T, pos_ptr, pos_imm, ldq, ldk, ldv);
+        WB_CUDA(launch_pdl(rope_kv_kernel<float>, dim3(blocks), dim3(256), 0, ctx->stream, q, k, v, (float *)k_cache, (float *)v_cache, cs_table, M, H, KVH,
+                                                                D, T, pos_ptr, pos_imm, ldq, ldk, ldv));
     LAUNCH_OK(ctx);
 }
 
@@ -419,31 +465,30 @@ int op_attention(wb_context *ctx, const float *q, const void *kmem, const void *
     dim3 grid(M, H);
     if (kv_f16) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(attention_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        attention_kernel<__half><<<grid, 128, smem, ctx->stream>>>(q, (const __half *)kmem, (const __half *)vmem, out, H, KVH, D, T,
-                                                                    past_ptr, past_imm, use_cache, ldq, kv_ld, scale);
+        WB_CUDA(launch_pdl(attention_kernel<__half>, dim3(grid), dim3(128), smem, ctx->stream, q, (const __half *)kmem, (const __half *)vmem, out, H, KVH, D, T,
+                                                                    past_ptr, past_imm, use_cache, ldq, kv_ld, scale));
     } else {
         if (smem > 48 * 1024) cudaFuncSetAttribute(attention_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        attention_kernel<float><<<grid, 128, smem, ctx->stream>>>(q, (const float *)kmem, (const float *)vmem, out, H, KVH, D, T,
-                                                                   past_ptr, past_imm, use_cache, ldq, kv_ld, scale);
+        WB_CUDA(launch_pdl(attention_kernel<float>, dim3(grid), dim3(128), smem, ctx->stream, q, (const float *)kmem, (const float *)vmem, out, H, KVH, D, T,
+                                                                   past_ptr, past_imm, use_cache, ldq, kv_ld, scale));
     }
     LAUNCH_OK(ctx);
 }
 
-int op_attention_decode(wb_context *ctx, const float *q, const void *kmem, const void *vmem, int kv_f16, float *out,
-                        float *scratch, unsigned *counters, int H, int KVH, int D, const int *past_ptr, int past_imm,
-                        int max_keys, int kv_ld)
+int op_attention_decode(wb_context *ctx, const float *q, void *kmem, void *vmem, int kv_f16, float *out, float *scratch,
+                        unsigned *counters, int H, int KVH, int D, const int *past_ptr, int past_imm, int max_keys, int kv_ld,
+                        const float *k_raw, const float *v_raw, const float *cs_table)
 {
     const int chunk = (max_keys + ATT_SPLITS - 1) / ATT_SPLITS;
-    const size_t smem = (size_t)(5 * D + chunk) * sizeof(float);
+    const size_t smem = (size_t)(7 * D + chunk) * sizeof(float);
     const float scale = 1.0f / sqrtf((float)D);
     dim3 grid(H, ATT_SPLITS);
     if (kv_f16)
-        attention_decode_kernel<__half><<<grid, 128, smem, ctx->stream>>>(q, (const __half *)kmem, (const __half *)vmem, out,
-                                                                           scratch, counters, H, KVH, D, past_ptr, past_imm,
-                                                                           kv_ld, scale);
+        WB_CUDA(launch_pdl(attention_decode_kernel<__half>, grid, dim3(128), smem, ctx->stream, q, (__half *)kmem, (__half *)vmem, out,
+                           scratch, counters, H, KVH, D, past_ptr, past_imm, kv_ld, scale, k_raw, v_raw, cs_table));
     else
-        attention_decode_kernel<float><<<grid, 128, smem, ctx->stream>>>(q, (const float *)kmem, (const float *)vmem, out, scratch,
-                                                                          counters, H, KVH, D, past_ptr, past_imm, kv_ld, scale);
+        WB_CUDA(launch_pdl(attention_decode_kernel<float>, grid, dim3(128), smem, ctx->stream, q, (float *)kmem, (float *)vmem, out,
+                           scratch, counters, H, KVH, D, past_ptr, past_imm, kv_ld, scale, k_raw, v_raw, cs_table));
     LAUNCH_OK(ctx);
 }
 
@@ -453,9 +498,9 @@ int op_argmax(wb_context *ctx, const float *logits, int V, float *bval, int *bid
               int *step_counter, int *cache_len)
 {
     const int nb = 128;
-    argmax_stage1<<<nb, 256, 0, ctx->stream>>>(logits, V, bval, bidx);
+    WB_CUDA(launch_pdl(argmax_stage1, dim3(nb), dim3(256), 0, ctx->stream, logits, V, bval, bidx));
     ctx->launches++;
-    argmax_stage2<<<1, 256, 0, ctx->stream>>>(bval, bidx, nb, token_out, history, step_counter, cache_len);
+    WB_CUDA(launch_pdl(argmax_stage2, dim3(1), dim3(256), 0, ctx->stream, bval, bidx, nb, token_out, history, step_counter, cache_len));
     LAUNCH_OK(ctx);
 }
 

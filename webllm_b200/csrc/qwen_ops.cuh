@@ -18,9 +18,11 @@ int op_attention(wb_context *ctx, const float *q, const void *kmem, const void *
                  int KVH, int D, int T, const int *past_ptr, int past_imm, int use_cache, int max_keys, int ldq, int kv_ld);
 // One query row against the cache, keys split over several CTAs per head; scratch holds the per-slice
 // softmax state (op_attention_decode_scratch_floats floats), counters one zeroed word per head.
-int op_attention_decode(wb_context *ctx, const float *q, const void *kmem, const void *vmem, int kv_f16, float *out,
-                        float *scratch, unsigned *counters, int H, int KVH, int D, const int *past_ptr, int past_imm,
-                        int max_keys, int kv_ld);
+// With k_raw / v_raw / cs_table set, q, k_raw and v_raw are the un-rotated projection outputs: the kernel applies the
+// rotary embedding and appends the new key and value to the cache itself (no op_rope_kv before it).
+int op_attention_decode(wb_context *ctx, const float *q, void *kmem, void *vmem, int kv_f16, float *out, float *scratch,
+                        unsigned *counters, int H, int KVH, int D, const int *past_ptr, int past_imm, int max_keys, int kv_ld,
+                        const float *k_raw = nullptr, const float *v_raw = nullptr, const float *cs_table = nullptr);
 int op_attention_decode_scratch_floats(int H, int D);
 int op_argmax(wb_context *ctx, const float *logits, int V, float *bval, int *bidx, uint32_t *token_out, uint32_t *history,
               int *step_counter, int *cache_len);

@@ -162,6 +162,10 @@ class Gpu:
                                     L.WB_F32 if A.dtype == "f32" else L.WB_F16,
                                     L.WB_F32 if Cout.dtype == "f32" else L.WB_F16, 1 if exact else 0))
 
+    def hint_next(self, weight: int | None) -> None:
+        """The next ``linear`` call also asks the L2 to fetch ``weight``, which a later call will stream."""
+        L.check(self._lib.wb_linear_hint_next(self._ctx, -1 if weight is None else weight))
+
     def plan(self, weight: int, M: int, act_dtype: str = "f32", exact: bool = False) -> dict:
         p = L.Plan()
         L.check(self._lib.wb_plan_query(self._ctx, weight, M, L.WB_F32 if act_dtype == "f32" else L.WB_F16,
