@@ -11,26 +11,36 @@ namespace wb {
 // =====================================================================================================
 // Fused int4 GEMV for 1 <= M <= 32  (C[M,N] = A[M,K] . W[N,K]^T + bias)
 //
-// HBM-bound: every packed word is read exactly once with 128-bit loads straight from the checkpoint
-// layout qweight[K/8, N] (a warp reads 4 packed rows x 32 columns = four full 128-byte lines per load
-// instruction). A scalar-FMA unpack needs >= 3 issue slots per weight, which at 2 weights per byte is
-// more than the SMs can issue at HBM speed, so the products run on the warp-level tensor-core MMA
+// HBM-bound: every packed word is read exactly once, with 16-byte cp.async copies straight from the
+// checkpoint layout qweight[K/8, N] (a warp reads 4 packed rows x 32 columns = four full 128-byte lines per
+// copy instruction) into a per-thread ring in shared memory, so that several chunks per thread are in flight
+// without holding registers. A scalar-FMA unpack needs >= 3 issue slots per weight, which at 2 weights per
+// byte is more than the SMs can issue at HBM speed, so the products run on the warp-level tensor-core MMA
 // (m16n8k16, fp16 in, f32 accumulate) with the weight tile as the 16-row operand and up to 8 activation
-// rows as the 8-column operand: ~1.3 issue slots per weight.
+// rows as the 8-column operand.
 //
-//   * unpack: (w & 0x000f000f) | 0x6400'6400 is the half2 (1024+q_j, 1024+q_{j+4}); the 0x00f000f0 mask
-//     gives (1024+16 q). Subtracting 1024+zero (resp. one fma with 1/16 and -(64+zero)) yields the exact
-//     integers q - zero in fp16. Per-group scales are applied in f32 to the group's partial sum, so no
-//     product is ever rounded to fp16.
-//   * the MMA only needs the two operands to agree on which k sits in which slot, so the nibble order
-//     that the masks produce is used as is and the activations are staged in shared memory in the same
-//     order: 16 bytes per (row m, packed row r) holding (x0,x4)(x1,x5)(x2,x6)(x3,x7) as half2.
+//   * unpack: none to speak of. w & 0x000f000f is, read as half2, the pair of fp16 SUBNORMALS
+//     (q_j, q_{j+4}) * 2^-24, and w & 0x00f000f0 the pair 16 * (q_{j+1}, q_{j+5}) * 2^-24 (the same two masks on
+//     w >> 8 give the other four nibbles). The MMA multiplies subnormals exactly; the even and odd nibbles go
+//     to separate f32 accumulators and are recombined as 2^24 * (acc_even + acc_odd / 16). The zero point
+//     never touches the weights: sum_k (q_k - z) x_k = sum_k q_k x_k - z * sum_k x_k, with the per-chunk
+//     activation sums computed once while the activations are staged. Per-group scales are applied in f32 to
+//     the group's partial sum, so no product is ever rounded to fp16.
+//   * the MMA only needs the two operands to agree on which k sits in which slot, so the nibble order that
+//     the masks produce is used as is and the activations are staged in shared memory in the same order:
+//     16 bytes per (row m, packed row r) holding (x0,x4)(x2,x6)(x1,x5)(x3,x7) as half2, plus a row of zeros
+//     that lanes without a batch row read (no predicates in the loop).
 //   * f32 activations are split into hi + lo fp16 halves (two MMAs per tile), which keeps ~22 bits of
 //     them: the reference's GEMV reads A as f32 (gemm_gemv_f16.wgsl:45-58). fp16 activations need one.
+//   * column tiles are persistent: the grid is what is resident at once and each CTA walks tiles
+//     blockIdx.x, blockIdx.x + gridDim.x, ..., the ring running ahead across tile boundaries.
 //   * split-K: grid.y slices of whole 128-k chunks. Each slice writes its partial tile to the workspace;
 //     the last CTA to arrive for a column tile (arrival counter, no waiting) adds the slices in slice
 //     order and the bias once, so the result does not depend on scheduling
 //     (cf. gemm_gemv_split_reduce.wgsl:36-38).
+//   * decode fusions (M <= 8, f32 activations): the staging step can compute rmsnorm(x + delta) * w or
+//     silu(x) * up instead of copying x (GemvPrologue), and one thread per CTA can ask the L2 for the weight
+//     of a following call (cp.async.bulk.prefetch.L2) so that call starts on L2 hits.
 // =====================================================================================================
 
 }  // namespace wb
@@ -40,29 +50,10 @@ namespace wb {
 namespace wb {
 
 
-#ifdef WB_GEMV_TRACE
-__device__ unsigned long long g_gemv_trace[64 * 8];
-__device__ unsigned g_gemv_trace_n;
-#define GT_INIT() __shared__ unsigned gt_slot; if (blockIdx.x == gridDim.x / 2 && blockIdx.y == 0 && threadIdx.x == 0) gt_slot = atomicAdd(&g_gemv_trace_n, 1u) & 63u
-#define GT(i) do { if (blockIdx.x == gridDim.x / 2 && blockIdx.y == 0 && threadIdx.x == 0) { unsigned long long _t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(_t)); g_gemv_trace[gt_slot * 8 + (i)] = _t; } } while (0)
-extern "C" int wb_debug_gemv_trace(unsigned long long *out, unsigned *n)
-{
-    cudaDeviceSynchronize();
-    cudaMemcpyFromSymbol(out, g_gemv_trace, sizeof(unsigned long long) * 512);
-    cudaMemcpyFromSymbol(n, g_gemv_trace_n, 4);
-    return 0;
-}
-#else
-#define GT_INIT()
-#define GT(i)
-#endif
-
 template <int MB, bool EXACT>
 __global__ void __launch_bounds__(MB == 1 ? 256 : 512, MB == 1 ? 3 : 1) gptq_gemv_mma_kernel(const GemvParams p)
 {
     extern __shared__ uint4 smem_u4[];
-    GT_INIT();
-    GT(0);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int wn = warp % p.wn, wk = warp / p.wn;
@@ -113,9 +104,7 @@ __global__ void __launch_bounds__(MB == 1 ? 256 : 512, MB == 1 ? 3 : 1) gptq_gem
             asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.pf_ptr + off), "r"(n) : "memory");
         }
     }
-    GT(1);
     pdl_sync();  // weights are constant: their first chunks are requested while the previous kernel still runs
-    GT(2);
 
     // ---- fused rmsnorm: the row statistic over the whole of K (not only this CTA's slice), fixed summation order
     __shared__ float pro_red[16];
@@ -234,8 +223,6 @@ __global__ void __launch_bounds__(MB == 1 ? 256 : 512, MB == 1 ? 3 : 1) gptq_gem
         if (rr == 0) xsum[task] = sx;
     }
     __syncthreads();
-
-    GT(3);
     // ---- main loop over this CTA's column tiles ----
     float *red = reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(smem_u4) + p.red_off);  // [wk][wn][MB*8][32]
     __shared__ int is_last;
@@ -257,7 +244,6 @@ __global__ void __launch_bounds__(MB == 1 ? 256 : 512, MB == 1 ? 3 : 1) gptq_gem
             request(slot_req);
             slot_req = slot_req + 1 == p.stages ? 0 : slot_req + 1;
             cp_async_wait(p.stages - 1);  // everything but the newest stages - 1 groups has landed
-            if (tj == 0 && i == 0) GT(4);
             ChunkRegs ra;
             read_slot(ring + slot_use * stage_stride, c, ra);
             slot_use = slot_use + 1 == p.stages ? 0 : slot_use + 1;
@@ -265,8 +251,6 @@ __global__ void __launch_bounds__(MB == 1 ? 256 : 512, MB == 1 ? 3 : 1) gptq_gem
             const int rl0 = chunk * 16 + t - row_begin;
             compute_chunk<MB, EXACT>(p, ra, rl0, g, t, xs_hi, xs_lo, xsum, chunk - ch_begin, chunks_cta, tot);
         }
-
-        if (tj == 0) GT(5);
         // reduce over the wk warps that share the column tile (fixed order), then write / split-K
 #pragma unroll
         for (int mb = 0; mb < MB; mb++)
@@ -320,7 +304,6 @@ __global__ void __launch_bounds__(MB == 1 ? 256 : 512, MB == 1 ? 3 : 1) gptq_gem
         __syncthreads();  // red and is_last are reused by the next tile
     }
     cp_async_wait(0);
-    GT(6);
 }
 
 // =====================================================================================================
@@ -651,7 +634,8 @@ int launch_linear(wb_context *ctx, const Weight &w, const void *A, void *C, cons
             if (fusion->kind == kPrologueSiluMul) p.ld_x = fusion->ld;
         }
         p.pf_ptr = nullptr, p.pf_bytes = 0;
-        if (ctx->prefetch_weight >= 0 && ctx->prefetch_weight < (int)ctx->weights.size()) {
+        static const bool l2pf = [] { const char *e = getenv("WEBLLM_B200_NO_L2PF"); return !(e && e[0] == '1'); }();
+        if (l2pf && ctx->prefetch_weight >= 0 && ctx->prefetch_weight < (int)ctx->weights.size()) {
             const Weight &nx = ctx->weights[ctx->prefetch_weight];
             p.pf_ptr = base + nx.off_main;  // qweight, scales and zeros of one registration are contiguous
             p.pf_bytes = (unsigned)std::min<uint64_t>(nx.bytes, kPrefetchLimit);
