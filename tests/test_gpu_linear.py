@@ -182,3 +182,23 @@ def test_argument_errors(gpu):
         gpu.linear(h, Tensor(gpu.arena.capacity - 256, 128), Cc, None, 1)
     with pytest.raises(WebllmError, match="缺少 f16 权重"):
         gpu.linear(hb, A, Cc, None, 1)
+
+
+def test_hint_next_prefetches_without_changing_results(gpu, oracle):
+    """wb_linear_hint_next only asks the L2 for a later call's weight: results are bitwise the same with it, the
+    hint is consumed by one call, and a bad handle is refused."""
+    from webllm_b200 import _lib
+    a = synthetic.random_gptq(896, 1152, 128, seed=41, zeros="any")
+    b = synthetic.random_gptq(896, 4864, 128, seed=42, zeros="any")
+    ha, hb = register(gpu, "hint_a", a), register(gpu, "hint_b", b)
+    x = np.random.default_rng(9).standard_normal((1, 896)).astype(np.float32)
+    plain = [run_linear(gpu, ha, x, 1, 1152), run_linear(gpu, hb, x, 1, 4864)]
+    gpu.hint_next(hb)
+    hinted_a = run_linear(gpu, ha, x, 1, 1152)
+    hinted_b = run_linear(gpu, hb, x, 1, 4864)  # no hint pending any more
+    assert np.array_equal(hinted_a.view(np.uint32), plain[0].view(np.uint32))
+    assert np.array_equal(hinted_b.view(np.uint32), plain[1].view(np.uint32))
+    gpu.hint_next(None)
+    with pytest.raises(_lib.WebllmError) as e:
+        gpu.hint_next(10 ** 6)
+    assert e.value.status == _lib.WB_ERR_NOT_FOUND

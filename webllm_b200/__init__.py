@@ -12,3 +12,4 @@ from .quant import GptqInt4Params, dequantize_gptq_int4  # noqa: F401
 from .qwen import QwenGpt, concat_gptq  # noqa: F401,E402
 from .generate import SamplerOptions, generate_qwen, sample_token  # noqa: F401,E402
 from .plan import plan_gemv_split  # noqa: F401,E402
+from .qwen_loader import QwenLoadResult, load_qwen_weights  # noqa: F401,E402
