@@ -50,10 +50,33 @@ namespace wb {
 namespace wb {
 
 
+
+// Build-time diagnostic (-DWB_GEMV_TRACE): one CTA of every launch records globaltimer stamps at the phase
+// boundaries into a ring of 64 launches, read back with wb_debug_gemv_trace. Compiled out otherwise.
+#ifdef WB_GEMV_TRACE
+__device__ unsigned long long g_gemv_trace[64 * 8];
+__device__ unsigned g_gemv_trace_n;
+#define GT_ON (blockIdx.x == gridDim.x / 2 && blockIdx.y == 0 && threadIdx.x == 0)
+#define GT_INIT() __shared__ unsigned gt_slot; if (GT_ON) gt_slot = atomicAdd(&g_gemv_trace_n, 1u) & 63u
+#define GT(i) do { if (GT_ON) { unsigned long long _t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(_t)); g_gemv_trace[gt_slot * 8 + (i)] = _t; } } while (0)
+extern "C" int wb_debug_gemv_trace(unsigned long long *out, unsigned *n)
+{
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(out, g_gemv_trace, sizeof(unsigned long long) * 512);
+    cudaMemcpyFromSymbol(n, g_gemv_trace_n, 4);
+    return 0;
+}
+#else
+#define GT_INIT()
+#define GT(i)
+#endif
+
 template <int MB, bool EXACT>
 __global__ void __launch_bounds__(MB == 1 ? 256 : 512, MB == 1 ? 3 : 1) gptq_gemv_mma_kernel(const GemvParams p)
 {
     extern __shared__ uint4 smem_u4[];
+    GT_INIT();
+    GT(0);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int wn = warp % p.wn, wk = warp / p.wn;
@@ -104,125 +127,231 @@ __global__ void __launch_bounds__(MB == 1 ? 256 : 512, MB == 1 ? 3 : 1) gptq_gem
             asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.pf_ptr + off), "r"(n) : "memory");
         }
     }
+    GT(1);
     pdl_sync();  // weights are constant: their first chunks are requested while the previous kernel still runs
 
-    // ---- fused rmsnorm: the row statistic over the whole of K (not only this CTA's slice), fixed summation order
+    GT(2);
+    // ---- stage the activations (see the two branches) ----
+    const int rows_pad = chunks_cta * 16;
     __shared__ float pro_red[16];
     __shared__ float pro_rstd[8];
-    if (p.prologue == kPrologueRmsNorm) {
-        const bool writer = p.x_out != nullptr && blockIdx.x == 0 && blockIdx.y == 0;
-        for (int m = 0; m < p.M; m++) {
-            const float *xr = (const float *)p.x + (int64_t)m * p.K;
+    // Decode fast path: one row of activations and at most one packed row (8 values) per thread. Everything a thread
+    // needs is loaded once into registers, the rmsnorm statistic is reduced across the CTA (K is not split when the
+    // norm is fused), the operand halves go to shared memory and the per-chunk sums come from a half-warp shuffle:
+    // one global round trip and two barriers instead of two round trips and four.
+    const bool fast = p.M == 1 && rows_pad <= nthreads && (p.prologue != kPrologueRmsNorm || gridDim.y == 1);
+    if (fast) {
+        const int rl = tid;
+        const bool has = rl < rows_pad, real = rl < rows_cta;
+        const int64_t k0 = (int64_t)(row_begin + rl) * 8;
+        float v[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) v[j] = 0.f;
+        auto load8 = [&](const float *src, float (&dst)[8]) {
+            const float4 a = *reinterpret_cast<const float4 *>(src), b = *reinterpret_cast<const float4 *>(src + 4);
+            dst[0] = a.x, dst[1] = a.y, dst[2] = a.z, dst[3] = a.w, dst[4] = b.x, dst[5] = b.y, dst[6] = b.z, dst[7] = b.w;
+        };
+        if (has) xs_hi[p.xs_stride + rl] = make_uint4(0, 0, 0, 0);  // the zero row (index M = 1)
+        if constexpr (EXACT)
+            if (has) xs_lo[p.xs_stride + rl] = make_uint4(0, 0, 0, 0);
+        if (p.prologue == kPrologueRmsNorm) {
+            float w8[8], d8[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++) w8[j] = 0.f, d8[j] = 0.f;
+            if (real) {
+                load8((const float *)p.x + k0, v);
+                if (p.delta) load8(p.delta + k0, d8);
+                load8(p.norm_w + k0, w8);
+            }
             float ss = 0.f;
-            for (int k = tid * 4; k < p.K; k += nthreads * 4) {
-                float4 a = *reinterpret_cast<const float4 *>(xr + k);
-                if (p.delta) {
-                    const float4 d = *reinterpret_cast<const float4 *>(p.delta + (int64_t)m * p.K + k);
-                    a.x += d.x, a.y += d.y, a.z += d.z, a.w += d.w;
-                    if (writer) *reinterpret_cast<float4 *>(p.x_out + (int64_t)m * p.K + k) = a;
-                }
-                ss = fmaf(a.x, a.x, ss), ss = fmaf(a.y, a.y, ss), ss = fmaf(a.z, a.z, ss), ss = fmaf(a.w, a.w, ss);
+#pragma unroll
+            for (int j = 0; j < 8; j++) v[j] += d8[j], ss = fmaf(v[j], v[j], ss);
+            if (real && p.delta && p.x_out != nullptr && blockIdx.x == 0) {
+                *reinterpret_cast<float4 *>(p.x_out + k0) = make_float4(v[0], v[1], v[2], v[3]);
+                *reinterpret_cast<float4 *>(p.x_out + k0 + 4) = make_float4(v[4], v[5], v[6], v[7]);
             }
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
             if (lane == 0) pro_red[warp] = ss;
             __syncthreads();
-            if (tid == 0) {
-                float tsum = 0.f;
-                for (int i = 0; i < (nthreads >> 5); i++) tsum += pro_red[i];
-                pro_rstd[m] = rsqrtf(tsum / (float)p.K + p.eps);
-            }
-            __syncthreads();
-        }
-    }
-
-    // ---- stage this slice of the activations in the MMA's k-slot order: (x0,x4)(x2,x6)(x1,x5)(x3,x7) per packed
-    // row, zeros for the rows of a last partial chunk, plus the per-chunk sums used for the zero-point term ----
-    const int rows_pad = chunks_cta * 16;
-    for (int rl = tid; rl < rows_pad; rl += nthreads) {
-        xs_hi[p.M * p.xs_stride + rl] = make_uint4(0, 0, 0, 0);
-        if constexpr (EXACT) xs_lo[p.M * p.xs_stride + rl] = make_uint4(0, 0, 0, 0);
-    }
-    for (int idx = tid; idx < p.M * rows_pad; idx += nthreads) {
-        const int m = idx / rows_pad, rl = idx - m * rows_pad;
-        const int64_t k0 = (int64_t)(row_begin + rl) * 8;
-        float v[8];
-        auto load8 = [&](const float *src) {
-            const float4 a = *reinterpret_cast<const float4 *>(src), b = *reinterpret_cast<const float4 *>(src + 4);
-            v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
-        };
-        if (rl >= rows_cta) {
+            float tsum = 0.f;
+            for (int i = 0; i < (nthreads >> 5); i++) tsum += pro_red[i];  // same order in every thread
+            const float rstd = rsqrtf(tsum / (float)p.K + p.eps);
 #pragma unroll
-            for (int j = 0; j < 8; j++) v[j] = 0.f;
-        } else if (p.prologue == kPrologueRmsNorm) {
-            load8((const float *)p.x + (int64_t)m * p.K + k0);
-            if (p.delta) {
-                const float4 a = *reinterpret_cast<const float4 *>(p.delta + (int64_t)m * p.K + k0);
-                const float4 b = *reinterpret_cast<const float4 *>(p.delta + (int64_t)m * p.K + k0 + 4);
-                v[0] += a.x, v[1] += a.y, v[2] += a.z, v[3] += a.w, v[4] += b.x, v[5] += b.y, v[6] += b.z, v[7] += b.w;
-            }
-            const float rstd = pro_rstd[m];
-#pragma unroll
-            for (int j = 0; j < 8; j++) v[j] = v[j] * rstd * p.norm_w[k0 + j];
+            for (int j = 0; j < 8; j++) v[j] = v[j] * rstd * w8[j];
         } else if (p.prologue == kPrologueSiluMul) {
-            float u[8];
-            load8(p.up + (int64_t)m * p.ld_x + k0);
+            if (real) {
+                float u[8];
+                load8(p.up + k0, u);
+                load8((const float *)p.x + k0, v);
 #pragma unroll
-            for (int j = 0; j < 8; j++) u[j] = v[j];
-            load8((const float *)p.x + (int64_t)m * p.ld_x + k0);
-#pragma unroll
-            for (int j = 0; j < 8; j++) v[j] = v[j] / (1.f + expf(-v[j])) * u[j];
-        } else if (p.x_f16) {
-            const uint4 raw = *reinterpret_cast<const uint4 *>((const __half *)p.x + (int64_t)m * p.K + k0);
-            const __half2 *h = reinterpret_cast<const __half2 *>(&raw);
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-                const float2 f = __half22float2(h[j]);
-                v[2 * j] = f.x;
-                v[2 * j + 1] = f.y;
+                for (int j = 0; j < 8; j++) v[j] = v[j] / (1.f + expf(-v[j])) * u[j];
             }
-        } else {
-            load8((const float *)p.x + (int64_t)m * p.K + k0);
+        } else if (real) {
+            if (p.x_f16) {
+                const uint4 raw = *reinterpret_cast<const uint4 *>((const __half *)p.x + k0);
+                const __half2 *h = reinterpret_cast<const __half2 *>(&raw);
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const float2 f = __half22float2(h[j]);
+                    v[2 * j] = f.x;
+                    v[2 * j + 1] = f.y;
+                }
+            } else {
+                load8((const float *)p.x + k0, v);
+            }
         }
-        __half hi[8];
+        if (has) {
+            auto sum8 = [](const uint4 &o) {
+                const float2 a = __half22float2(u32_as_h2(o.x)), b = __half22float2(u32_as_h2(o.y));
+                const float2 cc = __half22float2(u32_as_h2(o.z)), d = __half22float2(u32_as_h2(o.w));
+                return ((a.x + a.y) + (b.x + b.y)) + ((cc.x + cc.y) + (d.x + d.y));
+            };
+            __half hi[8];
 #pragma unroll
-        for (int j = 0; j < 8; j++) hi[j] = __float2half_rn(v[j]);
-        uint4 o;
-        o.x = h2_as_u32(__halves2half2(hi[0], hi[4]));
-        o.y = h2_as_u32(__halves2half2(hi[2], hi[6]));
-        o.z = h2_as_u32(__halves2half2(hi[1], hi[5]));
-        o.w = h2_as_u32(__halves2half2(hi[3], hi[7]));
-        xs_hi[m * p.xs_stride + rl] = o;
-        if constexpr (EXACT) {
-            __half lo[8];
+            for (int j = 0; j < 8; j++) hi[j] = __float2half_rn(v[j]);
+            uint4 o;
+            o.x = h2_as_u32(__halves2half2(hi[0], hi[4]));
+            o.y = h2_as_u32(__halves2half2(hi[2], hi[6]));
+            o.z = h2_as_u32(__halves2half2(hi[1], hi[5]));
+            o.w = h2_as_u32(__halves2half2(hi[3], hi[7]));
+            xs_hi[rl] = o;
+            float sx = sum8(o);
+            if constexpr (EXACT) {
+                __half lo[8];
 #pragma unroll
-            for (int j = 0; j < 8; j++) lo[j] = __float2half_rn(v[j] - __half2float(hi[j]));
-            o.x = h2_as_u32(__halves2half2(lo[0], lo[4]));
-            o.y = h2_as_u32(__halves2half2(lo[2], lo[6]));
-            o.z = h2_as_u32(__halves2half2(lo[1], lo[5]));
-            o.w = h2_as_u32(__halves2half2(lo[3], lo[7]));
-            xs_lo[m * p.xs_stride + rl] = o;
+                for (int j = 0; j < 8; j++) lo[j] = __float2half_rn(v[j] - __half2float(hi[j]));
+                o.x = h2_as_u32(__halves2half2(lo[0], lo[4]));
+                o.y = h2_as_u32(__halves2half2(lo[2], lo[6]));
+                o.z = h2_as_u32(__halves2half2(lo[1], lo[5]));
+                o.w = h2_as_u32(__halves2half2(lo[3], lo[7]));
+                xs_lo[rl] = o;
+                sx += sum8(o);
+            }
+            // rows_pad is a multiple of 16: a half-warp is wholly inside this branch or wholly outside
+            const unsigned half_mask = (lane & 16) ? 0xffff0000u : 0x0000ffffu;
+#pragma unroll
+            for (int o2 = 8; o2 > 0; o2 >>= 1) sx += __shfl_xor_sync(half_mask, sx, o2);
+            if ((rl & 15) == 0) xsum[rl >> 4] = sx;
         }
-    }
-    __syncthreads();
-    // per (row m, chunk): sum of the staged operand values (hi + lo), 16 threads per sum, fixed order
-    for (int idx = tid; idx < p.M * chunks_cta * 16; idx += nthreads) {
-        const int task = idx >> 4, rr = idx & 15;
-        const int m = task / chunks_cta, cl = task - m * chunks_cta;
-        auto sum8 = [](const uint4 &o) {
-            const float2 a = __half22float2(u32_as_h2(o.x)), b = __half22float2(u32_as_h2(o.y));
-            const float2 cc = __half22float2(u32_as_h2(o.z)), d = __half22float2(u32_as_h2(o.w));
-            return ((a.x + a.y) + (b.x + b.y)) + ((cc.x + cc.y) + (d.x + d.y));
-        };
-        float sx = sum8(xs_hi[m * p.xs_stride + cl * 16 + rr]);
-        if constexpr (EXACT) sx += sum8(xs_lo[m * p.xs_stride + cl * 16 + rr]);
-        // 16 consecutive lanes share a sum; a half-warp is either wholly inside this loop or wholly outside
-        const unsigned half_mask = (lane & 16) ? 0xffff0000u : 0x0000ffffu;
+        __syncthreads();
+    } else {
+        // ---- fused rmsnorm: the row statistic over the whole of K (not only this CTA's slice), fixed summation order
+        if (p.prologue == kPrologueRmsNorm) {
+            const bool writer = p.x_out != nullptr && blockIdx.x == 0 && blockIdx.y == 0;
+            for (int m = 0; m < p.M; m++) {
+                const float *xr = (const float *)p.x + (int64_t)m * p.K;
+                float ss = 0.f;
+                for (int k = tid * 4; k < p.K; k += nthreads * 4) {
+                    float4 a = *reinterpret_cast<const float4 *>(xr + k);
+                    if (p.delta) {
+                        const float4 d = *reinterpret_cast<const float4 *>(p.delta + (int64_t)m * p.K + k);
+                        a.x += d.x, a.y += d.y, a.z += d.z, a.w += d.w;
+                        if (writer) *reinterpret_cast<float4 *>(p.x_out + (int64_t)m * p.K + k) = a;
+                    }
+                    ss = fmaf(a.x, a.x, ss), ss = fmaf(a.y, a.y, ss), ss = fmaf(a.z, a.z, ss), ss = fmaf(a.w, a.w, ss);
+                }
 #pragma unroll
-        for (int o = 8; o > 0; o >>= 1) sx += __shfl_xor_sync(half_mask, sx, o);
-        if (rr == 0) xsum[task] = sx;
+                for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+                if (lane == 0) pro_red[warp] = ss;
+                __syncthreads();
+                if (tid == 0) {
+                    float tsum = 0.f;
+                    for (int i = 0; i < (nthreads >> 5); i++) tsum += pro_red[i];
+                    pro_rstd[m] = rsqrtf(tsum / (float)p.K + p.eps);
+                }
+                __syncthreads();
+            }
+        }
+
+        // ---- stage this slice of the activations in the MMA's k-slot order: (x0,x4)(x2,x6)(x1,x5)(x3,x7) per packed
+        // row, zeros for the rows of a last partial chunk, plus the per-chunk sums used for the zero-point term ----
+        for (int rl = tid; rl < rows_pad; rl += nthreads) {
+            xs_hi[p.M * p.xs_stride + rl] = make_uint4(0, 0, 0, 0);
+            if constexpr (EXACT) xs_lo[p.M * p.xs_stride + rl] = make_uint4(0, 0, 0, 0);
+        }
+        for (int idx = tid; idx < p.M * rows_pad; idx += nthreads) {
+            const int m = idx / rows_pad, rl = idx - m * rows_pad;
+            const int64_t k0 = (int64_t)(row_begin + rl) * 8;
+            float v[8];
+            auto load8 = [&](const float *src) {
+                const float4 a = *reinterpret_cast<const float4 *>(src), b = *reinterpret_cast<const float4 *>(src + 4);
+                v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
+            };
+            if (rl >= rows_cta) {
+#pragma unroll
+                for (int j = 0; j < 8; j++) v[j] = 0.f;
+            } else if (p.prologue == kPrologueRmsNorm) {
+                load8((const float *)p.x + (int64_t)m * p.K + k0);
+                if (p.delta) {
+                    const float4 a = *reinterpret_cast<const float4 *>(p.delta + (int64_t)m * p.K + k0);
+                    const float4 b = *reinterpret_cast<const float4 *>(p.delta + (int64_t)m * p.K + k0 + 4);
+                    v[0] += a.x, v[1] += a.y, v[2] += a.z, v[3] += a.w, v[4] += b.x, v[5] += b.y, v[6] += b.z, v[7] += b.w;
+                }
+                const float rstd = pro_rstd[m];
+#pragma unroll
+                for (int j = 0; j < 8; j++) v[j] = v[j] * rstd * p.norm_w[k0 + j];
+            } else if (p.prologue == kPrologueSiluMul) {
+                float u[8];
+                load8(p.up + (int64_t)m * p.ld_x + k0);
+#pragma unroll
+                for (int j = 0; j < 8; j++) u[j] = v[j];
+                load8((const float *)p.x + (int64_t)m * p.ld_x + k0);
+#pragma unroll
+                for (int j = 0; j < 8; j++) v[j] = v[j] / (1.f + expf(-v[j])) * u[j];
+            } else if (p.x_f16) {
+                const uint4 raw = *reinterpret_cast<const uint4 *>((const __half *)p.x + (int64_t)m * p.K + k0);
+                const __half2 *h = reinterpret_cast<const __half2 *>(&raw);
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const float2 f = __half22float2(h[j]);
+                    v[2 * j] = f.x;
+                    v[2 * j + 1] = f.y;
+                }
+            } else {
+                load8((const float *)p.x + (int64_t)m * p.K + k0);
+            }
+            __half hi[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++) hi[j] = __float2half_rn(v[j]);
+            uint4 o;
+            o.x = h2_as_u32(__halves2half2(hi[0], hi[4]));
+            o.y = h2_as_u32(__halves2half2(hi[2], hi[6]));
+            o.z = h2_as_u32(__halves2half2(hi[1], hi[5]));
+            o.w = h2_as_u32(__halves2half2(hi[3], hi[7]));
+            xs_hi[m * p.xs_stride + rl] = o;
+            if constexpr (EXACT) {
+                __half lo[8];
+#pragma unroll
+                for (int j = 0; j < 8; j++) lo[j] = __float2half_rn(v[j] - __half2float(hi[j]));
+                o.x = h2_as_u32(__halves2half2(lo[0], lo[4]));
+                o.y = h2_as_u32(__halves2half2(lo[2], lo[6]));
+                o.z = h2_as_u32(__halves2half2(lo[1], lo[5]));
+                o.w = h2_as_u32(__halves2half2(lo[3], lo[7]));
+                xs_lo[m * p.xs_stride + rl] = o;
+            }
+        }
+        __syncthreads();
+        // per (row m, chunk): sum of the staged operand values (hi + lo), 16 threads per sum, fixed order
+        for (int idx = tid; idx < p.M * chunks_cta * 16; idx += nthreads) {
+            const int task = idx >> 4, rr = idx & 15;
+            const int m = task / chunks_cta, cl = task - m * chunks_cta;
+            auto sum8 = [](const uint4 &o) {
+                const float2 a = __half22float2(u32_as_h2(o.x)), b = __half22float2(u32_as_h2(o.y));
+                const float2 cc = __half22float2(u32_as_h2(o.z)), d = __half22float2(u32_as_h2(o.w));
+                return ((a.x + a.y) + (b.x + b.y)) + ((cc.x + cc.y) + (d.x + d.y));
+            };
+            float sx = sum8(xs_hi[m * p.xs_stride + cl * 16 + rr]);
+            if constexpr (EXACT) sx += sum8(xs_lo[m * p.xs_stride + cl * 16 + rr]);
+            // 16 consecutive lanes share a sum; a half-warp is either wholly inside this loop or wholly outside
+            const unsigned half_mask = (lane & 16) ? 0xffff0000u : 0x0000ffffu;
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) sx += __shfl_xor_sync(half_mask, sx, o);
+            if (rr == 0) xsum[task] = sx;
+        }
+        __syncthreads();
     }
-    __syncthreads();
+    GT(3);
     // ---- main loop over this CTA's column tiles ----
     float *red = reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(smem_u4) + p.red_off);  // [wk][wn][MB*8][32]
     __shared__ int is_last;
@@ -244,6 +373,7 @@ __global__ void __launch_bounds__(MB == 1 ? 256 : 512, MB == 1 ? 3 : 1) gptq_gem
             request(slot_req);
             slot_req = slot_req + 1 == p.stages ? 0 : slot_req + 1;
             cp_async_wait(p.stages - 1);  // everything but the newest stages - 1 groups has landed
+            if (tj == 0 && i == 0) GT(4);
             ChunkRegs ra;
             read_slot(ring + slot_use * stage_stride, c, ra);
             slot_use = slot_use + 1 == p.stages ? 0 : slot_use + 1;
@@ -251,6 +381,7 @@ __global__ void __launch_bounds__(MB == 1 ? 256 : 512, MB == 1 ? 3 : 1) gptq_gem
             const int rl0 = chunk * 16 + t - row_begin;
             compute_chunk<MB, EXACT>(p, ra, rl0, g, t, xs_hi, xs_lo, xsum, chunk - ch_begin, chunks_cta, tot);
         }
+        if (tj == 0) GT(5);
         // reduce over the wk warps that share the column tile (fixed order), then write / split-K
 #pragma unroll
         for (int mb = 0; mb < MB; mb++)
@@ -304,6 +435,7 @@ __global__ void __launch_bounds__(MB == 1 ? 256 : 512, MB == 1 ? 3 : 1) gptq_gem
         __syncthreads();  // red and is_last are reused by the next tile
     }
     cp_async_wait(0);
+    GT(6);
 }
 
 // =====================================================================================================
@@ -483,13 +615,16 @@ static int gemv_grid_x(int sm_count, int ctas_n, int S, int block, size_t smem)
     return (ctas_n + waves - 1) / waves;
 }
 
-// Ring depth: 3 chunks ahead keeps ~3 x 64 bytes per thread in flight; fewer when a warp has fewer chunks or
-// when the activations leave no room.
+// Ring depth. `stages - 1` chunks are requested BEFORE the activations are staged (and before the wait on the
+// previous kernel), so the depth must exceed 1 even when a warp has a single chunk: otherwise the first weight
+// request is issued after the staging and its whole HBM latency lands on the critical path. A warp with one
+// or two chunks gets all of them in flight up front; longer loops keep two slots (shared memory is what limits
+// the resident CTAs of the large shapes).
 static int gemv_pick_stages(int64_t M, int cps, bool two_halves, int wn, int wk)
 {
-    int stages = (cps + wk - 1) / wk;
-    if (stages > 2) stages = 2;
-    if (stages < 1) stages = 1;
+    const int per_warp = (cps + wk - 1) / wk;
+    int stages = per_warp <= 2 ? per_warp + 1 : 2;
+    if (stages < 2) stages = 2;
     while (stages > 1 && gemv_smem_bytes(M, cps, two_halves, wn, wk, stages, nullptr) > (size_t)kGemvSmemLimit) stages--;
     return stages;
 }

@@ -108,7 +108,7 @@ int forward_impl(wb_qwen *m, const Bufs &b, int64_t M, int64_t B, int64_t T, int
     // embedding + cache append ride inside the projections and the attention kernel (see GemvPrologue).
     const LayerW &L0 = m->layers[0];
     const bool fused_step = M == 1 && use_cache && L0.qkv >= 0 && L0.gate_up >= 0 && D % 8 == 0 && D <= 128 &&
-                            (size_t)(7 * D + m->cfg.max_t / 8 + 1) * 4 <= 48 * 1024 &&
+                            op_attention_decode_smem(D, m->cfg.max_t, kv16) <= 160 * 1024 &&
                             linear_fusion_supported(ctx, ctx->weights[L0.qkv], 1) &&
                             linear_fusion_supported(ctx, ctx->weights[L0.gate_up], 1) &&
                             linear_fusion_supported(ctx, ctx->weights[L0.down], 1);
@@ -151,7 +151,7 @@ int forward_impl(wb_qwen *m, const Bufs &b, int64_t M, int64_t B, int64_t T, int
                             b.ldq, b.ldk, b.ldv));
         if (use_cache) {
             const int max_keys = past_ptr ? m->cfg.max_t : (int)(past + M);
-            if (M == 1 && D % 8 == 0 && D <= 128 && (size_t)(7 * D + max_keys / 8 + 1) * 4 <= 48 * 1024) {
+            if (M == 1 && D % 8 == 0 && D <= 128 && op_attention_decode_smem(D, max_keys, kv16) <= 160 * 1024) {
                 WB_CHECK(op_attention_decode(ctx, b.q, kc, vc, kv16, b.att, m->att_scratch, m->att_counters, H, KVH, D, past_ptr,
                                              (int)past, max_keys, KV));
             } else

@@ -226,10 +226,22 @@ __device__ __forceinline__ float dot_row<float>(const float *qs, const float *kp
     return dot;
 }
 
+// Decode attention: one query row against the KV cache, the keys of each head split over ATT_SPLITS CTAs (online
+// softmax per split, the last split to arrive merges). The kernel is a chain of dependent memory round trips, so the
+// order of its loads is the design: q (and the raw k, v) are requested before the position is known; as soon as it
+// is, the split's V rows start moving into shared memory (cp.async) and its K rows into registers, and they arrive
+// while the scores and the softmax are computed; the merge issues all of its loads before it uses any.
+//
 // With k_raw != nullptr the kernel also does the work of rope_half.wgsl + kv_store.wgsl for the new position
 // (ropeHalfRef, src/reference/qwen-ref.ts:35-64): q, k_raw, v_raw are the projection outputs; q is rotated while it is
 // staged; the split that owns the newest key rotates k itself (rounded to the cache type, as a later step will read
 // it) instead of reading the cache row, and the first head of each KV group stores k and v to the cache.
+__device__ __forceinline__ void att_cp_async_16(void *dst_smem, const void *src)
+{
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst_smem)), "l"(src)
+                 : "memory");
+}
+
 template <typename KV>
 __global__ void __launch_bounds__(128) attention_decode_kernel(const float *__restrict__ q, KV *__restrict__ kmem,
                                                                KV *__restrict__ vmem, float *__restrict__ out,
@@ -237,34 +249,56 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const float *__re
                                                                int H, int KVH, int D, const int *__restrict__ past_ptr,
                                                                int past_imm, int kv_ld, float scale,
                                                                const float *__restrict__ k_raw, const float *__restrict__ v_raw,
-                                                               const float *__restrict__ cs_table)
+                                                               const float *__restrict__ cs_table, int chunk_max)
 {
     pdl_sync();
-    extern __shared__ float sm[];  // [D] query (pre-scaled), [2][D] new k, v (16-byte aligned: read as float4), [chunk] scores, [4][D] per-warp value sums
+    // [D] query (pre-scaled), [2][D] new k, v, [chunk] scores, [4][D] per-warp value sums, then (16-byte aligned)
+    // the split's V rows [chunk_max][D] in the cache type
+    extern __shared__ float sm[];
     __shared__ float red[4];
     __shared__ int is_last;
     const int h = blockIdx.x, s = blockIdx.y, kvh = h / (H / KVH);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int half = D >> 1;  // D <= 128: one (i, i + half) pair per thread
+    const bool fused = k_raw != nullptr;
+    float q0 = 0.f, q1 = 0.f, x0 = 0.f, x1 = 0.f, v0f = 0.f, v1f = 0.f;
+    if (tid < half) {
+        q0 = q[h * D + tid], q1 = q[h * D + tid + half];
+        if (fused) {
+            x0 = k_raw[kvh * D + tid], x1 = k_raw[kvh * D + tid + half];
+            v0f = v_raw[kvh * D + tid], v1f = v_raw[kvh * D + tid + half];
+        }
+    }
     const int pos = past_ptr ? *past_ptr : past_imm;
     const int n_keys = pos + 1;
     const int chunk = (n_keys + ATT_SPLITS - 1) / ATT_SPLITS;
     const int k0 = s * chunk, k1 = min(n_keys, k0 + chunk), nk = max(0, k1 - k0);
-    float *qs = sm, *knew = sm + D, *vnew = sm + 2 * D, *sc = sm + 3 * D, *wacc = sc + chunk;
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const bool fused = k_raw != nullptr;
+    float *qs = sm, *knew = sm + D, *vnew = sm + 2 * D, *sc = sm + 3 * D, *wacc = sc + chunk_max;
+    KV *vt = reinterpret_cast<KV *>(sm + ((7 * D + chunk_max + 3) & ~3));
     const bool own_new = fused && k1 == n_keys && nk > 0;  // this split holds the newest key
-    if (!fused) {
-        for (int d = tid; d < D; d += blockDim.x) qs[d] = q[h * D + d] * scale;
-    } else {
-        const int half = D >> 1;
-        for (int i = tid; i < half; i += blockDim.x) {
+    const int nk_mem = own_new ? nk - 1 : nk;               // keys of this split that are read from memory
+
+    // V rows of this split -> shared memory, in flight from here on
+    {
+        const int per_row = D * (int)sizeof(KV) / 16;  // 16-byte pieces per row
+        for (int i = tid; i < nk_mem * per_row; i += blockDim.x) {
+            const int j = i / per_row, c = i - j * per_row;
+            att_cp_async_16(reinterpret_cast<char *>(vt + (size_t)j * D) + c * 16,
+                            reinterpret_cast<const char *>(vmem + (int64_t)(k0 + j) * kv_ld + kvh * D) + c * 16);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    if (tid < half) {
+        if (!fused) {
+            qs[tid] = q0 * scale, qs[tid + half] = q1 * scale;
+        } else {
+            const int i = tid;
             const float c = cs_table[((int64_t)pos * half + i) * 2], sn = cs_table[((int64_t)pos * half + i) * 2 + 1];
-            const float q0 = q[h * D + i], q1 = q[h * D + i + half];
             qs[i] = (q0 * c - q1 * sn) * scale;
             qs[i + half] = (q0 * sn + q1 * c) * scale;
             if (own_new) {
-                const float x0 = k_raw[kvh * D + i], x1 = k_raw[kvh * D + i + half];
                 const KV r0 = (KV)(x0 * c - x1 * sn), r1 = (KV)(x0 * sn + x1 * c);
-                const KV v0 = (KV)v_raw[kvh * D + i], v1 = (KV)v_raw[kvh * D + i + half];
+                const KV v0 = (KV)v0f, v1 = (KV)v1f;
                 knew[i] = (float)r0, knew[i + half] = (float)r1, vnew[i] = (float)v0, vnew[i + half] = (float)v1;
                 if (h == kvh * (H / KVH)) {
                     KV *kd = kmem + (int64_t)pos * kv_ld + kvh * D, *vd = vmem + (int64_t)pos * kv_ld + kvh * D;
@@ -274,7 +308,6 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const float *__re
         }
     }
     __syncthreads();
-    const int nk_mem = own_new ? nk - 1 : nk;  // keys of this split that are read from memory
 
     float lmax = -INFINITY;
     for (int j = tid; j < nk_mem; j += blockDim.x) {
@@ -299,14 +332,15 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const float *__re
         sc[j] = e;
         lsum += e;
     }
-    const float total = block_sum(lsum, red);  // also orders the sc[] writes before the reads below
+    asm volatile("cp.async.wait_group 0;" ::: "memory");  // this thread's V pieces; the barrier below covers the others'
+    const float total = block_sum(lsum, red);  // also orders the sc[] and V-tile writes before the reads below
     // weighted values: warp w takes keys w, w+4, ...; lane owns dims 2*lane, 2*lane+1 (and +64 for D = 128)
     for (int d0 = 0; d0 < D; d0 += 64) {
         float a0 = 0.f, a1 = 0.f;
         const int d = d0 + 2 * lane;
         if (d < D) {
             for (int j = warp; j < nk_mem; j += 4) {
-                const KV *vp = vmem + (int64_t)(k0 + j) * kv_ld + kvh * D + d;
+                const KV *vp = vt + (size_t)j * D + d;
                 a0 = fmaf(sc[j], kv_load(vp), a0);
                 a1 = fmaf(sc[j], kv_load(vp + 1), a1);
             }
@@ -324,20 +358,25 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const float *__re
     __syncthreads();
     if (!is_last) return;
     __threadfence();
+    // merge: every load is issued before the first use (one L2 round trip instead of three)
     const float *base = scratch + (int64_t)h * ATT_SPLITS * (D + 2);
-    float M = -INFINITY;
-    for (int i = 0; i < ATT_SPLITS; i++) M = fmaxf(M, __ldcg(base + i * (D + 2)));
-    float Lsum = 0.f;
-    for (int i = 0; i < ATT_SPLITS; i++) {
-        const float mi = __ldcg(base + i * (D + 2)), li = __ldcg(base + i * (D + 2) + 1);
-        if (li > 0.f) Lsum += li * expf(mi - M);
-    }
     for (int d = tid; d < D; d += blockDim.x) {
-        float acc = 0.f;
+        float mi[ATT_SPLITS], li[ATT_SPLITS], av[ATT_SPLITS];
+#pragma unroll
         for (int i = 0; i < ATT_SPLITS; i++) {
-            const float mi = __ldcg(base + i * (D + 2)), li = __ldcg(base + i * (D + 2) + 1);
-            if (li > 0.f) acc = fmaf(__ldcg(base + i * (D + 2) + 2 + d), expf(mi - M), acc);
+            mi[i] = __ldcg(base + i * (D + 2)), li[i] = __ldcg(base + i * (D + 2) + 1);
+            av[i] = __ldcg(base + i * (D + 2) + 2 + d);
         }
+        float M = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < ATT_SPLITS; i++) M = fmaxf(M, mi[i]);
+        float Lsum = 0.f, acc = 0.f;
+#pragma unroll
+        for (int i = 0; i < ATT_SPLITS; i++)
+            if (li[i] > 0.f) Lsum += li[i] * expf(mi[i] - M);
+#pragma unroll
+        for (int i = 0; i < ATT_SPLITS; i++)
+            if (li[i] > 0.f) acc = fmaf(av[i], expf(mi[i] - M), acc);
         out[h * D + d] = acc / Lsum;
     }
     if (tid == 0) counters[h] = 0u;
@@ -475,20 +514,29 @@ int op_attention(wb_context *ctx, const float *q, const void *kmem, const void *
     LAUNCH_OK(ctx);
 }
 
+size_t op_attention_decode_smem(int D, int max_keys, int kv_f16)
+{
+    const int chunk = (max_keys + ATT_SPLITS - 1) / ATT_SPLITS;
+    return (size_t)((7 * D + chunk + 3) & ~3) * sizeof(float) + (size_t)chunk * D * (kv_f16 ? 2 : 4);
+}
+
 int op_attention_decode(wb_context *ctx, const float *q, void *kmem, void *vmem, int kv_f16, float *out, float *scratch,
                         unsigned *counters, int H, int KVH, int D, const int *past_ptr, int past_imm, int max_keys, int kv_ld,
                         const float *k_raw, const float *v_raw, const float *cs_table)
 {
     const int chunk = (max_keys + ATT_SPLITS - 1) / ATT_SPLITS;
-    const size_t smem = (size_t)(7 * D + chunk) * sizeof(float);
+    const size_t smem = op_attention_decode_smem(D, max_keys, kv_f16);
     const float scale = 1.0f / sqrtf((float)D);
     dim3 grid(H, ATT_SPLITS);
-    if (kv_f16)
+    if (kv_f16) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(attention_decode_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         WB_CUDA(launch_pdl(attention_decode_kernel<__half>, grid, dim3(128), smem, ctx->stream, q, (__half *)kmem, (__half *)vmem, out,
-                           scratch, counters, H, KVH, D, past_ptr, past_imm, kv_ld, scale, k_raw, v_raw, cs_table));
-    else
+                           scratch, counters, H, KVH, D, past_ptr, past_imm, kv_ld, scale, k_raw, v_raw, cs_table, chunk));
+    } else {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(attention_decode_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         WB_CUDA(launch_pdl(attention_decode_kernel<float>, grid, dim3(128), smem, ctx->stream, q, (float *)kmem, (float *)vmem, out,
-                           scratch, counters, H, KVH, D, past_ptr, past_imm, kv_ld, scale, k_raw, v_raw, cs_table));
+                           scratch, counters, H, KVH, D, past_ptr, past_imm, kv_ld, scale, k_raw, v_raw, cs_table, chunk));
+    }
     LAUNCH_OK(ctx);
 }
 

@@ -24,6 +24,8 @@ int op_attention_decode(wb_context *ctx, const float *q, void *kmem, void *vmem,
                         unsigned *counters, int H, int KVH, int D, const int *past_ptr, int past_imm, int max_keys, int kv_ld,
                         const float *k_raw = nullptr, const float *v_raw = nullptr, const float *cs_table = nullptr);
 int op_attention_decode_scratch_floats(int H, int D);
+// Dynamic shared memory of the decode attention kernel for up to max_keys keys (it stages a split's V rows).
+size_t op_attention_decode_smem(int D, int max_keys, int kv_f16);
 int op_argmax(wb_context *ctx, const float *logits, int V, float *bval, int *bidx, uint32_t *token_out, uint32_t *history,
               int *step_counter, int *cache_len);
 
