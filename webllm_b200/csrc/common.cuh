@@ -157,17 +157,58 @@ inline bool pdl_enabled()
     return on;
 }
 
+// `cluster_y` > 1 launches thread-block clusters of (1, cluster_y, 1) CTAs (grid.y must be a multiple of it).
 template <typename... P, typename... A>
-inline cudaError_t launch_pdl(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, A &&...args)
+inline cudaError_t launch_pdl_cluster(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                      unsigned cluster_y, A &&...args)
 {
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = grid, cfg.blockDim = block, cfg.dynamicSmemBytes = smem, cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute attr[2];
+    unsigned n = 0;
+    if (pdl_enabled()) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        n++;
+    }
+    if (cluster_y > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = 1, attr[n].val.clusterDim.y = cluster_y, attr[n].val.clusterDim.z = 1;
+        n++;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    cfg.numAttrs = n;
     return cudaLaunchKernelEx(&cfg, kernel, P(args)...);
+}
+
+template <typename... P, typename... A>
+inline cudaError_t launch_pdl(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, A &&...args)
+{
+    return launch_pdl_cluster(kernel, grid, block, smem, stream, 1u, static_cast<A &&>(args)...);
+}
+
+// ---- thread-block clusters: distributed shared memory and the cluster barrier --------------------------------
+__device__ __forceinline__ uint32_t cluster_cta_rank()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// Address of `smem_ptr` (a pointer into this CTA's shared memory) in the shared memory of CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t cluster_map_shared(const void *smem_ptr, uint32_t rank)
+{
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"((uint32_t)__cvta_generic_to_shared(smem_ptr)), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_store_f32(uint32_t addr, float v)
+{
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+// Every thread of every CTA of the cluster must reach this; stores made before it (also remote ones) are visible after.
+__device__ __forceinline__ void cluster_barrier()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
 #endif  // __CUDACC__

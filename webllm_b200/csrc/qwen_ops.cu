@@ -252,11 +252,10 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const float *__re
                                                                const float *__restrict__ cs_table, int chunk_max)
 {
     pdl_sync();
-    // [D] query (pre-scaled), [2][D] new k, v, [chunk] scores, [4][D] per-warp value sums, then (16-byte aligned)
-    // the split's V rows [chunk_max][D] in the cache type
+    // [D] query (pre-scaled), [2][D] new k, v, [chunk] scores, [4][D] per-warp value sums, [ATT_SPLITS][D + 2] merge slots
+    // (written by the other CTAs of the cluster), then (16-byte aligned) the split's V rows [chunk_max][D] in the cache type
     extern __shared__ float sm[];
     __shared__ float red[4];
-    __shared__ int is_last;
     const int h = blockIdx.x, s = blockIdx.y, kvh = h / (H / KVH);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int half = D >> 1;  // D <= 128: one (i, i + half) pair per thread
@@ -273,8 +272,8 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const float *__re
     const int n_keys = pos + 1;
     const int chunk = (n_keys + ATT_SPLITS - 1) / ATT_SPLITS;
     const int k0 = s * chunk, k1 = min(n_keys, k0 + chunk), nk = max(0, k1 - k0);
-    float *qs = sm, *knew = sm + D, *vnew = sm + 2 * D, *sc = sm + 3 * D, *wacc = sc + chunk_max;
-    KV *vt = reinterpret_cast<KV *>(sm + ((7 * D + chunk_max + 3) & ~3));
+    float *qs = sm, *knew = sm + D, *vnew = sm + 2 * D, *sc = sm + 3 * D, *wacc = sc + chunk_max, *merge = wacc + 4 * D;
+    KV *vt = reinterpret_cast<KV *>(sm + ((7 * D + chunk_max + ATT_SPLITS * (D + 2) + 3) & ~3));
     const bool own_new = fused && k1 == n_keys && nk > 0;  // this split holds the newest key
     const int nk_mem = own_new ? nk - 1 : nk;               // keys of this split that are read from memory
 
@@ -349,37 +348,34 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const float *__re
         if (d < D) wacc[warp * D + d] = a0, wacc[warp * D + d + 1] = a1;
     }
     __syncthreads();
-    float *slot = scratch + ((int64_t)h * ATT_SPLITS + s) * (D + 2);
-    for (int d = tid; d < D; d += blockDim.x) slot[2 + d] = wacc[d] + wacc[D + d] + wacc[2 * D + d] + wacc[3 * D + d];
-    if (tid == 0) slot[0] = mx, slot[1] = total;
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) is_last = (atomicAdd(&counters[h], 1u) == (unsigned)(ATT_SPLITS - 1));
-    __syncthreads();
-    if (!is_last) return;
-    __threadfence();
-    // merge: every load is issued before the first use (one L2 round trip instead of three)
-    const float *base = scratch + (int64_t)h * ATT_SPLITS * (D + 2);
+    // The ATT_SPLITS CTAs of a head form one cluster: each stores its (max, sum, weighted values) into the shared memory
+    // of the cluster's first CTA, and after the cluster barrier that CTA merges them in split order. No global scratch,
+    // no fence, no atomic, and nothing depends on which CTA finishes last.
+    {
+        const uint32_t dst = cluster_map_shared(merge + (size_t)s * (D + 2), 0);
+        for (int d = tid; d < D; d += blockDim.x)
+            cluster_store_f32(dst + (2 + d) * 4, wacc[d] + wacc[D + d] + wacc[2 * D + d] + wacc[3 * D + d]);
+        if (tid == 0) cluster_store_f32(dst, mx), cluster_store_f32(dst + 4, total);
+    }
+    cluster_barrier();
+    if (s != 0) return;
     for (int d = tid; d < D; d += blockDim.x) {
-        float mi[ATT_SPLITS], li[ATT_SPLITS], av[ATT_SPLITS];
-#pragma unroll
-        for (int i = 0; i < ATT_SPLITS; i++) {
-            mi[i] = __ldcg(base + i * (D + 2)), li[i] = __ldcg(base + i * (D + 2) + 1);
-            av[i] = __ldcg(base + i * (D + 2) + 2 + d);
-        }
         float M = -INFINITY;
 #pragma unroll
-        for (int i = 0; i < ATT_SPLITS; i++) M = fmaxf(M, mi[i]);
+        for (int i = 0; i < ATT_SPLITS; i++) M = fmaxf(M, merge[i * (D + 2)]);
         float Lsum = 0.f, acc = 0.f;
 #pragma unroll
-        for (int i = 0; i < ATT_SPLITS; i++)
-            if (li[i] > 0.f) Lsum += li[i] * expf(mi[i] - M);
+        for (int i = 0; i < ATT_SPLITS; i++) {
+            const float li = merge[i * (D + 2) + 1];
+            if (li > 0.f) Lsum += li * expf(merge[i * (D + 2)] - M);
+        }
 #pragma unroll
-        for (int i = 0; i < ATT_SPLITS; i++)
-            if (li[i] > 0.f) acc = fmaf(av[i], expf(mi[i] - M), acc);
+        for (int i = 0; i < ATT_SPLITS; i++) {
+            const float li = merge[i * (D + 2) + 1];
+            if (li > 0.f) acc = fmaf(merge[i * (D + 2) + 2 + d], expf(merge[i * (D + 2)] - M), acc);
+        }
         out[h * D + d] = acc / Lsum;
     }
-    if (tid == 0) counters[h] = 0u;
 }
 
 // Greedy sampling (sampleToken with temperature <= 0, src/infer/sampler.ts:30-36): index of the first
@@ -517,7 +513,7 @@ int op_attention(wb_context *ctx, const float *q, const void *kmem, const void *
 size_t op_attention_decode_smem(int D, int max_keys, int kv_f16)
 {
     const int chunk = (max_keys + ATT_SPLITS - 1) / ATT_SPLITS;
-    return (size_t)((7 * D + chunk + 3) & ~3) * sizeof(float) + (size_t)chunk * D * (kv_f16 ? 2 : 4);
+    return (size_t)((7 * D + chunk + ATT_SPLITS * (D + 2) + 3) & ~3) * sizeof(float) + (size_t)chunk * D * (kv_f16 ? 2 : 4);
 }
 
 int op_attention_decode(wb_context *ctx, const float *q, void *kmem, void *vmem, int kv_f16, float *out, float *scratch,
@@ -530,11 +526,11 @@ int op_attention_decode(wb_context *ctx, const float *q, void *kmem, void *vmem,
     dim3 grid(H, ATT_SPLITS);
     if (kv_f16) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(attention_decode_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        WB_CUDA(launch_pdl(attention_decode_kernel<__half>, grid, dim3(128), smem, ctx->stream, q, (__half *)kmem, (__half *)vmem, out,
+        WB_CUDA(launch_pdl_cluster(attention_decode_kernel<__half>, grid, dim3(128), smem, ctx->stream, ATT_SPLITS, q, (__half *)kmem, (__half *)vmem, out,
                            scratch, counters, H, KVH, D, past_ptr, past_imm, kv_ld, scale, k_raw, v_raw, cs_table, chunk));
     } else {
         if (smem > 48 * 1024) cudaFuncSetAttribute(attention_decode_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        WB_CUDA(launch_pdl(attention_decode_kernel<float>, grid, dim3(128), smem, ctx->stream, q, (float *)kmem, (float *)vmem, out,
+        WB_CUDA(launch_pdl_cluster(attention_decode_kernel<float>, grid, dim3(128), smem, ctx->stream, ATT_SPLITS, q, (float *)kmem, (float *)vmem, out,
                            scratch, counters, H, KVH, D, past_ptr, past_imm, kv_ld, scale, k_raw, v_raw, cs_table, chunk));
     }
     LAUNCH_OK(ctx);
