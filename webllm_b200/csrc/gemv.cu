@@ -358,6 +358,8 @@ __global__ void __launch_bounds__(MB == 1 ? 256 : 512, MB == 1 ? 3 : 1) gptq_gem
     constexpr int J = MB * 8;
     const int tile_cols = p.wn * 32;
     const bool direct = p.S == 1;
+    float *cl_part = reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(smem_u4) + p.cl_off);  // [S][M * tile_cols]
+    const uint32_t cl_dst = p.cluster ? cluster_map_shared(cl_part + (size_t)blockIdx.y * p.M * p.wn * 32, 0) : 0u;
     int slot_use = 0, slot_req = p.stages - 1;
     for (int tj = 0; tj < tiles_cta; tj++) {
         const int tile = (int)blockIdx.x + tj * (int)gridDim.x;
@@ -407,11 +409,31 @@ __global__ void __launch_bounds__(MB == 1 ? 256 : 512, MB == 1 ? 3 : 1) gptq_gem
                 if (p.bias) v += p.bias[n];
                 if (p.out_f16) ((__half *)p.out)[(int64_t)m * p.N + n] = __float2half_rn(v);
                 else ((float *)p.out)[(int64_t)m * p.N + n] = v;
+            } else if (p.cluster) {
+                cluster_store_f32(cl_dst + (uint32_t)idx * 4u, v);
             } else {
                 p.partial[((int64_t)blockIdx.y * p.M + m) * p.N + n] = v;
             }
         }
-        if (!direct) {
+        if (!direct && p.cluster) {
+            // The S slices of this column tile are the CTAs of one cluster: each has just stored its partial tile into
+            // the first CTA's shared memory; after the cluster barrier that CTA adds them in slice order and the bias
+            // once. No workspace, fence or atomic, and the result does not depend on scheduling.
+            cluster_barrier();
+            if (blockIdx.y == 0) {
+                for (int idx = tid; idx < outputs; idx += nthreads) {
+                    const int m = idx / tile_cols;
+                    const int n = n_base + (idx - m * tile_cols);
+                    if (n >= p.N) continue;
+                    float v = 0.f;
+                    for (int sl = 0; sl < p.S; sl++) v += cl_part[sl * outputs + idx];
+                    if (p.bias) v += p.bias[n];
+                    if (p.out_f16) ((__half *)p.out)[(int64_t)m * p.N + n] = __float2half_rn(v);
+                    else ((float *)p.out)[(int64_t)m * p.N + n] = v;
+                }
+            }
+            if (tj + 1 < tiles_cta) cluster_barrier();  // the buffer is rewritten by the next tile
+        } else if (!direct) {
             // the last slice to arrive for this tile adds the slices in slice order and the bias once
             __threadfence();
             __syncthreads();
@@ -588,7 +610,7 @@ constexpr int kGemvSmemLimit = 200 * 1024;
 // activations; plus the per-chunk sums otherwise), then the cp.async ring (80 bytes per thread per stage).
 // The cross-warp reduction reuses the front of the buffer. Returns the total; 0 stages = size without a ring.
 static size_t gemv_smem_bytes(int64_t M, int cps, bool two_halves, int wn, int wk, int stages, int *ring_off,
-                              int *red_off = nullptr)
+                              int *red_off = nullptr, int cluster_slices = 0, int *cl_off = nullptr)
 {
     const int MB = M <= 8 ? 1 : (M <= 16 ? 2 : 4);
     size_t xs = (size_t)(M + 1) * (cps * 16 + 4) * 16 * (two_halves ? 2 : 1) + (size_t)M * cps * 4;
@@ -597,7 +619,8 @@ static size_t gemv_smem_bytes(int64_t M, int cps, bool two_halves, int wn, int w
     const size_t red = (size_t)wn * wk * MB * 8 * 32 * 4;
     if (ring_off) *ring_off = (int)xs;
     if (red_off) *red_off = (int)(xs + ring);
-    return xs + ring + red;
+    if (cl_off) *cl_off = (int)(xs + ring + red);
+    return xs + ring + red + (size_t)cluster_slices * M * wn * 32 * 4;
 }
 
 // Grid width: as many column tiles as are resident at once, evened out so that every CTA gets the same number
@@ -629,6 +652,10 @@ static int gemv_pick_stages(int64_t M, int cps, bool two_halves, int wn, int wk)
     return stages;
 }
 
+// Split-K slices of one column tile run as a thread-block cluster (and merge through its shared memory) when the
+// cluster is portable (<= 8 CTAs) and the merge buffer is small; otherwise through the workspace and arrival counters.
+static bool gemv_cluster_merge(int64_t M, int S) { return S > 1 && S <= 8 && M <= 8; }
+
 static void plan_gemv_mma(wb_context *ctx, const Weight &w, int64_t M, int two_halves, wb_plan *plan)
 {
     const int chunks = (int)((w.pack_rows + 15) / 16);
@@ -641,7 +668,13 @@ static void plan_gemv_mma(wb_context *ctx, const Weight &w, int64_t M, int two_h
     const int target = 2 * ctx->sm_count;
     int S = 1;
     const int per_warp = (chunks + wk - 1) / wk;
-    if (ctas_n < target && per_warp > 2) {
+    if (M <= 8 && ctas_n < target && per_warp > 1) {
+        // decode sizes: the slices of a tile merge through cluster shared memory (cheap), so K is split until a warp
+        // holds a single chunk, as far as that fills the GPU and a portable cluster (8 CTAs) allows
+        const int by_fill = (target + ctas_n - 1) / ctas_n;
+        S = per_warp < by_fill ? per_warp : by_fill;
+        if (S > 8) S = 8;
+    } else if (ctas_n < target && per_warp > 2) {
         const int by_work = (per_warp + 1) / 2;
         const int by_fill = (target + ctas_n - 1) / ctas_n;
         S = by_work < by_fill ? by_work : by_fill;
@@ -715,12 +748,13 @@ constexpr uint64_t kPrefetchLimit = 32ull << 20;
 template <int MB>
 static cudaError_t launch_gemv_mb(const GemvParams &p, dim3 grid, int block, size_t smem, bool exact, cudaStream_t st)
 {
+    const unsigned cl = p.cluster ? (unsigned)p.S : 1u;
     if (exact) {
         cudaFuncSetAttribute(gptq_gemv_mma_kernel<MB, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemvSmemLimit);
-        return launch_pdl(gptq_gemv_mma_kernel<MB, true>, grid, dim3(block), smem, st, p);
+        return launch_pdl_cluster(gptq_gemv_mma_kernel<MB, true>, grid, dim3(block), smem, st, cl, p);
     } else {
         cudaFuncSetAttribute(gptq_gemv_mma_kernel<MB, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemvSmemLimit);
-        return launch_pdl(gptq_gemv_mma_kernel<MB, false>, grid, dim3(block), smem, st, p);
+        return launch_pdl_cluster(gptq_gemv_mma_kernel<MB, false>, grid, dim3(block), smem, st, cl, p);
     }
 }
 
@@ -778,7 +812,9 @@ int launch_linear(wb_context *ctx, const Weight &w, const void *A, void *C, cons
         ctx->prefetch_weight = -1;
         const int MB = M <= 8 ? 1 : (M <= 16 ? 2 : 4);
         p.stages = gemv_pick_stages(M, p.chunks_per_split, ex_gemv, p.wn, p.wk);
-        const size_t smem = gemv_smem_bytes(M, p.chunks_per_split, ex_gemv, p.wn, p.wk, p.stages, &p.ring_off, &p.red_off);
+        p.cluster = gemv_cluster_merge(M, p.S) ? 1 : 0;
+        const size_t smem = gemv_smem_bytes(M, p.chunks_per_split, ex_gemv, p.wn, p.wk, p.stages, &p.ring_off, &p.red_off,
+                                            p.cluster ? p.S : 0, &p.cl_off);
         if (smem > (size_t)kGemvSmemLimit) return fail(WB_ERR_UNSUPPORTED, "GEMV_MMA: activations do not fit shared memory");
         // plan.grid_x counts column tiles; the launch covers them with one evenly loaded wave of CTAs
         dim3 grid(gemv_grid_x(ctx->sm_count, plan.grid_x, plan.grid_y, plan.block, smem), plan.grid_y);
@@ -920,7 +956,7 @@ extern "C" int wb_gptq_gemv_static(const void *qweight, const void *qzeros, cons
     p.M = (int)M, p.N = (int)N, p.K = (int)K, p.pack_rows = pack_rows, p.zcols = (int)((N + 7) / 8);
     p.chunks = chunks, p.chunks_per_split = cps, p.group_chunks = (int)(group_size / 128), p.S = S;
     p.wn = wn, p.wk = wk, p.x_f16 = act_dtype == WB_F16, p.out_f16 = out_dtype == WB_F16, p.xs_stride = xs_stride;
-    p.stages = stages, p.ring_off = ring_off, p.red_off = red_off;
+    p.stages = stages, p.ring_off = ring_off, p.red_off = red_off, p.cluster = 0, p.cl_off = 0;
     p.pf_ptr = nullptr, p.pf_bytes = 0;
     p.prologue = kPrologueNone, p.delta = nullptr, p.x_out = nullptr, p.norm_w = nullptr, p.eps = 0.f, p.up = nullptr, p.ld_x = (int)K;
     int sms = 148;

@@ -31,6 +31,8 @@ struct GemvParams {
     int stages;         // depth of the per-thread cp.async ring
     int ring_off;       // byte offset of the ring in dynamic shared memory
     int red_off;        // byte offset of the cross-warp reduction buffer
+    int cluster;        // 1: the S slices of a column tile are one thread-block cluster and merge through its shared memory
+    int cl_off;         // byte offset of the [S][M * tile columns] merge buffer (used in the cluster's first CTA)
     const char *pf_ptr;   // weight of a later call to pull into L2 while this one runs (nullable)
     unsigned pf_bytes;    // multiple of 16
     // Optional work fused in front of the projection (f32 activations, M <= 8); see GemvPrologue.
