@@ -125,12 +125,22 @@ __device__ __forceinline__ unsigned short f32_to_f16_bits_ref(float f)
     return h;
 }
 
+// Weights are read once per token and are far larger than the L2 (458 MB per decode step against 126 MB): they are
+// loaded with an evict-first L2 policy so that they do not push out what IS reused between kernels and steps
+// (activations, the KV cache, the rotary table, norm weights), which then stays an L2 hit.
+__device__ __forceinline__ uint64_t l2_evict_first_policy()
+{
+    uint64_t pol;
+    asm("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+
 __device__ __forceinline__ uint4 ldg_stream_v4(const void *p)
 {
     uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+    asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.v4.u32 {%0,%1,%2,%3}, [%4], %5;"
                  : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                 : "l"(p));
+                 : "l"(p), "l"(l2_evict_first_policy()));
     return v;
 }
 

@@ -99,6 +99,9 @@ __device__ __forceinline__ void fetch_chunk(const GemvParams &p, int ch, int t, 
 // without holding a register: this is what keeps enough bytes in flight to cover the HBM latency.
 constexpr int kSlotBytes = 80;
 
+// Plain 16-byte copy. (An L2 evict-first cache hint on this instruction raised "illegal instruction" in the
+// 512-thread instance of the GEMV kernel at M = 16 while the same code ran at M <= 9; the cause was not found,
+// so the hint is not used here. The dense fp16 GEMV, which streams most of a decode step's bytes, carries it.)
 __device__ __forceinline__ void cp_async_16(uint32_t dst, const void *src)
 {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");

@@ -277,6 +277,9 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const float *__re
     const bool own_new = fused && k1 == n_keys && nk > 0;  // this split holds the newest key
     const int nk_mem = own_new ? nk - 1 : nk;               // keys of this split that are read from memory
 
+    // rotary table entry of this position first: it is the shortest wait and gates the staging of q
+    float rc = 1.f, rs = 0.f;
+    if (fused && tid < half) rc = cs_table[((int64_t)pos * half + tid) * 2], rs = cs_table[((int64_t)pos * half + tid) * 2 + 1];
     // V rows of this split -> shared memory, in flight from here on
     {
         const int per_row = D * (int)sizeof(KV) / 16;  // 16-byte pieces per row
@@ -287,12 +290,24 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const float *__re
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     }
+    // K row of this thread's first key -> registers (rows of up to 128 bytes), requested before the rotary
+    // table is needed so that its latency overlaps the staging of q
+    constexpr int KREGS = 8;
+    const int k_pieces = D * (int)sizeof(KV) / 16;
+    const bool k_pre = k_pieces <= KREGS && tid < nk_mem;
+    uint4 kreg[KREGS];
+    if (k_pre) {
+        const uint4 *kp = reinterpret_cast<const uint4 *>(kmem + (int64_t)(k0 + tid) * kv_ld + kvh * D);
+#pragma unroll
+        for (int c = 0; c < KREGS; c++)
+            if (c < k_pieces) kreg[c] = kp[c];
+    }
     if (tid < half) {
         if (!fused) {
             qs[tid] = q0 * scale, qs[tid + half] = q1 * scale;
         } else {
             const int i = tid;
-            const float c = cs_table[((int64_t)pos * half + i) * 2], sn = cs_table[((int64_t)pos * half + i) * 2 + 1];
+            const float c = rc, sn = rs;
             qs[i] = (q0 * c - q1 * sn) * scale;
             qs[i + half] = (q0 * sn + q1 * c) * scale;
             if (own_new) {
@@ -309,7 +324,30 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const float *__re
     __syncthreads();
 
     float lmax = -INFINITY;
-    for (int j = tid; j < nk_mem; j += blockDim.x) {
+    if (k_pre) {  // same order of operations as dot_row
+        float dot = 0.f;
+#pragma unroll
+        for (int c = 0; c < KREGS; c++) {
+            if (c < k_pieces) {
+                if constexpr (sizeof(KV) == 2) {
+                    const __half2 *hh = reinterpret_cast<const __half2 *>(&kreg[c]);
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        const float2 f = __half22float2(hh[j]);
+                        dot = fmaf(qs[c * 8 + 2 * j], f.x, dot);
+                        dot = fmaf(qs[c * 8 + 2 * j + 1], f.y, dot);
+                    }
+                } else {
+                    const float4 f = *reinterpret_cast<const float4 *>(&kreg[c]);
+                    dot = fmaf(qs[c * 4], f.x, dot), dot = fmaf(qs[c * 4 + 1], f.y, dot);
+                    dot = fmaf(qs[c * 4 + 2], f.z, dot), dot = fmaf(qs[c * 4 + 3], f.w, dot);
+                }
+            }
+        }
+        sc[tid] = dot;
+        lmax = dot;
+    }
+    for (int j = tid + (k_pre ? (int)blockDim.x : 0); j < nk_mem; j += blockDim.x) {
         const float dot = dot_row<KV>(qs, kmem + (int64_t)(k0 + j) * kv_ld + kvh * D, D);
         sc[j] = dot;
         lmax = fmaxf(lmax, dot);
@@ -367,12 +405,11 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const float *__re
 #pragma unroll
         for (int i = 0; i < ATT_SPLITS; i++) {
             const float li = merge[i * (D + 2) + 1];
-            if (li > 0.f) Lsum += li * expf(merge[i * (D + 2)] - M);
-        }
-#pragma unroll
-        for (int i = 0; i < ATT_SPLITS; i++) {
-            const float li = merge[i * (D + 2) + 1];
-            if (li > 0.f) acc = fmaf(merge[i * (D + 2) + 2 + d], expf(merge[i * (D + 2)] - M), acc);
+            if (li > 0.f) {
+                const float e = expf(merge[i * (D + 2)] - M);
+                Lsum += li * e;
+                acc = fmaf(merge[i * (D + 2) + 2 + d], e, acc);
+            }
         }
         out[h * D + d] = acc / Lsum;
     }
