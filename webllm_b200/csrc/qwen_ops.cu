@@ -290,14 +290,17 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const float *__re
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     }
-    // K row of this thread's first key -> registers (rows of up to 128 bytes), requested before the rotary
-    // table is needed so that its latency overlaps the staging of q
+    // Warps are specialised for the staging phase: the first warp(s) (tid < half) rotate q and the new k, the others
+    // own the keys. A key thread requests the K row of its first key (rows of up to 128 bytes) into registers right
+    // away, so the row's HBM latency overlaps the staging of q; the rotating warps issue no K loads, so their wait on
+    // the rotary table is not held up by them (loads that share a scoreboard complete together).
     constexpr int KREGS = 8;
     const int k_pieces = D * (int)sizeof(KV) / 16;
-    const bool k_pre = k_pieces <= KREGS && tid < nk_mem;
+    const int kbase = ((half + 31) >> 5) << 5, kthreads = (int)blockDim.x - kbase, kt = tid - kbase;
+    const bool k_pre = k_pieces <= KREGS && kt >= 0 && kt < nk_mem;
     uint4 kreg[KREGS];
     if (k_pre) {
-        const uint4 *kp = reinterpret_cast<const uint4 *>(kmem + (int64_t)(k0 + tid) * kv_ld + kvh * D);
+        const uint4 *kp = reinterpret_cast<const uint4 *>(kmem + (int64_t)(k0 + kt) * kv_ld + kvh * D);
 #pragma unroll
         for (int c = 0; c < KREGS; c++)
             if (c < k_pieces) kreg[c] = kp[c];
@@ -344,10 +347,10 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const float *__re
                 }
             }
         }
-        sc[tid] = dot;
+        sc[kt] = dot;
         lmax = dot;
     }
-    for (int j = tid + (k_pre ? (int)blockDim.x : 0); j < nk_mem; j += blockDim.x) {
+    for (int j = kt >= 0 ? kt + (k_pre ? kthreads : 0) : nk_mem; j < nk_mem; j += kthreads) {
         const float dot = dot_row<KV>(qs, kmem + (int64_t)(k0 + j) * kv_ld + kvh * D, D);
         sc[j] = dot;
         lmax = fmaxf(lmax, dot);
