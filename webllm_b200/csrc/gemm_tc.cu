@@ -137,6 +137,8 @@ struct Params {
     int M, N, K;
     int zcols, group_blocks;  // group / 64
     int out_f16;
+    int kb_per_slice;     // k-blocks per grid.z slice (split-K); the whole K when gridDim.z == 1
+    float *partial;       // [slices][M][N] f32 partial sums when gridDim.z > 1
 };
 
 }  // namespace tc
@@ -152,7 +154,7 @@ struct Smem {
     static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
-template <int MT, bool DENSE>
+template <int MT, bool DENSE, bool SPLIT>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, const Params p)
 {
@@ -167,7 +169,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m0 = blockIdx.x * MT, n0 = blockIdx.y * BN;
-    const int KB = p.K / BK;
+    // split-K: slice blockIdx.z covers k-blocks [kb0, KB); the ring's stage and phase count from the slice start
+    // (SPLIT is a template parameter so that the unsplit kernel keeps compile-time zero here)
+    const int kb0 = SPLIT ? blockIdx.z * p.kb_per_slice : 0;
+    const int KB = SPLIT ? min(p.K / BK, kb0 + p.kb_per_slice) : p.K / BK;
 
     auto xs = [&](int s) { return smem + s * S::STAGE_BYTES; };
     auto wd = [&](int s) { return smem + s * S::STAGE_BYTES + S::X_BYTES; };
@@ -192,9 +197,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
-            for (int kb = 0; kb < KB; kb++) {
-                const int s = kb % STAGES;
-                const uint32_t ph = (kb / STAGES) & 1;
+            for (int kb = kb0; kb < KB; kb++) {
+                const int s = (kb - kb0) % STAGES;
+                const uint32_t ph = ((kb - kb0) / STAGES) & 1;
                 if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 1)) break;
                 mbar_expect_tx(&full[s], S::X_BYTES + (DENSE ? S::WD_BYTES : S::WP_BYTES));
                 tma_load_2d(xs(s), &map_x, kb * BK, m0, &full[s]);
@@ -207,9 +212,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         if (lane == 0) {
             constexpr uint32_t idesc = idesc_f16(BN, MT);
             bool ok = true;
-            for (int kb = 0; kb < KB && ok; kb++) {
-                const int s = kb % STAGES;
-                const uint32_t ph = (kb / STAGES) & 1;
+            for (int kb = kb0; kb < KB && ok; kb++) {
+                const int s = (kb - kb0) % STAGES;
+                const uint32_t ph = ((kb - kb0) / STAGES) & 1;
                 ok = mbar_wait(&full[s], ph, abort_flag, p.status, 2);
                 if (ok && !DENSE) ok = mbar_wait(&deq[s], ph, abort_flag, p.status, 3);
                 if (!ok) break;
@@ -218,7 +223,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 const uint64_t b0 = smem_desc_sw128(smem_u32(xs(s)));
 #pragma unroll
                 for (int k = 0; k < BK / 16; k++)  // 16 fp16 = 32 bytes = 2 descriptor units along K
-                    umma_f16(tmem_base, a0 + 2 * k, b0 + 2 * k, idesc, (kb | k) != 0);
+                    umma_f16(tmem_base, a0 + 2 * k, b0 + 2 * k, idesc, ((kb - kb0) | k) != 0);
                 umma_commit(&empty[s]);
             }
             if (ok) umma_commit(acc_full);
@@ -234,10 +239,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             const bool n_ok = n < p.N;
             __half2 scale2 = __float2half2_rn(0.f), zsub = scale2, zfma = scale2;
             const __half2 sixteenth = __float2half2_rn(0.0625f);
-            for (int kb = 0; kb < KB; kb++) {
-                const int s = kb % STAGES;
-                const uint32_t ph = (kb / STAGES) & 1;
-                if (kb % p.group_blocks == 0) {
+            for (int kb = kb0; kb < KB; kb++) {
+                const int s = (kb - kb0) % STAGES;
+                const uint32_t ph = ((kb - kb0) / STAGES) & 1;
+                if (kb == kb0 || kb % p.group_blocks == 0) {
                     const int G = kb / p.group_blocks;
                     float z = 8.f;
                     if (n_ok) {
@@ -285,7 +290,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             tc_fence_after();
             const int q = warp & 3;
             const int n = n0 + q * 32 + lane;
-            const float bias = (p.bias && n < p.N) ? p.bias[n] : 0.f;
+            // split-K: slices write f32 partial sums, splitk_reduce_kernel adds them and the bias
+            constexpr bool split = SPLIT;
+            float *part = SPLIT ? p.partial + (int64_t)blockIdx.z * p.M * p.N : nullptr;
+            const float bias = (!split && p.bias && n < p.N) ? p.bias[n] : 0.f;
 #pragma unroll 1
             // the two warps that share a TMEM lane quarter split the columns
             constexpr int CSPAN = MT >= 32 ? MT / 2 : MT;
@@ -301,7 +309,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                         const int m = m0 + c + j;
                         if (m < p.M) {
                             const float v = __uint_as_float(r[j]) + bias;
-                            if (p.out_f16) ((__half *)p.out)[(int64_t)m * p.N + n] = __float2half_rn(v);
+                            if (split) part[(int64_t)m * p.N + n] = v;  // this slice's partial sum, f32
+                            else if (p.out_f16) ((__half *)p.out)[(int64_t)m * p.N + n] = __float2half_rn(v);
                             else ((float *)p.out)[(int64_t)m * p.N + n] = v;
                         }
                     }
@@ -326,6 +335,19 @@ __global__ void cast_f32_to_f16_kernel(const float *__restrict__ in, __half *__r
         o.y = *reinterpret_cast<uint32_t *>(&b);
         *reinterpret_cast<uint2 *>(out + i) = o;
     }
+}
+
+// out[m, n] = bias[n] + sum over slices (in slice order) of partial[s][m][n]
+__global__ void splitk_reduce_kernel(const float *__restrict__ partial, const float *__restrict__ bias, void *__restrict__ out,
+                                     int64_t MN, int N, int S, int out_f16)
+{
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= MN) return;
+    float v = 0.f;
+    for (int s = 0; s < S; s++) v += partial[(int64_t)s * MN + i];
+    if (bias) v += bias[i % N];
+    if (out_f16) ((__half *)out)[i] = __float2half_rn(v);
+    else ((float *)out)[i] = v;
 }
 
 }  // namespace tc
@@ -385,15 +407,31 @@ int plan_gemm_tc(wb_context *ctx, const Weight &w, int64_t M, int act_dtype, int
     (void)exact;
     const int mt = pick_mt(M, w.N, ctx->sm_count);
     plan->kernel = WB_KERNEL_GEMM_TC;
-    plan->split_k = 1;
     plan->grid_x = (int)((M + mt - 1) / mt);
     plan->grid_y = (int)((w.N + 127) / 128);
-    plan->grid_z = 1;
+    // Split-K when the tiles would leave most of the GPU idle and K is long (a tile walks its k-blocks one after the
+    // other at ~0.75 us each): slices of at least 8 k-blocks, as many as fill the SMs, partial sums in the workspace
+    // after the fp16 staging of the activations, then one reduce launch.
+    const int kblocks = (int)(w.K / 64);
+    const int64_t tiles = (int64_t)plan->grid_x * plan->grid_y;
+    int S = 1;
+    if (ctx->force_split > 0) S = ctx->force_split;
+    else if (tiles * 2 <= ctx->sm_count && kblocks >= 16) {
+        S = (int)(ctx->sm_count / tiles);
+        if (S > kblocks / 8) S = kblocks / 8;
+    }
+    if (S > kblocks) S = kblocks;
+    if (S < 1) S = 1;
+    const int per = (kblocks + S - 1) / S;
+    S = (kblocks + per - 1) / per;  // drop empty slices
+    plan->split_k = S;
+    plan->grid_z = S;
     plan->block = tc::THREADS;
     plan->tile_m = mt;
     plan->tile_n = 128;
-    plan->launches = act_dtype == WB_F32 ? 2 : 1;
-    plan->scratch_bytes = act_dtype == WB_F32 ? (uint64_t)M * w.K * 2 : 0;
+    const uint64_t stage_bytes = act_dtype == WB_F32 ? align_up((uint64_t)M * w.K * 2) : 0;
+    plan->launches = (act_dtype == WB_F32 ? 2 : 1) + (S > 1 ? 1 : 0);
+    plan->scratch_bytes = stage_bytes + (S > 1 ? (uint64_t)S * M * w.N * 4 : 0);
     if (plan->scratch_bytes > kWorkspaceBytes)
         return fail(WB_ERR_OOM, "fp16 staging of %lld x %lld activations exceeds the workspace; pass fp16 activations or split M",
                     (long long)M, (long long)w.K);
@@ -404,9 +442,15 @@ template <int MT, bool DENSE>
 static cudaError_t launch_tc(const CUtensorMap &mx, const CUtensorMap &mw, const tc::Params &p, dim3 grid, cudaStream_t st)
 {
     constexpr int smem = tc::Smem<MT, DENSE>::TOTAL;
-    cudaError_t e = cudaFuncSetAttribute(tc::gemm_tc_kernel<MT, DENSE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return e;
-    tc::gemm_tc_kernel<MT, DENSE><<<grid, tc::THREADS, smem, st>>>(mx, mw, p);
+    if (grid.z > 1) {
+        cudaError_t e = cudaFuncSetAttribute(tc::gemm_tc_kernel<MT, DENSE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return e;
+        tc::gemm_tc_kernel<MT, DENSE, true><<<grid, tc::THREADS, smem, st>>>(mx, mw, p);
+    } else {
+        cudaError_t e = cudaFuncSetAttribute(tc::gemm_tc_kernel<MT, DENSE, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return e;
+        tc::gemm_tc_kernel<MT, DENSE, false><<<grid, tc::THREADS, smem, st>>>(mx, mw, p);
+    }
     return cudaGetLastError();
 }
 
@@ -445,7 +489,11 @@ int launch_gemm_tc(wb_context *ctx, const Weight &w, const void *A, void *C, con
     p.out = C, p.bias = bias, p.status = ctx->status_word;
     p.M = (int)M, p.N = (int)w.N, p.K = (int)w.K;
     p.out_f16 = out_dtype == WB_F16;
-    dim3 grid(plan.grid_x, plan.grid_y);
+    const int S = plan.split_k > 0 ? plan.split_k : 1;
+    const int kblocks = (int)(w.K / tc::BK);
+    p.kb_per_slice = (kblocks + S - 1) / S;
+    p.partial = (float *)(ctx->workspace + (act_dtype == WB_F32 ? align_up((uint64_t)M * w.K * 2) : 0));
+    dim3 grid(plan.grid_x, plan.grid_y, S);
     cudaError_t e;
     if (w.kind == WeightKind::Gptq) {
         WB_CHECK(make_map_2d(ctx, &mw, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, base + w.off_main, (uint64_t)w.N,
@@ -463,6 +511,13 @@ int launch_gemm_tc(wb_context *ctx, const Weight &w, const void *A, void *C, con
     }
     ctx->launches++;
     WB_CUDA(e);
+    if (S > 1) {
+        const int64_t MN = M * w.N;
+        tc::splitk_reduce_kernel<<<(unsigned)((MN + 255) / 256), 256, 0, ctx->stream>>>(p.partial, bias, C, MN, (int)w.N, S,
+                                                                                         out_dtype == WB_F16);
+        ctx->launches++;
+        WB_CUDA(cudaGetLastError());
+    }
     return WB_OK;
 }
 

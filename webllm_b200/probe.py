@@ -3,12 +3,16 @@
     python -m webllm_b200.probe gemv   K N [--m 1] [--copies 8] [--act f32|f16] [--reps 2]
     python -m webllm_b200.probe gemm   K N M [--reps 2]
     python -m webllm_b200.probe decode [--steps 3] [--prompt 64] [--mode auto|graph|single] [--layers 24]
+    python -m webllm_b200.probe sweep  [--which batch|big|all]
 
 ``gemv`` / ``gemm`` run one GPTQ-int4 linear (wb_linear) over ``copies`` separately registered copies of
 the same synthetic weight, so that consecutive launches read different memory (no L2 reuse between
 them); ``decode`` builds the Qwen2.5-0.5B-shaped synthetic GPTQ model, prefills a short random prompt and
 decodes ``steps`` tokens greedily. Every run prints the launch plan and a wall-clock figure; the figure is
 only a sanity check (a profiler serialises kernels), the numbers that count come from ``bench.py``.
+``sweep`` is the timing table behind the batch-size sweep (M = 1 .. 64 over the seven 0.5B projection shapes)
+and the 7B-class shapes (M = 1 and M = 4096): each case is a command batch over weight copies larger than L2,
+replayed and timed with CUDA events (needs torch for the events).
 """
 from __future__ import annotations
 
@@ -60,6 +64,53 @@ def _decode(args) -> None:
     print(f"{args.steps} steps, {dt * 1e3:.3f} ms per step by wall clock, tokens {toks[:4].tolist()}")
 
 
+def _sweep(args) -> None:
+    import torch
+    gpu = Gpu(0, weight_bytes=6 << 30, act_bytes=3 << 30)
+    stream = torch.cuda.Stream()
+    gpu.set_stream(stream.cuda_stream)
+
+    def timed(batch, launches, reps=10):
+        for _ in range(3):
+            batch.submit()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(reps):
+            batch.submit()
+        e1.record(stream)
+        e1.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / reps / launches  # us per launch
+
+    def case(name, K, N, Ms, act="f16"):
+        t = synthetic.random_gptq(K, N, 128, seed=1)
+        copies = max(2, min(64, int(300e6 // t.nbytes)))  # > 126 MB of distinct weights per pass
+        hs = [gpu.gptq_register(f"{name}_{K}x{N}_{i}", t.qweight, t.qzeros, t.scales, K, N, 128) for i in range(copies)]
+        for M in Ms:
+            gpu.arena.reset()
+            A = gpu.arena.alloc(M * K, dtype=act)
+            Cc = gpu.arena.alloc(M * N, dtype=act)
+            plan = gpu.plan(hs[0], M, act)
+            with gpu.batch() as b:
+                for h in hs:
+                    gpu.linear(h, A, Cc, None, M)
+            us = timed(b, copies)
+            b.destroy()
+            esz = 2 if act == "f16" else 4
+            nbytes = t.nbytes + esz * M * (K + N)
+            print(f"{name:7s} K={K:5d} N={N:5d} M={M:4d} {plan['kernel_name']:8s} split={plan['split_k']:2d} "
+                  f"{us:9.2f} us {nbytes / us / 1e3:8.1f} GB/s {2.0 * M * N * K / us / 1e6:8.2f} TFLOP/s", flush=True)
+        for i in range(copies):  # weights are a stack: hand the copies back
+            gpu.weight_pop()
+
+    if args.which in ("batch", "all"):
+        for name, (K, N) in synthetic.QWEN05B_SHAPES.items():
+            case(name, K, N, (1, 2, 4, 8, 16, 32, 64))
+    if args.which in ("big", "all"):
+        for name, (K, N) in synthetic.QWEN7B_SHAPES.items():
+            if name in ("q", "k", "gate", "down"):
+                case(name + "7b", K, N, (1, 4096))
+
+
 def main(argv=None) -> None:
     ap = argparse.ArgumentParser(prog="python -m webllm_b200.probe", description=__doc__.split("\n")[0])
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -74,8 +125,12 @@ def main(argv=None) -> None:
     d.add_argument("--steps", type=int, default=3), d.add_argument("--prompt", type=int, default=64)
     d.add_argument("--mode", choices=("auto", "graph", "single"), default="auto")
     d.add_argument("--layers", type=int, default=synthetic.QWEN25_05B.n_layer)
+    w = sub.add_parser("sweep")
+    w.add_argument("--which", choices=("batch", "big", "all"), default="all")
     args = ap.parse_args(argv)
-    if args.cmd == "gemv":
+    if args.cmd == "sweep":
+        _sweep(args)
+    elif args.cmd == "gemv":
         _linear(args, args.m, args.act)
     elif args.cmd == "gemm":
         _linear(args, args.M, "f16")
