@@ -126,3 +126,35 @@ def test_7b_shapes(gpu, oracle):
         rows = sorted(set(np.random.default_rng(2).integers(0, M, 30).tolist()) | {0, M - 1})
         assert_close(oracle, got[rows], _ref_rows(oracle, x16, W16, rows), F16_RTOL, f"{name} M={M}")
     gpu.synchronize()
+
+
+@pytest.mark.parametrize("M,act", [(48, "f16"), (128, "f32")])
+def test_split_k_gemm_when_few_tiles(gpu, oracle, M, act):
+    """K = 4864 -> N = 896 at a mid-size batch gives 7 tiles for 148 SMs: the planner cuts K into slices (f32 partial
+    sums in the workspace, one reduce launch, bias added once), the result is the same as the reference's and
+    repeats bit for bit; a forced single slice agrees with it to rounding."""
+    h, W16 = _weight(gpu, oracle, "down", 4864, 896)
+    bias = np.random.default_rng(896).standard_normal(896).astype(np.float32)
+    try:
+        hb = gpu.weight("tcb_down")
+    except WebllmError:
+        hb = gpu.f32_upload("tcb_down", bias)
+    x16 = np.random.default_rng(M).standard_normal((M, 4864)).astype(np.float16)
+    x = x16 if act == "f16" else x16.astype(np.float32)
+    ref = _ref_rows(oracle, x16, W16, list(range(M)), bias)
+    gpu.plan_override(_lib.WB_KERNEL_GEMM_TC, 0)
+    try:
+        p = gpu.plan(h, M, act)
+        assert p["kernel_name"] == "gemm_tc" and p["split_k"] > 1 and p["grid_z"] == p["split_k"]
+        assert p["launches"] == (2 if act == "f16" else 3)
+        got = run_linear(gpu, h, x, M, 896, hb, act=act)
+        assert_close(oracle, got, ref, F16_RTOL, f"split-K gemm M={M}")
+        again = run_linear(gpu, h, x, M, 896, hb, act=act)
+        assert np.array_equal(got.view(np.uint32), again.view(np.uint32))
+        gpu.plan_override(_lib.WB_KERNEL_GEMM_TC, 1)
+        assert gpu.plan(h, M, act)["split_k"] == 1
+        one = run_linear(gpu, h, x, M, 896, hb, act=act)
+        assert_close(oracle, one, got, F16_RTOL, "one slice vs split")  # both are rounded to the output type
+        gpu.synchronize()
+    finally:
+        gpu.plan_override(0, 0)

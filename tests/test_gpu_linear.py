@@ -202,3 +202,31 @@ def test_hint_next_prefetches_without_changing_results(gpu, oracle):
     with pytest.raises(_lib.WebllmError) as e:
         gpu.hint_next(10 ** 6)
     assert e.value.status == _lib.WB_ERR_NOT_FOUND
+
+
+@pytest.mark.parametrize("K,N,S", [(2560, 640, 1), (3584, 2048, 1), (5120, 256, 2), (7680, 96, 3)])
+@pytest.mark.parametrize("M", [1, 2, 3, 4])
+@pytest.mark.parametrize("zeros", ["any", "none"])
+def test_streaming_kernel_matches_oracle(gpu, oracle, K, N, S, M, zeros):
+    """The streaming variant of the int4 GEMV (M <= 4, >= 20 whole chunks per K slice, N % 32 == 0): both
+    activation types against the oracle, bias once, split-K through the workspace, and bitwise agreement between
+    repeated launches. The same shapes with WEBLLM_B200_NO_STREAM=1 run the general kernel."""
+    t = synthetic.random_gptq(K, N, 128, seed=K + N + M, zeros=zeros)
+    W = oracle_weight(oracle, t)
+    h = register(gpu, f"stream_{K}x{N}_{M}_{zeros}", t)
+    bias = np.random.default_rng(N + M).standard_normal(N).astype(np.float32)
+    hb = gpu.f32_upload(f"streamb_{K}x{N}_{M}_{zeros}", bias)
+    x = _x(M, K, 7 * M + K)
+    gpu.plan_override(_lib.WB_KERNEL_GEMV_MMA, S)
+    try:
+        assert gpu.plan(h, M, "f32")["split_k"] == S
+        ref = oracle.gemm_nt_ref(x, W, M, N, K, bias, threads=oracle.max_threads())
+        got = run_linear(gpu, h, x, M, N, hb)
+        assert_close(oracle, got, ref, F32_RTOL, f"stream K={K} N={N} M={M} S={S} f32")
+        again = run_linear(gpu, h, x, M, N, hb)
+        assert np.array_equal(got.view(np.uint32), again.view(np.uint32))
+        x16 = x.astype(np.float16)
+        ref16 = oracle.gemm_nt_ref(x16.astype(np.float32), W, M, N, K, bias, threads=oracle.max_threads())
+        assert_close(oracle, run_linear(gpu, h, x16, M, N, hb, act="f16"), ref16, F16_RTOL, f"stream K={K} N={N} M={M} S={S} f16")
+    finally:
+        gpu.plan_override(0, 0)

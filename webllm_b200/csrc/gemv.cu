@@ -764,6 +764,10 @@ bool linear_fusion_supported(wb_context *ctx, const Weight &w, int64_t M)
     return gemv_mma_supports(w, M);  // what plan_linear picks first for M <= 16
 }
 
+// gemv_stream.cu
+bool gemv_stream_supports(const Weight &w, int64_t M, int chunks_per_split);
+int launch_gemv_stream(wb_context *ctx, const Weight &w, const GemvParams &gp, bool has_lo, bool *launched);
+
 int launch_linear(wb_context *ctx, const Weight &w, const void *A, void *C, const float *bias, int64_t M,
                   int act_dtype, int out_dtype, int exact, const LinearFusion *fusion)
 {
@@ -795,6 +799,16 @@ int launch_linear(wb_context *ctx, const Weight &w, const void *A, void *C, cons
         p.wn = plan.tile_m, p.wk = plan.tile_n;
         p.x_f16 = act_dtype == WB_F16, p.out_f16 = out_dtype == WB_F16;
         p.xs_stride = p.chunks_per_split * 16 + 4;
+        static const bool stream_on = [] { const char *e = getenv("WEBLLM_B200_NO_STREAM"); return !(e && e[0] == '1'); }();
+        if (stream_on && !(fusion && fusion->kind != 0) && gemv_stream_supports(w, M, p.chunks_per_split)) {
+            // bandwidth-bound shape: the TMA-fed streaming kernel (whole chunks, M <= 4)
+            bool launched = false;
+            WB_CHECK(launch_gemv_stream(ctx, w, p, ex_gemv != 0, &launched));
+            if (launched) {
+                ctx->prefetch_weight = -1;
+                return WB_OK;
+            }
+        }
         p.prologue = kPrologueNone, p.delta = nullptr, p.x_out = nullptr, p.norm_w = nullptr, p.eps = 0.f, p.up = nullptr;
         p.ld_x = (int)w.K;
         if (fusion && fusion->kind != 0) {
