@@ -77,6 +77,7 @@ __global__ void __launch_bounds__(MB == 1 ? 256 : 512, MB == 1 ? 3 : 1) gptq_gem
     extern __shared__ uint4 smem_u4[];
     GT_INIT();
     GT(0);
+    const uint64_t l2_policy = MB == 1 ? l2_evict_first_policy() : 0ull;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int wn = warp % p.wn, wk = warp / p.wn;
@@ -109,7 +110,7 @@ __global__ void __launch_bounds__(MB == 1 ? 256 : 512, MB == 1 ? 3 : 1) gptq_gem
     auto request = [&](int slot) {
         if (rq_tile < tiles_cta && n_i > 0) {
             const int cc = col_of(rq_tile);
-            fetch_chunk_async(p, ch_begin + wk + rq_i * p.wk, t, cc, cc < p.N, ring + slot * stage_stride);
+            fetch_chunk_async<MB == 1>(p, ch_begin + wk + rq_i * p.wk, t, cc, cc < p.N, ring + slot * stage_stride, l2_policy);
             if (++rq_i == n_i) rq_i = 0, rq_tile++;
         }
         cp_async_commit();
