@@ -257,7 +257,7 @@ def kernel_sections(gpu, torch, stream, cfg, G, args) -> dict:
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of gptq_gemv_mma_kernel, mean over the four projections
 # of a layer, from the ncu capture summarised in profiles/gptq_gemv_mma_kernel_qwen05b_decode.md (taken on a
 # 2-layer model of the same shapes; traffic is proportional to the number of layers, so the mean carries over).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 2005131
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 2019392
 
 
 def run_ours(args) -> None:
