@@ -680,6 +680,27 @@ static void plan_gemv_mma(wb_context *ctx, const Weight &w, int64_t M, int two_h
         const int by_fill = (target + ctas_n - 1) / ctas_n;
         S = by_work < by_fill ? by_work : by_fill;
     }
+    // Bandwidth-bound shapes (M <= 4, whole chunks and tiles) go to the streaming kernel, whose CTAs are persistent
+    // over 32-column tiles, two per SM: the split is the one that makes the longest CTA shortest (tiles per CTA x
+    // chunks per slice) while a slice keeps at least 20 chunks.
+    if (M <= 4 && w.K % 128 == 0 && w.N % 32 == 0 && w.group % 128 == 0 && chunks >= 20) {
+        const int tiles = (int)(w.N / 32);
+        int best_s = 0;
+        long best_cost = 0;
+        for (int s = 1; s <= 8; s++) {
+            const int c = (chunks + s - 1) / s;
+            if (c < 20) break;
+            const int s_eff = (chunks + c - 1) / c;
+            int cap = 2 * ctx->sm_count / s_eff;
+            if (cap < 1) cap = 1;
+            const int waves = (tiles + cap - 1) / cap;
+            const long cost = (long)waves * c;
+            const int ctas = (tiles + waves - 1) / waves * s_eff;
+            if (ctas * 2 < ctx->sm_count) continue;  // too few CTAs to stream: the general kernel with clusters does better
+            if (best_s == 0 || cost < best_cost) best_s = s_eff, best_cost = cost;
+        }
+        if (best_s > 0) S = best_s;
+    }
     // shared memory: staged activations (16 bytes per row per packed row, twice in exact mode)
     auto smem_for = [&](int s) { return (uint64_t)gemv_smem_bytes(M, (chunks + s - 1) / s, two_halves, wn, wk, 1, nullptr); };
     while (smem_for(S) > (uint64_t)kGemvSmemLimit && S < chunks) S++;

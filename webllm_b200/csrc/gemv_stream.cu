@@ -51,7 +51,8 @@ __device__ __forceinline__ void stream_fetch(const GemvParams &p, const uint32_t
 
 }  // namespace
 
-// grid (column tiles of 32, K slices); block 256 = 8 warps over the chunks of the slice. HAS_LO: f32 activations.
+// grid (resident CTAs walking the column tiles of 32, K slices); block 256 = 8 warps over the chunks of the slice.
+// HAS_LO: f32 activations.
 template <bool HAS_LO>
 __global__ void __launch_bounds__(256, 2) gptq_gemv_stream_kernel(const GemvParams p)
 {
@@ -61,7 +62,10 @@ __global__ void __launch_bounds__(256, 2) gptq_gemv_stream_kernel(const GemvPara
     const int ch_end = min(p.chunks, ch_begin + p.chunks_per_split);
     const int chunks_cta = ch_end - ch_begin;
     const int rows_pad = chunks_cta * 16, row_begin = ch_begin * 16;
-    const int c = blockIdx.x * 32 + 4 * g;
+    // Column tiles are persistent: this CTA walks tiles blockIdx.x, blockIdx.x + gridDim.x, ... so the activations are
+    // staged once per CTA and the prefetch runs on across tile boundaries.
+    const int col_tiles = p.N >> 5;
+    const int tiles_cta = (int)blockIdx.x < col_tiles ? (col_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
 
     // operand rows: hi of batch row j at index j, lo at M + j, then one row of zeros
     const int n_rows = HAS_LO ? 2 * p.M : p.M;
@@ -69,13 +73,25 @@ __global__ void __launch_bounds__(256, 2) gptq_gemv_stream_kernel(const GemvPara
     float *xsum = reinterpret_cast<float *>(smem_u4 + (size_t)(n_rows + 1) * p.xs_stride);  // [M][chunks_cta]
     float *red = xsum + ((p.M * chunks_cta + 3) & ~3);                                       // [8 warps][32 lanes][4]
 
-    // the first two chunks of this warp: requested before anything else (and before the wait on the previous kernel)
-    const uint32_t *wbase = p.qw + (int64_t)t * p.N + c;
+    // This warp's work is the sequence (tile j, chunk ch_begin + warp + 8 i); `pf` is the position two steps ahead.
+    // The first two chunks are requested before anything else (and before the wait on the previous kernel).
+    const uint32_t *wrow = p.qw + (int64_t)t * p.N + 4 * g;
     const int64_t row_step = (int64_t)4 * p.N;
+    const int ch_first = ch_begin + warp;  // chunks_cta >= 20: every warp has chunks
+    auto fetch_at = [&](int j, int ch, StreamRegs &r) {
+        const int tile = (int)blockIdx.x + j * (int)gridDim.x;
+        stream_fetch(p, wrow + tile * 32, row_step, ch, tile * 32 + 4 * g, r);
+    };
     StreamRegs cur, nxt, nxt2;
-    int ch = ch_begin + warp;
-    if (ch < ch_end) stream_fetch(p, wbase, row_step, ch, c, cur);
-    if (ch + 8 < ch_end) stream_fetch(p, wbase, row_step, ch + 8, c, nxt);
+    int pf_j = 0, pf_ch = ch_first;
+    auto pf_advance = [&]() {
+        pf_ch += 8;
+        if (pf_ch >= ch_end) pf_ch = ch_first, pf_j++;
+    };
+    if (pf_j < tiles_cta) fetch_at(pf_j, pf_ch, cur);
+    pf_advance();
+    if (pf_j < tiles_cta) fetch_at(pf_j, pf_ch, nxt);
+    pf_advance();
     pdl_sync();
 
     // ---- stage the activations in the MMA's k-slot order (x0,x4)(x2,x6)(x1,x5)(x3,x7), hi and lo rows ----
@@ -142,91 +158,96 @@ __global__ void __launch_bounds__(256, 2) gptq_gemv_stream_kernel(const GemvPara
     const int brow = bj < p.M ? ((g & 1) ? (HAS_LO ? p.M + bj : n_rows) : bj) : n_rows;
     const uint4 *xrow = xs + (size_t)brow * p.xs_stride + t;
     const float *xsum_t = xsum + (t < p.M ? t : 0) * chunks_cta;  // this thread's outputs belong to batch row t
-    float tot[4] = {0.f, 0.f, 0.f, 0.f};  // columns c .. c + 3 of batch row t
-    for (; ch < ch_end; ch += 8) {
-        const bool more = ch + 8 < ch_end;
-        if (ch + 16 < ch_end) stream_fetch(p, wbase, row_step, ch + 16, c, nxt2);
-        const int rl0 = (ch - ch_begin) * 16;
-        float ae[2][4], ao[2][4];
-#pragma unroll
-        for (int st = 0; st < 4; st++) {
-            uint32_t e0[4], e1[4], o0[4], o1[4];
-            const uint32_t wv[4] = {cur.w[st].x, cur.w[st].y, cur.w[st].z, cur.w[st].w};
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-                const uint32_t w8 = wv[j] >> 8;
-                e0[j] = wv[j] & 0x000f000fu;
-                o0[j] = wv[j] & 0x00f000f0u;
-                e1[j] = w8 & 0x000f000fu;
-                o1[j] = w8 & 0x00f000f0u;
-            }
-            const uint4 xb = xrow[rl0 + st * 4];
-            if (st == 0) {
-                mma_16816_zero(ae[0], e0[0], e0[1], e1[0], e1[1], xb.x, xb.y);
-                mma_16816_zero(ao[0], o0[0], o0[1], o1[0], o1[1], xb.z, xb.w);
-                mma_16816_zero(ae[1], e0[2], e0[3], e1[2], e1[3], xb.x, xb.y);
-                mma_16816_zero(ao[1], o0[2], o0[3], o1[2], o1[3], xb.z, xb.w);
-            } else {
-                mma_16816(ae[0], e0[0], e0[1], e1[0], e1[1], xb.x, xb.y);
-                mma_16816(ao[0], o0[0], o0[1], o1[0], o1[1], xb.z, xb.w);
-                mma_16816(ae[1], e0[2], e0[3], e1[2], e1[3], xb.x, xb.y);
-                mma_16816(ao[1], o0[2], o0[3], o1[2], o1[3], xb.z, xb.w);
-            }
-        }
-        // epilogue of the chunk: accumulator elements (0, 1) = (hi, lo) of column c + 2s, (2, 3) of column c + 2s + 1
-        const float2 s01 = __half22float2(u32_as_h2(cur.s.x)), s23 = __half22float2(u32_as_h2(cur.s.y));
-        const float scale[4] = {s01.x, s01.y, s23.x, s23.y};
-        const uint32_t zw = cur.z >> ((c & 7) * 4);
-        const float sx = xsum_t[ch - ch_begin];
-#pragma unroll
-        for (int j = 0; j < 4; j++) {
-            const int s = j >> 1, e = (j & 1) * 2;
-            const float q = fmaf(ao[s][e], 0.0625f, ae[s][e]) + fmaf(ao[s][e + 1], 0.0625f, ae[s][e + 1]);
-            const float zp = (float)(((zw >> (4 * j)) & 15u) + 1u);
-            tot[j] = fmaf(scale[j], fmaf(q, 16777216.f, -zp * sx), tot[j]);
-        }
-        if (more) cur = nxt, nxt = nxt2;
-    }
-
-    // ---- reduce over the 8 warps (fixed order), then write / split-K through the workspace ----
-    *reinterpret_cast<float4 *>(red + (warp * 32 + lane) * 4) = make_float4(tot[0], tot[1], tot[2], tot[3]);
-    __syncthreads();
     __shared__ int is_last;
-    const int n_base = blockIdx.x * 32;
-    const int outputs = p.M * 32;
-    if (tid < outputs) {
-        const int m = tid >> 5, col = tid & 31;
-        const int src = ((col >> 2) * 4 + m) * 4 + (col & 3);
-        float v = 0.f;
+    for (int j = 0; j < tiles_cta; j++) {
+        const int tile = (int)blockIdx.x + j * (int)gridDim.x;
+        const int c = tile * 32 + 4 * g;
+        float tot[4] = {0.f, 0.f, 0.f, 0.f};  // columns c .. c + 3 of batch row t
+        for (int ch = ch_first; ch < ch_end; ch += 8) {
+            if (pf_j < tiles_cta) fetch_at(pf_j, pf_ch, nxt2);
+            pf_advance();
+            const int rl0 = (ch - ch_begin) * 16;
+            float ae[2][4], ao[2][4];
 #pragma unroll
-        for (int w = 0; w < 8; w++) v += red[w * 128 + src];
-        const int n = n_base + col;
-        if (p.S == 1) {
-            if (p.bias) v += p.bias[n];
-            if (p.out_f16) ((__half *)p.out)[(int64_t)m * p.N + n] = __float2half_rn(v);
-            else ((float *)p.out)[(int64_t)m * p.N + n] = v;
-        } else {
-            p.partial[((int64_t)blockIdx.y * p.M + m) * p.N + n] = v;
+            for (int st = 0; st < 4; st++) {
+                uint32_t e0[4], e1[4], o0[4], o1[4];
+                const uint32_t wv[4] = {cur.w[st].x, cur.w[st].y, cur.w[st].z, cur.w[st].w};
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const uint32_t w8 = wv[i] >> 8;
+                    e0[i] = wv[i] & 0x000f000fu;
+                    o0[i] = wv[i] & 0x00f000f0u;
+                    e1[i] = w8 & 0x000f000fu;
+                    o1[i] = w8 & 0x00f000f0u;
+                }
+                const uint4 xb = xrow[rl0 + st * 4];
+                if (st == 0) {
+                    mma_16816_zero(ae[0], e0[0], e0[1], e1[0], e1[1], xb.x, xb.y);
+                    mma_16816_zero(ao[0], o0[0], o0[1], o1[0], o1[1], xb.z, xb.w);
+                    mma_16816_zero(ae[1], e0[2], e0[3], e1[2], e1[3], xb.x, xb.y);
+                    mma_16816_zero(ao[1], o0[2], o0[3], o1[2], o1[3], xb.z, xb.w);
+                } else {
+                    mma_16816(ae[0], e0[0], e0[1], e1[0], e1[1], xb.x, xb.y);
+                    mma_16816(ao[0], o0[0], o0[1], o1[0], o1[1], xb.z, xb.w);
+                    mma_16816(ae[1], e0[2], e0[3], e1[2], e1[3], xb.x, xb.y);
+                    mma_16816(ao[1], o0[2], o0[3], o1[2], o1[3], xb.z, xb.w);
+                }
+            }
+            // epilogue of the chunk: accumulator elements (0, 1) = (hi, lo) of column c + 2s, (2, 3) of column c + 2s + 1
+            const float2 s01 = __half22float2(u32_as_h2(cur.s.x)), s23 = __half22float2(u32_as_h2(cur.s.y));
+            const float scale[4] = {s01.x, s01.y, s23.x, s23.y};
+            const uint32_t zw = cur.z >> ((c & 7) * 4);
+            const float sx = xsum_t[ch - ch_begin];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int s = i >> 1, e = (i & 1) * 2;
+                const float q = fmaf(ao[s][e], 0.0625f, ae[s][e]) + fmaf(ao[s][e + 1], 0.0625f, ae[s][e + 1]);
+                const float zp = (float)(((zw >> (4 * i)) & 15u) + 1u);
+                tot[i] = fmaf(scale[i], fmaf(q, 16777216.f, -zp * sx), tot[i]);
+            }
+            cur = nxt, nxt = nxt2;
         }
-    }
-    if (p.S > 1) {
-        // the last slice to arrive for this tile adds the slices in slice order and the bias once
-        __threadfence();
+
+        // ---- reduce over the 8 warps (fixed order), then write / split-K through the workspace ----
+        *reinterpret_cast<float4 *>(red + (warp * 32 + lane) * 4) = make_float4(tot[0], tot[1], tot[2], tot[3]);
         __syncthreads();
-        if (tid == 0) is_last = (atomicAdd(&p.counters[blockIdx.x], 1u) == (unsigned)(p.S - 1));
-        __syncthreads();
-        if (is_last) {
-            __threadfence();
-            if (tid < outputs) {
-                const int m = tid >> 5, n = n_base + (tid & 31);
-                float v = 0.f;
-                for (int s = 0; s < p.S; s++) v += __ldcg(&p.partial[((int64_t)s * p.M + m) * p.N + n]);
+        const int n_base = tile * 32;
+        const int outputs = p.M * 32;
+        if (tid < outputs) {
+            const int m = tid >> 5, col = tid & 31;
+            const int src = ((col >> 2) * 4 + m) * 4 + (col & 3);
+            float v = 0.f;
+#pragma unroll
+            for (int w = 0; w < 8; w++) v += red[w * 128 + src];
+            const int n = n_base + col;
+            if (p.S == 1) {
                 if (p.bias) v += p.bias[n];
                 if (p.out_f16) ((__half *)p.out)[(int64_t)m * p.N + n] = __float2half_rn(v);
                 else ((float *)p.out)[(int64_t)m * p.N + n] = v;
+            } else {
+                p.partial[((int64_t)blockIdx.y * p.M + m) * p.N + n] = v;
             }
-            if (tid == 0) p.counters[blockIdx.x] = 0u;
         }
+        if (p.S > 1) {
+            // the last slice to arrive for this tile adds the slices in slice order and the bias once
+            __threadfence();
+            __syncthreads();
+            if (tid == 0) is_last = (atomicAdd(&p.counters[tile], 1u) == (unsigned)(p.S - 1));
+            __syncthreads();
+            if (is_last) {
+                __threadfence();
+                if (tid < outputs) {
+                    const int m = tid >> 5, n = n_base + (tid & 31);
+                    float v = 0.f;
+                    for (int s = 0; s < p.S; s++) v += __ldcg(&p.partial[((int64_t)s * p.M + m) * p.N + n]);
+                    if (p.bias) v += p.bias[n];
+                    if (p.out_f16) ((__half *)p.out)[(int64_t)m * p.N + n] = __float2half_rn(v);
+                    else ((float *)p.out)[(int64_t)m * p.N + n] = v;
+                }
+                if (tid == 0) p.counters[tile] = 0u;
+            }
+        }
+        __syncthreads();  // red and is_last are reused by the next tile
     }
 }
 
@@ -248,7 +269,12 @@ int launch_gemv_stream(wb_context *ctx, const Weight &w, const GemvParams &gp, b
     const size_t rows = (size_t)(has_lo ? 2 * M : M) + 1;
     const size_t smem = rows * p.xs_stride * 16 + (size_t)((M * cps + 3) & ~3) * 4 + 8 * 32 * 4 * 4;
     if (smem > 100 * 1024) return WB_OK;  // two CTAs per SM
-    dim3 grid((unsigned)(w.N / 32), (unsigned)p.S);
+    // grid: what is resident at once (two CTAs per SM), evened out so that every CTA walks the same number of tiles
+    const int col_tiles = (int)(w.N / 32);
+    int capacity = ctx->sm_count * 2 / p.S;
+    if (capacity < 1) capacity = 1;
+    const int waves = (col_tiles + capacity - 1) / capacity;
+    dim3 grid((unsigned)((col_tiles + waves - 1) / waves), (unsigned)p.S);
     cudaError_t e;
     if (has_lo) {
         cudaFuncSetAttribute(gptq_gemv_stream_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
