@@ -71,8 +71,13 @@ extern "C" int wb_debug_gemv_trace(unsigned long long *out, unsigned *n)
 #define GT(i)
 #endif
 
-template <int MB, bool EXACT>
-__global__ void __launch_bounds__(MB == 1 ? 256 : 512, MB == 1 ? 3 : 1) gptq_gemv_mma_kernel(const GemvParams p)
+// DIRECT (MB == 1 only): every warp holds at most one chunk of one tile and loads it straight into registers with
+// 128-bit streaming loads instead of going through the cp.async ring. Issuing six cp.async per thread costs ~0.4 us
+// more than plain loads; that is hidden when the kernel's prologue runs under its predecessor (programmatic dependent
+// launch), so the variant is used where it is not: the split-K projection that follows a kernel which fills the SMs.
+// It needs more registers (two CTAs per SM instead of three).
+template <int MB, bool EXACT, bool DIRECT>
+__global__ void __launch_bounds__(MB == 1 ? 256 : 512, MB == 1 ? (DIRECT ? 2 : 3) : 1) gptq_gemv_mma_kernel(const GemvParams p)
 {
     extern __shared__ uint4 smem_u4[];
     GT_INIT();
@@ -115,7 +120,15 @@ __global__ void __launch_bounds__(MB == 1 ? 256 : 512, MB == 1 ? 3 : 1) gptq_gem
         }
         cp_async_commit();
     };
-    for (int s = 0; s < p.stages - 1; s++) request(s);
+    ChunkRegs pre;
+    if constexpr (DIRECT) {
+        if (tiles_cta > 0 && n_i > 0) {
+            const int cc = col_of(0);
+            fetch_chunk(p, ch_begin + wk, t, cc, cc < p.N, pre);
+        }
+    } else {
+        for (int s = 0; s < p.stages - 1; s++) request(s);
+    }
     if (p.pf_bytes && tid == 0) {
         // L2 prefetch of the weight that a following call will stream: each CTA asks for one slice, so the whole
         // matrix is on its way while this kernel (and the small kernels after it) run, and that call finds its
@@ -373,13 +386,17 @@ __global__ void __launch_bounds__(MB == 1 ? 256 : 512, MB == 1 ? 3 : 1) gptq_gem
 #pragma unroll
                 for (int i = 0; i < 4; i++) tot[mb][s][i] = 0.f;
         for (int i = 0; i < n_i; i++) {
-            request(slot_req);
-            slot_req = slot_req + 1 == p.stages ? 0 : slot_req + 1;
-            cp_async_wait(p.stages - 1);  // everything but the newest stages - 1 groups has landed
-            if (tj == 0 && i == 0) GT(4);
             ChunkRegs ra;
-            read_slot(ring + slot_use * stage_stride, c, ra);
-            slot_use = slot_use + 1 == p.stages ? 0 : slot_use + 1;
+            if constexpr (DIRECT) {
+                ra = pre;
+            } else {
+                request(slot_req);
+                slot_req = slot_req + 1 == p.stages ? 0 : slot_req + 1;
+                cp_async_wait(p.stages - 1);  // everything but the newest stages - 1 groups has landed
+                read_slot(ring + slot_use * stage_stride, c, ra);
+                slot_use = slot_use + 1 == p.stages ? 0 : slot_use + 1;
+            }
+            if (tj == 0 && i == 0) GT(4);
             const int chunk = ch_begin + wk + i * p.wk;
             const int rl0 = chunk * 16 + t - row_begin;
             compute_chunk<MB, EXACT>(p, ra, rl0, g, t, xs_hi, xs_lo, xsum, chunk - ch_begin, chunks_cta, tot);
@@ -767,17 +784,20 @@ int plan_linear(wb_context *ctx, const Weight &w, int64_t M, int act_dtype, int 
 // Most of a later weight that one call asks the L2 to fetch (a fraction of the 126 MB L2).
 constexpr uint64_t kPrefetchLimit = 32ull << 20;
 
+template <int MB, bool EXACT, bool DIRECT>
+static cudaError_t launch_gemv_inst(const GemvParams &p, dim3 grid, int block, size_t smem, cudaStream_t st)
+{
+    cudaFuncSetAttribute(gptq_gemv_mma_kernel<MB, EXACT, DIRECT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemvSmemLimit);
+    return launch_pdl_cluster(gptq_gemv_mma_kernel<MB, EXACT, DIRECT>, grid, dim3(block), smem, st, p.cluster ? (unsigned)p.S : 1u, p);
+}
+
 template <int MB>
 static cudaError_t launch_gemv_mb(const GemvParams &p, dim3 grid, int block, size_t smem, bool exact, cudaStream_t st)
 {
-    const unsigned cl = p.cluster ? (unsigned)p.S : 1u;
-    if (exact) {
-        cudaFuncSetAttribute(gptq_gemv_mma_kernel<MB, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemvSmemLimit);
-        return launch_pdl_cluster(gptq_gemv_mma_kernel<MB, true>, grid, dim3(block), smem, st, cl, p);
-    } else {
-        cudaFuncSetAttribute(gptq_gemv_mma_kernel<MB, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemvSmemLimit);
-        return launch_pdl_cluster(gptq_gemv_mma_kernel<MB, false>, grid, dim3(block), smem, st, cl, p);
+    if constexpr (MB == 1) {
+        if (p.direct) return exact ? launch_gemv_inst<1, true, true>(p, grid, block, smem, st) : launch_gemv_inst<1, false, true>(p, grid, block, smem, st);
     }
+    return exact ? launch_gemv_inst<MB, true, false>(p, grid, block, smem, st) : launch_gemv_inst<MB, false, false>(p, grid, block, smem, st);
 }
 
 bool linear_fusion_supported(wb_context *ctx, const Weight &w, int64_t M)
@@ -849,6 +869,8 @@ int launch_linear(wb_context *ctx, const Weight &w, const void *A, void *C, cons
         const int MB = M <= 8 ? 1 : (M <= 16 ? 2 : 4);
         p.stages = gemv_pick_stages(M, p.chunks_per_split, ex_gemv, p.wn, p.wk);
         p.cluster = gemv_cluster_merge(M, p.S) ? 1 : 0;
+        // register path: one chunk per warp, one tile per CTA, and a split-K launch (see the kernel's comment)
+        p.direct = (M <= 8 && p.cluster && p.chunks_per_split <= p.wk && plan.grid_x * plan.grid_y <= ctx->sm_count) ? 1 : 0;
         const size_t smem = gemv_smem_bytes(M, p.chunks_per_split, ex_gemv, p.wn, p.wk, p.stages, &p.ring_off, &p.red_off,
                                             p.cluster ? p.S : 0, &p.cl_off);
         if (smem > (size_t)kGemvSmemLimit) return fail(WB_ERR_UNSUPPORTED, "GEMV_MMA: activations do not fit shared memory");
@@ -992,7 +1014,7 @@ extern "C" int wb_gptq_gemv_static(const void *qweight, const void *qzeros, cons
     p.M = (int)M, p.N = (int)N, p.K = (int)K, p.pack_rows = pack_rows, p.zcols = (int)((N + 7) / 8);
     p.chunks = chunks, p.chunks_per_split = cps, p.group_chunks = (int)(group_size / 128), p.S = S;
     p.wn = wn, p.wk = wk, p.x_f16 = act_dtype == WB_F16, p.out_f16 = out_dtype == WB_F16, p.xs_stride = xs_stride;
-    p.stages = stages, p.ring_off = ring_off, p.red_off = red_off, p.cluster = 0, p.cl_off = 0;
+    p.stages = stages, p.ring_off = ring_off, p.red_off = red_off, p.cluster = 0, p.cl_off = 0, p.direct = 0;
     p.pf_ptr = nullptr, p.pf_bytes = 0;
     p.prologue = kPrologueNone, p.delta = nullptr, p.x_out = nullptr, p.norm_w = nullptr, p.eps = 0.f, p.up = nullptr, p.ld_x = (int)K;
     int sms = 148;

@@ -31,6 +31,7 @@ struct GemvParams {
     int stages;         // depth of the per-thread cp.async ring
     int ring_off;       // byte offset of the ring in dynamic shared memory
     int red_off;        // byte offset of the cross-warp reduction buffer
+    int direct;         // 1: every warp holds at most one chunk of one tile: it is loaded straight into registers
     int cluster;        // 1: the S slices of a column tile are one thread-block cluster and merge through its shared memory
     int cl_off;         // byte offset of the [S][M * tile columns] merge buffer (used in the cluster's first CTA)
     const char *pf_ptr;   // weight of a later call to pull into L2 while this one runs (nullable)
