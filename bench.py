@@ -255,8 +255,9 @@ def kernel_sections(gpu, torch, stream, cfg, G, args) -> dict:
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of gptq_gemv_mma_kernel, mean over the four projections
-# of a layer, from the ncu capture summarised in profiles/gptq_gemv_mma_kernel_qwen05b_decode.md (taken on a
-# 2-layer model of the same shapes; traffic is proportional to the number of layers, so the mean carries over).
+# of a layer, from an ncu capture of a 2-layer model of the same shapes (one pass per launch, caches flushed between
+# launches, the L2 prefetch of the next weight switched off); traffic is proportional to the number of layers, so the
+# mean carries over to the 24-layer step. Algorithmic bytes of the same four launches: 1 956 704 on average.
 NCU_TRAFFIC_BYTES_PER_LAUNCH = 2019392
 
 
