@@ -12,7 +12,9 @@
 //   * weights go from global memory into registers with 128-bit streaming loads, two chunks ahead (issuing a plain
 //     load costs a third of a cp.async to shared memory, and nothing has to be read back from a ring);
 //   * accumulators start from the zero register instead of being cleared, and the per-chunk epilogue touches the four
-//     outputs a thread owns, not sixteen.
+//     outputs a thread owns, not sixteen;
+//   * CTAs are persistent over column tiles (two CTAs per SM, one wave): the activations are staged once per CTA and the
+//     register prefetch runs on across tile boundaries, so the loads never drain between tiles.
 // A TMA-fed variant of this kernel (one elected thread copying [16 rows x 32 columns] boxes into a ring of shared-memory
 // slots, persistent over column tiles) was built and measured slower (16.7 us against 14.0 us on K = 3584, N = 18944),
 // so the loads stay per thread.
@@ -256,7 +258,7 @@ bool gemv_stream_supports(const Weight &w, int64_t M, int chunks_per_split)
 {
     // whole chunks and tiles only; enough chunks per slice that streaming (not latency) is what matters
     return w.kind == WeightKind::Gptq && M >= 1 && M <= 4 && w.K % 128 == 0 && w.N % 32 == 0 && w.group % 128 == 0 &&
-           chunks_per_split >= 20;
+           chunks_per_split >= 20 && w.N / 32 <= kMaxCounters;  // one arrival counter per column tile when K is split
 }
 
 // Returns WB_OK and *launched = true when the streaming kernel took the call; *launched = false when it does not fit.
