@@ -24,9 +24,8 @@ namespace wb {
 
 namespace tc {
 
-constexpr int BN = 128;       // output columns per CTA (UMMA M)
+constexpr int BN = 128;       // output columns per accumulator (UMMA M); a CTA holds NH = 1 or 2 of them
 constexpr int BK = 64;        // k per stage: one 128-byte swizzle atom of fp16
-constexpr int STAGES = 4;
 constexpr int THREADS = 320;
 constexpr uint32_t SPIN_LIMIT = 1u << 20;
 
@@ -145,21 +144,31 @@ struct Params {
 
 namespace tc {
 
-template <int MT, bool DENSE>
+template <int MT, bool DENSE, int NH>
 struct Smem {
+    static constexpr int COLS = BN * NH;  // output columns per CTA
     static constexpr int X_BYTES = MT * BK * 2;
-    static constexpr int WD_BYTES = BN * BK * 2;
-    static constexpr int WP_BYTES = DENSE ? 0 : 8 * BN * 4;
+    static constexpr int WD_BYTES = COLS * BK * 2;
+    static constexpr int WP_BYTES = DENSE ? 0 : 8 * COLS * 4;
     static constexpr int STAGE_BYTES = X_BYTES + WD_BYTES + WP_BYTES;  // every piece is a multiple of 1024
+#ifdef WB_EXP_STAGES
+    static constexpr int STAGES = WB_EXP_STAGES;
+#else
+    static constexpr int STAGES = (4 * STAGE_BYTES + 1280 <= 227 * 1024) ? 4 : 3;
+#endif
     static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    
 };
 
-template <int MT, bool DENSE, bool SPLIT>
+template <int MT, bool DENSE, bool SPLIT, int NH>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, const Params p)
 {
-    using S = Smem<MT, DENSE>;
-    constexpr uint32_t TMEM_COLS = MT < 32 ? 32 : MT;
+    using S = Smem<MT, DENSE, NH>;
+    constexpr int STAGES = S::STAGES;
+    constexpr int COLS = S::COLS;
+    constexpr uint32_t ACC_COLS = MT < 32 ? 32 : MT;  // TMEM columns of one accumulator
+    constexpr uint32_t TMEM_COLS = ACC_COLS * NH;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t *bars = (uint64_t *)(smem + STAGES * S::STAGE_BYTES);
@@ -168,7 +177,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.x * MT, n0 = blockIdx.y * BN;
+    const int m0 = blockIdx.x * MT, n0 = blockIdx.y * COLS;
     // split-K: slice blockIdx.z covers k-blocks [kb0, KB); the ring's stage and phase count from the slice start
     // (SPLIT is a template parameter so that the unsplit kernel keeps compile-time zero here)
     const int kb0 = SPLIT ? blockIdx.z * p.kb_per_slice : 0;
@@ -222,8 +231,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 const uint64_t a0 = smem_desc_sw128(smem_u32(wd(s)));
                 const uint64_t b0 = smem_desc_sw128(smem_u32(xs(s)));
 #pragma unroll
-                for (int k = 0; k < BK / 16; k++)  // 16 fp16 = 32 bytes = 2 descriptor units along K
-                    umma_f16(tmem_base, a0 + 2 * k, b0 + 2 * k, idesc, ((kb - kb0) | k) != 0);
+                for (int k = 0; k < BK / 16; k++) {  // 16 fp16 = 32 bytes = 2 descriptor units along K
+#pragma unroll
+                    for (int h = 0; h < NH; h++)  // the halves of the weight tile are 128 rows = 16 KB = 1024 units apart
+                        umma_f16(tmem_base + h * ACC_COLS, a0 + 1024 * h + 2 * k, b0 + 2 * k, idesc, ((kb - kb0) | k) != 0);
+                }
                 umma_commit(&empty[s]);
             }
             if (ok) umma_commit(acc_full);
@@ -231,35 +243,48 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         __syncwarp();
     } else {
         // ------------------------------------------------------------------ unpack, then epilogue
-        const int tn = (threadIdx.x - 64) & 127;   // column of the tile
-        const int rhalf = (threadIdx.x - 64) >> 7;  // which 4 of the 8 packed rows of a k-block
+        constexpr int RPT = 4 * NH;                    // packed rows of a k-block per thread: 256 threads, 8 rows x COLS words
+        const int tn = (threadIdx.x - 64) % COLS;      // column of the tile
+        const int rhalf = (threadIdx.x - 64) / COLS;   // which RPT of the 8 packed rows
         bool ok = true;
         if constexpr (!DENSE) {
             const int n = n0 + tn;
             const bool n_ok = n < p.N;
             __half2 scale2 = __float2half2_rn(0.f), zsub = scale2, zfma = scale2;
             const __half2 sixteenth = __float2half2_rn(0.0625f);
+            // scale and zero point of a group are requested one group ahead, so that the trip to L2 overlaps the
+            // unpack of the current group instead of standing in front of it
+            const int n_groups = p.K / (p.group_blocks * BK);
+            __half next_scale = __float2half_rn(0.f);
+            uint32_t next_zeros = 0x77777777u;  // stored zero - 1 = 7: the symmetric default
+            auto request_group = [&](int g) {
+                if (n_ok && g < n_groups) {
+                    next_scale = p.sc[(int64_t)g * p.N + n];
+                    if (p.qz) next_zeros = p.qz[(int64_t)g * p.zcols + (n >> 3)];
+                }
+            };
+            request_group(kb0 / p.group_blocks);
             for (int kb = kb0; kb < KB; kb++) {
                 const int s = (kb - kb0) % STAGES;
                 const uint32_t ph = ((kb - kb0) / STAGES) & 1;
                 if (kb == kb0 || kb % p.group_blocks == 0) {
-                    const int G = kb / p.group_blocks;
-                    float z = 8.f;
-                    if (n_ok) {
-                        scale2 = __half2half2(p.sc[(int64_t)G * p.N + n]);
-                        if (p.qz) z = (float)(((p.qz[(int64_t)G * p.zcols + (n >> 3)] >> ((n & 7) * 4)) & 15u) + 1u);
-                    }
+                    const float z = (float)(((next_zeros >> ((n & 7) * 4)) & 15u) + 1u);
+                    scale2 = __half2half2(next_scale);
                     zsub = __float2half2_rn(1024.f + z);
                     zfma = __float2half2_rn(-(64.f + z));
+                    request_group(kb / p.group_blocks + 1);
                 }
                 ok = mbar_wait(&full[s], ph, abort_flag, p.status, 4);
                 if (!ok) break;
                 const uint32_t *src = wp(s) + tn;
                 uint8_t *dst_row = wd(s) + tn * 128;
 #pragma unroll
-                for (int rr = 0; rr < 4; rr++) {
-                    const int r = rhalf * 4 + rr;
-                    uint32_t w = src[r * BN];
+                for (int rr = 0; rr < RPT; rr++) {
+#ifdef WB_EXP_NOSTS
+                    if (p.M > 0) break;
+#endif
+                    const int r = rhalf * RPT + rr;
+                    uint32_t w = src[r * COLS];
                     const uint32_t lo0 = (w & 0x000f000fu) | 0x64006400u;
                     const uint32_t hi0 = (w & 0x00f000f0u) | 0x64006400u;
                     w >>= 8;
@@ -289,19 +314,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         if (ok) {
             tc_fence_after();
             const int q = warp & 3;
-            const int n = n0 + q * 32 + lane;
             // split-K: slices write f32 partial sums, splitk_reduce_kernel adds them and the bias
             constexpr bool split = SPLIT;
             float *part = SPLIT ? p.partial + (int64_t)blockIdx.z * p.M * p.N : nullptr;
-            const float bias = (!split && p.bias && n < p.N) ? p.bias[n] : 0.f;
-#pragma unroll 1
             // the two warps that share a TMEM lane quarter split the columns
             constexpr int CSPAN = MT >= 32 ? MT / 2 : MT;
             const int c_begin = MT >= 32 ? ((warp - 2) >> 2) * CSPAN : 0;
             const int c_end = (MT >= 32 || warp < 6) ? c_begin + CSPAN : 0;
+#pragma unroll 1
+            for (int h = 0; h < NH; h++) {
+            const int n = n0 + h * BN + q * 32 + lane;
+            const float bias = (!split && p.bias && n < p.N) ? p.bias[n] : 0.f;
+#pragma unroll 1
             for (int c = c_begin; c < c_end; c += 16) {
                 uint32_t r[16];
-                tmem_ld_32x32b_x16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c, r);
+                tmem_ld_32x32b_x16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(h * ACC_COLS + c), r);
                 tmem_ld_wait();
                 if (n < p.N) {
 #pragma unroll
@@ -315,6 +342,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                         }
                     }
                 }
+            }
             }
         }
     }
@@ -382,33 +410,39 @@ bool gemm_tc_supports(const Weight &w, int64_t M)
     return w.kind == WeightKind::DenseF16;
 }
 
-static int pick_mt(int64_t M, int64_t N, int sms)
+// Tokens (mt) and output columns (128 * nh) of a CTA's tile.
+static void pick_tile(int64_t M, int64_t N, int sms, int *mt_out, int *nh_out)
 {
-    if (M <= 16) return 16;
-    if (M <= 32) return 32;
-    if (M <= 64) return 64;
-    if (M <= 128) return 128;
-    const int64_t n_tiles = (N + 127) / 128;
-    int best = 256;
+    *nh_out = 1;
+    if (M <= 16) { *mt_out = 16; return; }
+    if (M <= 32) { *mt_out = 32; return; }
+    if (M <= 64) { *mt_out = 64; return; }
+    static const int force_nh = getenv("WEBLLM_B200_GEMM_NH") ? atoi(getenv("WEBLLM_B200_GEMM_NH")) : 0;
+    // relative time of one k-block of a tile, measured: {mt, nh, cost}
+    static const int shapes[4][3] = {{256, 1, 100}, {128, 1, 85}, {256, 2, 115}, {128, 2, 95}};
+    int best_mt = 256, best_nh = 1;
     int64_t best_cost = -1;
-    for (int mt : {256, 128}) {
-        const int64_t tiles = ((M + mt - 1) / mt) * n_tiles;
+    for (const auto &sh : shapes) {
+        const int mt = sh[0], nh = sh[1];
+        if (M <= 128 && mt == 256) continue;
+        if (force_nh && nh != force_nh) continue;
+        if (nh == 2 && N < 256) continue;
+        const int64_t tiles = ((M + mt - 1) / mt) * ((N + 128 * nh - 1) / (128 * nh));
         const int64_t waves = (tiles + sms - 1) / sms;
-        // measured: a 128-token tile is bound by the unpack of its weight tile and takes ~0.85 of the time of a
-        // 256-token tile, so the taller tile wins whenever it does not add waves
-        const int64_t cost = waves * (mt == 256 ? 100 : 85);
-        if (best_cost < 0 || cost < best_cost) best = mt, best_cost = cost;
+        const int64_t cost = waves * sh[2];
+        if (best_cost < 0 || cost < best_cost) best_mt = mt, best_nh = nh, best_cost = cost;
     }
-    return best;
+    *mt_out = best_mt, *nh_out = best_nh;
 }
 
 int plan_gemm_tc(wb_context *ctx, const Weight &w, int64_t M, int act_dtype, int exact, wb_plan *plan)
 {
     (void)exact;
-    const int mt = pick_mt(M, w.N, ctx->sm_count);
+    int mt, nh;
+    pick_tile(M, w.N, ctx->sm_count, &mt, &nh);
     plan->kernel = WB_KERNEL_GEMM_TC;
     plan->grid_x = (int)((M + mt - 1) / mt);
-    plan->grid_y = (int)((w.N + 127) / 128);
+    plan->grid_y = (int)((w.N + 128 * nh - 1) / (128 * nh));
     // Split-K when the tiles would leave most of the GPU idle and K is long (a tile walks its k-blocks one after the
     // other at ~0.75 us each): slices of at least 8 k-blocks, as many as fill the SMs, partial sums in the workspace
     // after the fp16 staging of the activations, then one reduce launch.
@@ -428,7 +462,7 @@ int plan_gemm_tc(wb_context *ctx, const Weight &w, int64_t M, int act_dtype, int
     plan->grid_z = S;
     plan->block = tc::THREADS;
     plan->tile_m = mt;
-    plan->tile_n = 128;
+    plan->tile_n = 128 * nh;
     const uint64_t stage_bytes = act_dtype == WB_F32 ? align_up((uint64_t)M * w.K * 2) : 0;
     plan->launches = (act_dtype == WB_F32 ? 2 : 1) + (S > 1 ? 1 : 0);
     plan->scratch_bytes = stage_bytes + (S > 1 ? (uint64_t)S * M * w.N * 4 : 0);
@@ -438,31 +472,33 @@ int plan_gemm_tc(wb_context *ctx, const Weight &w, int64_t M, int act_dtype, int
     return WB_OK;
 }
 
-template <int MT, bool DENSE>
+template <int MT, bool DENSE, int NH>
 static cudaError_t launch_tc(const CUtensorMap &mx, const CUtensorMap &mw, const tc::Params &p, dim3 grid, cudaStream_t st)
 {
-    constexpr int smem = tc::Smem<MT, DENSE>::TOTAL;
+    constexpr int smem = tc::Smem<MT, DENSE, NH>::TOTAL;
     if (grid.z > 1) {
-        cudaError_t e = cudaFuncSetAttribute(tc::gemm_tc_kernel<MT, DENSE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaError_t e = cudaFuncSetAttribute(tc::gemm_tc_kernel<MT, DENSE, true, NH>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return e;
-        tc::gemm_tc_kernel<MT, DENSE, true><<<grid, tc::THREADS, smem, st>>>(mx, mw, p);
+        tc::gemm_tc_kernel<MT, DENSE, true, NH><<<grid, tc::THREADS, smem, st>>>(mx, mw, p);
     } else {
-        cudaError_t e = cudaFuncSetAttribute(tc::gemm_tc_kernel<MT, DENSE, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaError_t e = cudaFuncSetAttribute(tc::gemm_tc_kernel<MT, DENSE, false, NH>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return e;
-        tc::gemm_tc_kernel<MT, DENSE, false><<<grid, tc::THREADS, smem, st>>>(mx, mw, p);
+        tc::gemm_tc_kernel<MT, DENSE, false, NH><<<grid, tc::THREADS, smem, st>>>(mx, mw, p);
     }
     return cudaGetLastError();
 }
 
+// tile_n = 256 (two accumulators per CTA) exists for the 128- and 256-token tiles only
 template <bool DENSE>
-static cudaError_t launch_tc_mt(int mt, const CUtensorMap &mx, const CUtensorMap &mw, const tc::Params &p, dim3 grid, cudaStream_t st)
+static cudaError_t launch_tc_mt(int mt, int nh, const CUtensorMap &mx, const CUtensorMap &mw, const tc::Params &p, dim3 grid,
+                                cudaStream_t st)
 {
     switch (mt) {
-    case 16: return launch_tc<16, DENSE>(mx, mw, p, grid, st);
-    case 32: return launch_tc<32, DENSE>(mx, mw, p, grid, st);
-    case 64: return launch_tc<64, DENSE>(mx, mw, p, grid, st);
-    case 128: return launch_tc<128, DENSE>(mx, mw, p, grid, st);
-    default: return launch_tc<256, DENSE>(mx, mw, p, grid, st);
+    case 16: return launch_tc<16, DENSE, 1>(mx, mw, p, grid, st);
+    case 32: return launch_tc<32, DENSE, 1>(mx, mw, p, grid, st);
+    case 64: return launch_tc<64, DENSE, 1>(mx, mw, p, grid, st);
+    case 128: return nh == 2 ? launch_tc<128, DENSE, 2>(mx, mw, p, grid, st) : launch_tc<128, DENSE, 1>(mx, mw, p, grid, st);
+    default: return nh == 2 ? launch_tc<256, DENSE, 2>(mx, mw, p, grid, st) : launch_tc<256, DENSE, 1>(mx, mw, p, grid, st);
     }
 }
 
@@ -483,6 +519,7 @@ int launch_gemm_tc(wb_context *ctx, const Weight &w, const void *A, void *C, con
         a16 = ctx->workspace;
     }
     const int mt = plan.tile_m;
+    const int nh = plan.tile_n == 2 * tc::BN ? 2 : 1;
     CUtensorMap mx, mw;
     WB_CHECK(make_map_2d(ctx, &mx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a16, (uint64_t)w.K, (uint64_t)M, tc::BK, (uint32_t)mt, true));
     tc::Params p;
@@ -497,17 +534,17 @@ int launch_gemm_tc(wb_context *ctx, const Weight &w, const void *A, void *C, con
     cudaError_t e;
     if (w.kind == WeightKind::Gptq) {
         WB_CHECK(make_map_2d(ctx, &mw, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, base + w.off_main, (uint64_t)w.N,
-                             (uint64_t)w.pack_rows, tc::BN, 8, false));
+                             (uint64_t)w.pack_rows, tc::BN * nh, 8, false));
         p.qz = w.has_zeros ? (const uint32_t *)(base + w.off_zeros) : nullptr;
         p.sc = (const __half *)(base + w.off_scales);
         p.zcols = (int)w.zcols;
         p.group_blocks = (int)(w.group / 64);
-        e = launch_tc_mt<false>(mt, mx, mw, p, grid, ctx->stream);
+        e = launch_tc_mt<false>(mt, nh, mx, mw, p, grid, ctx->stream);
     } else {
         WB_CHECK(make_map_2d(ctx, &mw, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, base + w.off_main, (uint64_t)w.K, (uint64_t)w.N,
-                             tc::BK, tc::BN, true));
+                             tc::BK, tc::BN * nh, true));
         p.qz = nullptr, p.sc = nullptr, p.zcols = 0, p.group_blocks = 1;
-        e = launch_tc_mt<true>(mt, mx, mw, p, grid, ctx->stream);
+        e = launch_tc_mt<true>(mt, nh, mx, mw, p, grid, ctx->stream);
     }
     ctx->launches++;
     WB_CUDA(e);
