@@ -3,17 +3,21 @@
 // (src/gpu/kernels/gemm/gemm_nt_f16_from_f32.wgsl:39-95), the tiled GEMM behind QwenGpt.gemm for M > 1
 // (src/model/qwen.ts:613-617).
 //
-// One CTA computes a 128 (output columns n) x MT (tokens m) tile of C^T: the weight tile is the 128-row
-// operand of tcgen05.mma, the activation tile its MT-column operand, the f32 accumulator lives in TMEM
-// (128 lanes x MT columns). Roles, 10 warps:
+// One CTA computes a (128 * NH output columns n) x (MT tokens m) tile of C^T, NH = 1 or 2: each 128-column half of
+// the weight tile is the 128-row operand of a tcgen05.mma, the activation tile the MT-column operand both halves
+// share, and each half has its f32 accumulator in TMEM (128 lanes x MT columns). With NH = 2 an activation tile
+// fetched from L2 feeds twice the arithmetic. Roles, 18 warps:
 //   warp 0      TMA producer: per 64-k block one box of activations [MT x 64] fp16 (128-byte swizzle) and
-//               one box of packed weights [8 packed rows x 128 columns] int32, into a 4-stage ring.
-//   warp 1      allocates TMEM, then one elected lane issues 4 x tcgen05.mma (K = 16 each) per block and
+//               one box of packed weights [8 packed rows x 128 * NH columns] int32, into a ring of 4 stages
+//               (3 when 4 do not fit the shared memory).
+//   warp 1      allocates TMEM, then one elected lane issues 4 x NH tcgen05.mma (K = 16 each) per block and
 //               commits the stage back to the producer.
-//   warps 2-9   unpack: two threads per column n, each turns 4 of its 8 words into 32 fp16 values w = (q - zero) * scale
+//   warps 2-17  unpack: each thread turns 2 * NH words of one column into fp16 values w = (q - zero) * scale
 //               (exact integer in fp16, one rounding in the multiply: the fp16 weight the reference
 //               uploads, src/gpu/buffer.ts:103-120) and stores them as the K-major, 128-byte-swizzled
-//               operand tile; afterwards the same warps drain TMEM (tcgen05.ld), add the bias and store.
+//               operand tile; the group's scale and zero point are requested one group ahead. Afterwards the
+//               same warps drain TMEM (tcgen05.ld), add the bias and store.
+// The unpack bounds the kernel (with its stores left out the rest runs at 0.84 of the cuBLAS fp16 rate).
 // Every wait on an mbarrier is bounded: when a wait gives up it raises a CTA-wide abort flag, records a
 // code in the context's status word, and all roles fall through to the common exit where TMEM is freed.
 #include <cuda.h>
@@ -26,7 +30,8 @@ namespace tc {
 
 constexpr int BN = 128;       // output columns per accumulator (UMMA M); a CTA holds NH = 1 or 2 of them
 constexpr int BK = 64;        // k per stage: one 128-byte swizzle atom of fp16
-constexpr int THREADS = 320;
+constexpr int UNPACK_WARPS = 16;  // a multiple of 4: they also drain TMEM, one lane quarter per warp % 4
+constexpr int THREADS = 64 + 32 * UNPACK_WARPS;
 constexpr uint32_t SPIN_LIMIT = 1u << 20;
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -151,12 +156,9 @@ struct Smem {
     static constexpr int WD_BYTES = COLS * BK * 2;
     static constexpr int WP_BYTES = DENSE ? 0 : 8 * COLS * 4;
     static constexpr int STAGE_BYTES = X_BYTES + WD_BYTES + WP_BYTES;  // every piece is a multiple of 1024
-#ifdef WB_EXP_STAGES
-    static constexpr int STAGES = WB_EXP_STAGES;
-#else
     static constexpr int STAGES = (4 * STAGE_BYTES + 1280 <= 227 * 1024) ? 4 : 3;
-#endif
     static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    static_assert(TOTAL <= 227 * 1024, "tile does not fit the shared memory of one CTA");
     
 };
 
@@ -190,7 +192,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
             mbar_init(&full[s], 1);
-            mbar_init(&deq[s], 8);
+            mbar_init(&deq[s], UNPACK_WARPS);
             mbar_init(&empty[s], 1);
         }
         mbar_init(acc_full, 1);
@@ -243,7 +245,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         __syncwarp();
     } else {
         // ------------------------------------------------------------------ unpack, then epilogue
-        constexpr int RPT = 4 * NH;                    // packed rows of a k-block per thread: 256 threads, 8 rows x COLS words
+        constexpr int RPT = 8 * COLS / (32 * UNPACK_WARPS);  // packed rows of a k-block per thread: 8 rows x COLS words in all
         const int tn = (threadIdx.x - 64) % COLS;      // column of the tile
         const int rhalf = (threadIdx.x - 64) / COLS;   // which RPT of the 8 packed rows
         bool ok = true;
@@ -280,9 +282,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 uint8_t *dst_row = wd(s) + tn * 128;
 #pragma unroll
                 for (int rr = 0; rr < RPT; rr++) {
-#ifdef WB_EXP_NOSTS
-                    if (p.M > 0) break;
-#endif
                     const int r = rhalf * RPT + rr;
                     uint32_t w = src[r * COLS];
                     const uint32_t lo0 = (w & 0x000f000fu) | 0x64006400u;
@@ -317,10 +316,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             // split-K: slices write f32 partial sums, splitk_reduce_kernel adds them and the bias
             constexpr bool split = SPLIT;
             float *part = SPLIT ? p.partial + (int64_t)blockIdx.z * p.M * p.N : nullptr;
-            // the two warps that share a TMEM lane quarter split the columns
-            constexpr int CSPAN = MT >= 32 ? MT / 2 : MT;
-            const int c_begin = MT >= 32 ? ((warp - 2) >> 2) * CSPAN : 0;
-            const int c_end = (MT >= 32 || warp < 6) ? c_begin + CSPAN : 0;
+            // the warps that share a TMEM lane quarter split the columns
+            constexpr int SHARE = UNPACK_WARPS / 4;                      // warps per lane quarter
+            constexpr int NSPLIT = MT / 16 < SHARE ? MT / 16 : SHARE;    // how many of them get columns (16 at a time)
+            constexpr int CSPAN = MT / NSPLIT;
+            const int c_begin = ((warp - 2) >> 2) * CSPAN;
+            const int c_end = ((warp - 2) >> 2) < NSPLIT ? c_begin + CSPAN : c_begin;
 #pragma unroll 1
             for (int h = 0; h < NH; h++) {
             const int n = n0 + h * BN + q * 32 + lane;
@@ -418,8 +419,9 @@ static void pick_tile(int64_t M, int64_t N, int sms, int *mt_out, int *nh_out)
     if (M <= 32) { *mt_out = 32; return; }
     if (M <= 64) { *mt_out = 64; return; }
     static const int force_nh = getenv("WEBLLM_B200_GEMM_NH") ? atoi(getenv("WEBLLM_B200_GEMM_NH")) : 0;
-    // relative time of one k-block of a tile, measured: {mt, nh, cost}
-    static const int shapes[4][3] = {{256, 1, 100}, {128, 1, 85}, {256, 2, 115}, {128, 2, 95}};
+    // {mt, nh, time of one k-block of such a tile in 10 ns units, measured}: the unpack of the weight tile bounds all
+    // four, so the tile with the most tokens per unpacked column wins unless it adds waves
+    static const int shapes[4][3] = {{256, 1, 70}, {128, 1, 63}, {256, 2, 97}, {128, 2, 87}};
     int best_mt = 256, best_nh = 1;
     int64_t best_cost = -1;
     for (const auto &sh : shapes) {
