@@ -411,55 +411,58 @@ bool gemm_tc_supports(const Weight &w, int64_t M)
     return w.kind == WeightKind::DenseF16;
 }
 
-// Tokens (mt) and output columns (128 * nh) of a CTA's tile.
-static void pick_tile(int64_t M, int64_t N, int sms, int *mt_out, int *nh_out)
+static int env_int(const char *name)
 {
-    *nh_out = 1;
-    if (M <= 16) { *mt_out = 16; return; }
-    if (M <= 32) { *mt_out = 32; return; }
-    if (M <= 64) { *mt_out = 64; return; }
-    static const int force_nh = getenv("WEBLLM_B200_GEMM_NH") ? atoi(getenv("WEBLLM_B200_GEMM_NH")) : 0;
-    // {mt, nh, time of one k-block of such a tile in 10 ns units, measured}: the unpack of the weight tile bounds all
-    // four, so the tile with the most tokens per unpacked column wins unless it adds waves
-    static const int shapes[4][3] = {{256, 1, 70}, {128, 1, 63}, {256, 2, 97}, {128, 2, 87}};
-    int best_mt = 256, best_nh = 1;
-    int64_t best_cost = -1;
-    for (const auto &sh : shapes) {
-        const int mt = sh[0], nh = sh[1];
-        if (M <= 128 && mt == 256) continue;
-        if (force_nh && nh != force_nh) continue;
-        if (nh == 2 && N < 256) continue;
-        const int64_t tiles = ((M + mt - 1) / mt) * ((N + 128 * nh - 1) / (128 * nh));
-        const int64_t waves = (tiles + sms - 1) / sms;
-        const int64_t cost = waves * sh[2];
-        if (best_cost < 0 || cost < best_cost) best_mt = mt, best_nh = nh, best_cost = cost;
+    const char *v = getenv(name);
+    return v ? atoi(v) : 0;
+}
+
+// Tile (mt tokens x 128 * nh output columns) and number of K slices, by a small cost model in microseconds whose
+// constants are measurements: the time of one 64-k block of a tile (the unpack of the weight tile bounds it, so it
+// depends on the columns far more than on the tokens), a fixed time per tile (pipeline fill, TMEM drain and stores),
+// and for split-K the reduce launch, which moves slices + 1 copies of the output.
+// WEBLLM_B200_GEMM_MT / _NH / _SPLIT pin one of the three for experiments.
+static void pick_plan(int64_t M, int64_t N, int kblocks, int sms, int force_split, int *mt_out, int *nh_out, int *s_out)
+{
+    static const int force_mt = env_int("WEBLLM_B200_GEMM_MT"), force_nh = env_int("WEBLLM_B200_GEMM_NH"),
+                     env_split = env_int("WEBLLM_B200_GEMM_SPLIT");
+    if (force_split <= 0) force_split = env_split;
+    static const int mts[5] = {16, 32, 64, 128, 256};
+    double best = -1.;
+    *mt_out = 128, *nh_out = 1, *s_out = 1;
+    for (int mt : mts) {
+        // up to 128 tokens the smallest tile that holds them, above that 128 or 256
+        const bool fits = M > 128 ? mt >= 128 : (mt >= M && (mt == 16 || mt < 2 * M));
+        if (force_mt ? mt != force_mt : !fits) continue;
+        for (int nh = 1; nh <= 2; nh++) {
+            if (force_nh ? nh != force_nh : false) continue;
+            if (nh == 2 && (mt < 128 || N < 256)) continue;
+            const double t_kb = nh == 2 ? (mt == 256 ? 0.97 : 0.87) : (mt == 256 ? 0.70 : 0.63);
+            const double t_tile = 1.5 + 2.7 * nh * mt / 256.;
+            const int64_t tiles = ((M + mt - 1) / mt) * ((N + 128 * nh - 1) / (128 * nh));
+            for (int S = 1; S <= 16; S++) {
+                if (force_split > 0 ? S != (force_split < kblocks ? force_split : kblocks) : (S > 1 && kblocks / S < 8)) continue;
+                const int per = (kblocks + S - 1) / S;
+                if ((kblocks + per - 1) / per != S) continue;  // would leave an empty slice
+                if (S > 1 && (double)S * M * N * 4. > 64e6) continue;  // partial sums must fit the workspace
+                const int64_t waves = (tiles * S + sms - 1) / sms;
+                double t = 2.0 + waves * (per * t_kb + t_tile);
+                if (S > 1) t += 2.5 + (S + 1) * (double)M * N * 4. / 4e6;
+                if (best < 0. || t < best) best = t, *mt_out = mt, *nh_out = nh, *s_out = S;
+            }
+        }
     }
-    *mt_out = best_mt, *nh_out = best_nh;
 }
 
 int plan_gemm_tc(wb_context *ctx, const Weight &w, int64_t M, int act_dtype, int exact, wb_plan *plan)
 {
     (void)exact;
-    int mt, nh;
-    pick_tile(M, w.N, ctx->sm_count, &mt, &nh);
+    const int kblocks = (int)(w.K / 64);
+    int mt, nh, S;
+    pick_plan(M, w.N, kblocks, ctx->sm_count, ctx->force_split, &mt, &nh, &S);
     plan->kernel = WB_KERNEL_GEMM_TC;
     plan->grid_x = (int)((M + mt - 1) / mt);
     plan->grid_y = (int)((w.N + 128 * nh - 1) / (128 * nh));
-    // Split-K when the tiles would leave most of the GPU idle and K is long (a tile walks its k-blocks one after the
-    // other at ~0.75 us each): slices of at least 8 k-blocks, as many as fill the SMs, partial sums in the workspace
-    // after the fp16 staging of the activations, then one reduce launch.
-    const int kblocks = (int)(w.K / 64);
-    const int64_t tiles = (int64_t)plan->grid_x * plan->grid_y;
-    int S = 1;
-    if (ctx->force_split > 0) S = ctx->force_split;
-    else if (tiles * 2 <= ctx->sm_count && kblocks >= 16) {
-        S = (int)(ctx->sm_count / tiles);
-        if (S > kblocks / 8) S = kblocks / 8;
-    }
-    if (S > kblocks) S = kblocks;
-    if (S < 1) S = 1;
-    const int per = (kblocks + S - 1) / S;
-    S = (kblocks + per - 1) / per;  // drop empty slices
     plan->split_k = S;
     plan->grid_z = S;
     plan->block = tc::THREADS;
