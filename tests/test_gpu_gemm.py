@@ -1,5 +1,9 @@
 """GPU parity: the tcgen05 / TMEM GEMM (int4 unpack in shared memory, and dense fp16 weights) against
 gemmNTRef on the fp16 weights the reference keeps on the device, through the C ABI."""
+import os
+import subprocess
+import sys
+
 import numpy as np
 import pytest
 
@@ -158,3 +162,24 @@ def test_split_k_gemm_when_few_tiles(gpu, oracle, M, act):
         gpu.synchronize()
     finally:
         gpu.plan_override(0, 0)
+
+
+def test_planner_uses_the_wide_tile_and_split_k_at_prefill_sizes(gpu, oracle):
+    """256 output columns per CTA (two accumulators sharing one activation tile) where the tiles still fill the GPU,
+    K slices where they would not; N = 896 is not a multiple of 256, so the last column tile is half empty."""
+    h, _ = _weight(gpu, oracle, "gate", 896, 4864)
+    p = gpu.plan(h, 2048, "f16")
+    assert (p["tile_m"], p["tile_n"], p["split_k"]) == (256, 256, 1) and p["grid_y"] == 19
+    h, _ = _weight(gpu, oracle, "down", 4864, 896)
+    p = gpu.plan(h, 2048, "f16")
+    assert p["tile_n"] == 256 and p["split_k"] > 1 and p["grid_y"] == 4
+
+
+@pytest.mark.skipif(os.environ.get("WEBLLM_B200_GEMM_NH") is not None, reason="already the forced run")
+def test_every_tile_shape_with_two_accumulators():
+    """The tile switches are read once per process, so the ragged-M, dense and split-K cases above run again in a
+    child process with the 256-column tile forced for every token count from 100 up (128 x 256 and 256 x 256)."""
+    env = dict(os.environ, WEBLLM_B200_GEMM_NH="2")
+    r = subprocess.run([sys.executable, "-m", "pytest", __file__, "-q", "-x", "-k", "ragged or dense or split_k_gemm or 7b"],
+                       env=env, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
