@@ -208,14 +208,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
+            int s = 0;
+            uint32_t ph = 0;
             for (int kb = kb0; kb < KB; kb++) {
-                const int s = (kb - kb0) % STAGES;
-                const uint32_t ph = ((kb - kb0) / STAGES) & 1;
                 if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 1)) break;
                 mbar_expect_tx(&full[s], S::X_BYTES + (DENSE ? S::WD_BYTES : S::WP_BYTES));
                 tma_load_2d(xs(s), &map_x, kb * BK, m0, &full[s]);
                 if constexpr (DENSE) tma_load_2d(wd(s), &map_w, kb * BK, n0, &full[s]);
                 else tma_load_2d(wp(s), &map_w, n0, kb * 8, &full[s]);
+                if (++s == STAGES) s = 0, ph ^= 1;
             }
         }
     } else if (warp == 1) {
@@ -223,9 +224,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         if (lane == 0) {
             constexpr uint32_t idesc = idesc_f16(BN, MT);
             bool ok = true;
+            int s = 0;
+            uint32_t ph = 0;
             for (int kb = kb0; kb < KB && ok; kb++) {
-                const int s = (kb - kb0) % STAGES;
-                const uint32_t ph = ((kb - kb0) / STAGES) & 1;
                 ok = mbar_wait(&full[s], ph, abort_flag, p.status, 2);
                 if (ok && !DENSE) ok = mbar_wait(&deq[s], ph, abort_flag, p.status, 3);
                 if (!ok) break;
@@ -239,6 +240,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                         umma_f16(tmem_base + h * ACC_COLS, a0 + 1024 * h + 2 * k, b0 + 2 * k, idesc, ((kb - kb0) | k) != 0);
                 }
                 umma_commit(&empty[s]);
+                if (++s == STAGES) s = 0, ph ^= 1;
             }
             if (ok) umma_commit(acc_full);
         }
@@ -265,25 +267,34 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                     if (p.qz) next_zeros = p.qz[(int64_t)g * p.zcols + (n >> 3)];
                 }
             };
-            request_group(kb0 / p.group_blocks);
+            int group = kb0 / p.group_blocks;
+            int blocks_left = 0;  // k-blocks until the next group starts; 0 at the slice start takes the first group in
+            request_group(group);
+            // loop-invariant addressing: the thread's first word in a stage and the swizzled 16-byte slots it fills
+            const int src_off = S::X_BYTES + S::WD_BYTES + (tn + rhalf * RPT * COLS) * 4;
+            int dst_off[RPT];
+#pragma unroll
+            for (int rr = 0; rr < RPT; rr++)  // 16-byte chunk r of row tn, at its 128-byte-swizzle position
+                dst_off[rr] = S::X_BYTES + tn * 128 + (((rhalf * RPT + rr) ^ (tn & 7)) << 4);
+            int s = 0;
+            uint32_t ph = 0;
+            uint8_t *stage = smem;
             for (int kb = kb0; kb < KB; kb++) {
-                const int s = (kb - kb0) % STAGES;
-                const uint32_t ph = ((kb - kb0) / STAGES) & 1;
-                if (kb == kb0 || kb % p.group_blocks == 0) {
+                if (blocks_left == 0) {
                     const float z = (float)(((next_zeros >> ((n & 7) * 4)) & 15u) + 1u);
                     scale2 = __half2half2(next_scale);
                     zsub = __float2half2_rn(1024.f + z);
                     zfma = __float2half2_rn(-(64.f + z));
-                    request_group(kb / p.group_blocks + 1);
+                    blocks_left = p.group_blocks - (kb == kb0 ? kb0 % p.group_blocks : 0);
+                    request_group(++group);
                 }
+                blocks_left--;
                 ok = mbar_wait(&full[s], ph, abort_flag, p.status, 4);
                 if (!ok) break;
-                const uint32_t *src = wp(s) + tn;
-                uint8_t *dst_row = wd(s) + tn * 128;
+                const uint32_t *src = (const uint32_t *)(stage + src_off);
 #pragma unroll
                 for (int rr = 0; rr < RPT; rr++) {
-                    const int r = rhalf * RPT + rr;
-                    uint32_t w = src[r * COLS];
+                    uint32_t w = src[rr * COLS];
                     const uint32_t lo0 = (w & 0x000f000fu) | 0x64006400u;
                     const uint32_t hi0 = (w & 0x00f000f0u) | 0x64006400u;
                     w >>= 8;
@@ -300,12 +311,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                     o.y = __byte_perm(uc, ud, 0x5410);
                     o.z = __byte_perm(ua, ub, 0x7632);
                     o.w = __byte_perm(uc, ud, 0x7632);
-                    // 16-byte chunk r of row tn, at its 128-byte-swizzle position
-                    *(uint4 *)(dst_row + ((r ^ (tn & 7)) << 4)) = o;
+                    *(uint4 *)(stage + dst_off[rr]) = o;
                 }
                 fence_async_smem();  // make the generic-proxy stores visible to the tensor core's reads
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&deq[s]);
+                stage += S::STAGE_BYTES;
+                if (++s == STAGES) s = 0, ph ^= 1, stage = smem;
             }
         }
         // epilogue: warp w may touch TMEM lanes 32*(w%4) .. +31
@@ -435,7 +447,7 @@ static void pick_plan(int64_t M, int64_t N, int kblocks, int sms, int force_spli
         const bool fits = M > 128 ? mt >= 128 : (mt >= M && (mt == 16 || mt < 2 * M));
         if (force_mt ? mt != force_mt : !fits) continue;
         for (int nh = 1; nh <= 2; nh++) {
-            if (force_nh ? nh != force_nh : false) continue;
+            if (force_nh && nh != force_nh && mt >= 128 && N >= 256) continue;  // pinned wherever it exists
             if (nh == 2 && (mt < 128 || N < 256)) continue;
             const double t_kb = nh == 2 ? (mt == 256 ? 0.97 : 0.87) : (mt == 256 ? 0.70 : 0.63);
             const double t_tile = 1.5 + 2.7 * nh * mt / 256.;
