@@ -164,15 +164,20 @@ def test_split_k_gemm_when_few_tiles(gpu, oracle, M, act):
         gpu.plan_override(0, 0)
 
 
-def test_planner_uses_the_wide_tile_and_split_k_at_prefill_sizes(gpu, oracle):
-    """256 output columns per CTA (two accumulators sharing one activation tile) where the tiles still fill the GPU,
-    K slices where they would not; N = 896 is not a multiple of 256, so the last column tile is half empty."""
-    h, _ = _weight(gpu, oracle, "gate", 896, 4864)
-    p = gpu.plan(h, 2048, "f16")
-    assert (p["tile_m"], p["tile_n"], p["split_k"]) == (256, 256, 1) and p["grid_y"] == 19
-    h, _ = _weight(gpu, oracle, "down", 4864, 896)
-    p = gpu.plan(h, 2048, "f16")
-    assert p["tile_n"] == 256 and p["split_k"] > 1 and p["grid_y"] == 4
+def test_planner_picks_tile_and_slices_together(gpu, oracle):
+    """The plan is self-consistent for either tile width, K is cut into slices where the tiles alone would leave
+    SMs idle (down at M = 2048: 56 or 32 tiles for 148 SMs), and a long-K, many-tile shape takes 256 output columns
+    per CTA (two accumulators sharing one activation tile)."""
+    for name, K, N in (("gate", 896, 4864), ("down", 4864, 896)):
+        h, _ = _weight(gpu, oracle, name, K, N)
+        p = gpu.plan(h, 2048, "f16")
+        assert p["tile_n"] in (128, 256) and p["tile_m"] in (128, 256)
+        assert p["grid_y"] == -(-N // p["tile_n"]) and p["grid_x"] == -(-2048 // p["tile_m"])
+        assert (p["split_k"] > 1) == (name == "down") and p["grid_z"] == p["split_k"]
+    if os.environ.get("WEBLLM_B200_GEMM_NH") is None:
+        h, _ = _weight(gpu, oracle, "q7", 3584, 3584, zeros="7or8")
+        p = gpu.plan(h, 4096, "f16")
+        assert (p["tile_m"], p["tile_n"], p["split_k"]) == (256, 256, 1)
 
 
 @pytest.mark.skipif(os.environ.get("WEBLLM_B200_GEMM_NH") is not None, reason="already the forced run")

@@ -12,12 +12,13 @@
 //               (3 when 4 do not fit the shared memory).
 //   warp 1      allocates TMEM, then one elected lane issues 4 x NH tcgen05.mma (K = 16 each) per block and
 //               commits the stage back to the producer.
-//   warps 2-17  unpack: each thread turns 2 * NH words of one column into fp16 values w = (q - zero) * scale
-//               (exact integer in fp16, one rounding in the multiply: the fp16 weight the reference
-//               uploads, src/gpu/buffer.ts:103-120) and stores them as the K-major, 128-byte-swizzled
-//               operand tile; the group's scale and zero point are requested one group ahead. Afterwards the
-//               same warps drain TMEM (tcgen05.ld), add the bias and store.
-// The unpack bounds the kernel (with its stores left out the rest runs at 0.84 of the cuBLAS fp16 rate).
+//   warps 2-17  unpack, in 4 / NH sets of one thread per column that take the k-blocks in turn: a thread turns
+//               the 8 words of its column into 64 fp16 values w = (q - zero) * scale (exact integer in fp16, one
+//               rounding in the multiply: the fp16 weight the reference uploads, src/gpu/buffer.ts:103-120) and
+//               stores them as the K-major, 128-byte-swizzled operand tile; the scale and zero point of the
+//               set's next k-block are requested while the current one is unpacked. Afterwards the same warps
+//               drain TMEM (tcgen05.ld), add the bias and store.
+// With the unpack's work left out the rest of the kernel runs at 0.84 of the cuBLAS fp16 rate; with it, at 0.82.
 // Every wait on an mbarrier is bounded: when a wait gives up it raises a CTA-wide abort flag, records a
 // code in the context's status word, and all roles fall through to the common exit where TMEM is freed.
 #include <cuda.h>
@@ -171,6 +172,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     constexpr int COLS = S::COLS;
     constexpr uint32_t ACC_COLS = MT < 32 ? 32 : MT;  // TMEM columns of one accumulator
     constexpr uint32_t TMEM_COLS = ACC_COLS * NH;
+    // The unpack warps form KG sets of one thread per column; set g unpacks k-blocks g, g + KG, ... so that KG
+    // k-blocks are in the works at once and a warp pays the waits and the fence of a block once per 8 packed rows.
+    constexpr int KG = 32 * UNPACK_WARPS / COLS;
+    static_assert(KG <= STAGES && UNPACK_WARPS % KG == 0 && (32 * UNPACK_WARPS / KG) % COLS == 0, "unpack sets");
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t *bars = (uint64_t *)(smem + STAGES * S::STAGE_BYTES);
@@ -192,7 +197,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
             mbar_init(&full[s], 1);
-            mbar_init(&deq[s], UNPACK_WARPS);
+            mbar_init(&deq[s], UNPACK_WARPS / KG);
             mbar_init(&empty[s], 1);
         }
         mbar_init(acc_full, 1);
@@ -247,9 +252,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         __syncwarp();
     } else {
         // ------------------------------------------------------------------ unpack, then epilogue
-        constexpr int RPT = 8 * COLS / (32 * UNPACK_WARPS);  // packed rows of a k-block per thread: 8 rows x COLS words in all
-        const int tn = (threadIdx.x - 64) % COLS;      // column of the tile
-        const int rhalf = (threadIdx.x - 64) / COLS;   // which RPT of the 8 packed rows
+        constexpr int SET_THREADS = 32 * UNPACK_WARPS / KG;
+        constexpr int RPT = 8 * COLS / SET_THREADS;    // packed rows of a k-block per thread: 8 rows x COLS words in all
+        const int kg = (threadIdx.x - 64) / SET_THREADS;          // which set
+        const int tn = (threadIdx.x - 64) % SET_THREADS % COLS;   // column of the tile
+        const int rhalf = (threadIdx.x - 64) % SET_THREADS / COLS;  // which RPT of the 8 packed rows
         bool ok = true;
         if constexpr (!DENSE) {
             const int n = n0 + tn;
@@ -267,30 +274,37 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                     if (p.qz) next_zeros = p.qz[(int64_t)g * p.zcols + (n >> 3)];
                 }
             };
-            int group = kb0 / p.group_blocks;
-            int blocks_left = 0;  // k-blocks until the next group starts; 0 at the slice start takes the first group in
-            request_group(group);
+            // the set's first k-block, its group and position in the group; both advance without a division
+            int group = (kb0 + kg) / p.group_blocks, in_group = (kb0 + kg) % p.group_blocks;
+            bool fresh = true;  // next_scale / next_zeros hold a group that is not applied yet
+            if (kb0 + kg < KB) request_group(group);
             // loop-invariant addressing: the thread's first word in a stage and the swizzled 16-byte slots it fills
             const int src_off = S::X_BYTES + S::WD_BYTES + (tn + rhalf * RPT * COLS) * 4;
             int dst_off[RPT];
 #pragma unroll
             for (int rr = 0; rr < RPT; rr++)  // 16-byte chunk r of row tn, at its 128-byte-swizzle position
                 dst_off[rr] = S::X_BYTES + tn * 128 + (((rhalf * RPT + rr) ^ (tn & 7)) << 4);
-            int s = 0;
+            int s = kg;
             uint32_t ph = 0;
-            uint8_t *stage = smem;
-            for (int kb = kb0; kb < KB; kb++) {
-                if (blocks_left == 0) {
+            for (int kb = kb0 + kg; kb < KB; kb += KG) {
+                if (fresh) {
                     const float z = (float)(((next_zeros >> ((n & 7) * 4)) & 15u) + 1u);
                     scale2 = __half2half2(next_scale);
                     zsub = __float2half2_rn(1024.f + z);
                     zfma = __float2half2_rn(-(64.f + z));
-                    blocks_left = p.group_blocks - (kb == kb0 ? kb0 % p.group_blocks : 0);
-                    request_group(++group);
+                    fresh = false;
                 }
-                blocks_left--;
+                // the group of the set's next k-block is requested now and lands while this one is unpacked
+                in_group += KG;
+                if (in_group >= p.group_blocks) {
+                    do in_group -= p.group_blocks, group++;
+                    while (in_group >= p.group_blocks);
+                    request_group(group);
+                    fresh = true;
+                }
                 ok = mbar_wait(&full[s], ph, abort_flag, p.status, 4);
                 if (!ok) break;
+                uint8_t *stage = smem + s * S::STAGE_BYTES;
                 const uint32_t *src = (const uint32_t *)(stage + src_off);
 #pragma unroll
                 for (int rr = 0; rr < RPT; rr++) {
@@ -316,8 +330,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 fence_async_smem();  // make the generic-proxy stores visible to the tensor core's reads
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&deq[s]);
-                stage += S::STAGE_BYTES;
-                if (++s == STAGES) s = 0, ph ^= 1, stage = smem;
+                s += KG;
+                if (s >= STAGES) s -= STAGES, ph ^= 1;
             }
         }
         // epilogue: warp w may touch TMEM lanes 32*(w%4) .. +31
@@ -449,7 +463,7 @@ static void pick_plan(int64_t M, int64_t N, int kblocks, int sms, int force_spli
         for (int nh = 1; nh <= 2; nh++) {
             if (force_nh && nh != force_nh && mt >= 128 && N >= 256) continue;  // pinned wherever it exists
             if (nh == 2 && (mt < 128 || N < 256)) continue;
-            const double t_kb = nh == 2 ? (mt == 256 ? 0.97 : 0.87) : (mt == 256 ? 0.70 : 0.63);
+            const double t_kb = nh == 2 ? (mt == 256 ? 0.91 : 0.80) : (mt == 256 ? 0.62 : 0.55);
             const double t_tile = 1.5 + 2.7 * nh * mt / 256.;
             const int64_t tiles = ((M + mt - 1) / mt) * ((N + 128 * nh - 1) / (128 * nh));
             for (int S = 1; S <= 16; S++) {
