@@ -75,8 +75,9 @@ __global__ void __launch_bounds__(256, 2) gptq_gemv_stream_kernel(const GemvPara
     float *xsum = reinterpret_cast<float *>(smem_u4 + (size_t)(n_rows + 1) * p.xs_stride);  // [M][chunks_cta]
     float *red = xsum + ((p.M * chunks_cta + 3) & ~3);                                       // [8 warps][32 lanes][4]
 
-    // This warp's work is the sequence (tile j, chunk ch_begin + warp + 8 i); `pf` is the position two steps ahead.
-    // The first two chunks are requested before anything else (and before the wait on the previous kernel).
+    // This warp's work is the sequence (tile j, chunk ch_begin + warp + 8 i); `pf` is the position of the next request.
+    // The first three chunks are requested before anything else (and before the wait on the previous kernel), so that
+    // three are in flight while the activations are staged; in the loop two are in flight behind the one in use.
     const uint32_t *wrow = p.qw + (int64_t)t * p.N + 4 * g;
     const int64_t row_step = (int64_t)4 * p.N;
     const int ch_first = ch_begin + warp;  // chunks_cta >= 20: every warp has chunks
@@ -84,16 +85,20 @@ __global__ void __launch_bounds__(256, 2) gptq_gemv_stream_kernel(const GemvPara
         const int tile = (int)blockIdx.x + j * (int)gridDim.x;
         stream_fetch(p, wrow + tile * 32, row_step, ch, tile * 32 + 4 * g, r);
     };
-    StreamRegs cur, nxt, nxt2;
+    // Three register buffers, used in turn by a loop unrolled three times: a buffer is refilled right after its chunk
+    // has been consumed and nothing is ever moved from one buffer to another (a move would wait for the load that it
+    // reads), so a warp has two chunks in flight while it computes and three while it waits or stages.
+    StreamRegs buf[3];
     int pf_j = 0, pf_ch = ch_first;
     auto pf_advance = [&]() {
         pf_ch += 8;
         if (pf_ch >= ch_end) pf_ch = ch_first, pf_j++;
     };
-    if (pf_j < tiles_cta) fetch_at(pf_j, pf_ch, cur);
-    pf_advance();
-    if (pf_j < tiles_cta) fetch_at(pf_j, pf_ch, nxt);
-    pf_advance();
+#pragma unroll
+    for (int u = 0; u < 3; u++) {
+        if (pf_j < tiles_cta) fetch_at(pf_j, pf_ch, buf[u]);
+        pf_advance();
+    }
     pdl_sync();
 
     // ---- stage the activations in the MMA's k-slot order (x0,x4)(x2,x6)(x1,x5)(x3,x7), hi and lo rows ----
@@ -124,6 +129,12 @@ __global__ void __launch_bounds__(256, 2) gptq_gemv_stream_kernel(const GemvPara
         o.z = h2_as_u32(__halves2half2(hi[1], hi[5]));
         o.w = h2_as_u32(__halves2half2(hi[3], hi[7]));
         xs[m * p.xs_stride + rl] = o;
+        // sum of the staged operand values of this 8-k slot, in a fixed order (the zero point multiplies it)
+        auto sum8 = [](const __half (&h)[8]) {
+            return ((__half2float(h[0]) + __half2float(h[4])) + (__half2float(h[2]) + __half2float(h[6]))) +
+                   ((__half2float(h[1]) + __half2float(h[5])) + (__half2float(h[3]) + __half2float(h[7])));
+        };
+        float sx = sum8(hi);
         if constexpr (HAS_LO) {
             __half lo[8];
 #pragma unroll
@@ -133,24 +144,14 @@ __global__ void __launch_bounds__(256, 2) gptq_gemv_stream_kernel(const GemvPara
             o.z = h2_as_u32(__halves2half2(lo[1], lo[5]));
             o.w = h2_as_u32(__halves2half2(lo[3], lo[7]));
             xs[(p.M + m) * p.xs_stride + rl] = o;
+            sx += sum8(lo);
         }
-    }
-    __syncthreads();
-    // per (row m, chunk): sum of the staged operand values (hi + lo), 16 threads per sum, fixed order
-    for (int idx = tid; idx < p.M * chunks_cta * 16; idx += 256) {
-        const int task = idx >> 4, rr = idx & 15;
-        const int m = task / chunks_cta, cl = task - m * chunks_cta;
-        auto sum8 = [](const uint4 &o) {
-            const float2 a = __half22float2(u32_as_h2(o.x)), b = __half22float2(u32_as_h2(o.y));
-            const float2 cc = __half22float2(u32_as_h2(o.z)), d = __half22float2(u32_as_h2(o.w));
-            return ((a.x + a.y) + (b.x + b.y)) + ((cc.x + cc.y) + (d.x + d.y));
-        };
-        float sx = sum8(xs[m * p.xs_stride + cl * 16 + rr]);
-        if constexpr (HAS_LO) sx += sum8(xs[(p.M + m) * p.xs_stride + cl * 16 + rr]);
+        // per (row m, chunk): the 16 slots of a chunk sit in one half-warp (rows_pad % 16 == 0), so the chunk's sum is
+        // a shuffle reduction in this same pass
         const unsigned half_mask = (lane & 16) ? 0xffff0000u : 0x0000ffffu;
 #pragma unroll
-        for (int o = 8; o > 0; o >>= 1) sx += __shfl_xor_sync(half_mask, sx, o);
-        if (rr == 0) xsum[task] = sx;
+        for (int o2 = 8; o2 > 0; o2 >>= 1) sx += __shfl_xor_sync(half_mask, sx, o2);
+        if ((rl & 15) == 0) xsum[m * chunks_cta + (rl >> 4)] = sx;
     }
     __syncthreads();
 
@@ -161,56 +162,54 @@ __global__ void __launch_bounds__(256, 2) gptq_gemv_stream_kernel(const GemvPara
     const uint4 *xrow = xs + (size_t)brow * p.xs_stride + t;
     const float *xsum_t = xsum + (t < p.M ? t : 0) * chunks_cta;  // this thread's outputs belong to batch row t
     __shared__ int is_last;
-    for (int j = 0; j < tiles_cta; j++) {
-        const int tile = (int)blockIdx.x + j * (int)gridDim.x;
-        const int c = tile * 32 + 4 * g;
-        float tot[4] = {0.f, 0.f, 0.f, 0.f};  // columns c .. c + 3 of batch row t
-        for (int ch = ch_first; ch < ch_end; ch += 8) {
-            if (pf_j < tiles_cta) fetch_at(pf_j, pf_ch, nxt2);
-            pf_advance();
-            const int rl0 = (ch - ch_begin) * 16;
-            float ae[2][4], ao[2][4];
+    const int zshift = ((4 * g) & 7) * 4;  // nibble of column 4 g in its zero word (tiles start at multiples of 32)
+
+    // one 128-k chunk of one column tile: 16 MMAs, then scale and zero point
+    auto chunk_step = [&](const StreamRegs &cur, int ch, float (&tot)[4]) {
+        const int rl0 = (ch - ch_begin) * 16;
+        float ae[2][4], ao[2][4];
 #pragma unroll
-            for (int st = 0; st < 4; st++) {
-                uint32_t e0[4], e1[4], o0[4], o1[4];
-                const uint32_t wv[4] = {cur.w[st].x, cur.w[st].y, cur.w[st].z, cur.w[st].w};
-#pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    const uint32_t w8 = wv[i] >> 8;
-                    e0[i] = wv[i] & 0x000f000fu;
-                    o0[i] = wv[i] & 0x00f000f0u;
-                    e1[i] = w8 & 0x000f000fu;
-                    o1[i] = w8 & 0x00f000f0u;
-                }
-                const uint4 xb = xrow[rl0 + st * 4];
-                if (st == 0) {
-                    mma_16816_zero(ae[0], e0[0], e0[1], e1[0], e1[1], xb.x, xb.y);
-                    mma_16816_zero(ao[0], o0[0], o0[1], o1[0], o1[1], xb.z, xb.w);
-                    mma_16816_zero(ae[1], e0[2], e0[3], e1[2], e1[3], xb.x, xb.y);
-                    mma_16816_zero(ao[1], o0[2], o0[3], o1[2], o1[3], xb.z, xb.w);
-                } else {
-                    mma_16816(ae[0], e0[0], e0[1], e1[0], e1[1], xb.x, xb.y);
-                    mma_16816(ao[0], o0[0], o0[1], o1[0], o1[1], xb.z, xb.w);
-                    mma_16816(ae[1], e0[2], e0[3], e1[2], e1[3], xb.x, xb.y);
-                    mma_16816(ao[1], o0[2], o0[3], o1[2], o1[3], xb.z, xb.w);
-                }
-            }
-            // epilogue of the chunk: accumulator elements (0, 1) = (hi, lo) of column c + 2s, (2, 3) of column c + 2s + 1
-            const float2 s01 = __half22float2(u32_as_h2(cur.s.x)), s23 = __half22float2(u32_as_h2(cur.s.y));
-            const float scale[4] = {s01.x, s01.y, s23.x, s23.y};
-            const uint32_t zw = cur.z >> ((c & 7) * 4);
-            const float sx = xsum_t[ch - ch_begin];
+        for (int st = 0; st < 4; st++) {
+            uint32_t e0[4], e1[4], o0[4], o1[4];
+            const uint32_t wv[4] = {cur.w[st].x, cur.w[st].y, cur.w[st].z, cur.w[st].w};
 #pragma unroll
             for (int i = 0; i < 4; i++) {
-                const int s = i >> 1, e = (i & 1) * 2;
-                const float q = fmaf(ao[s][e], 0.0625f, ae[s][e]) + fmaf(ao[s][e + 1], 0.0625f, ae[s][e + 1]);
-                const float zp = (float)(((zw >> (4 * i)) & 15u) + 1u);
-                tot[i] = fmaf(scale[i], fmaf(q, 16777216.f, -zp * sx), tot[i]);
+                const uint32_t w8 = wv[i] >> 8;
+                e0[i] = wv[i] & 0x000f000fu;
+                o0[i] = wv[i] & 0x00f000f0u;
+                e1[i] = w8 & 0x000f000fu;
+                o1[i] = w8 & 0x00f000f0u;
             }
-            cur = nxt, nxt = nxt2;
+            const uint4 xb = xrow[rl0 + st * 4];
+            if (st == 0) {
+                mma_16816_zero(ae[0], e0[0], e0[1], e1[0], e1[1], xb.x, xb.y);
+                mma_16816_zero(ao[0], o0[0], o0[1], o1[0], o1[1], xb.z, xb.w);
+                mma_16816_zero(ae[1], e0[2], e0[3], e1[2], e1[3], xb.x, xb.y);
+                mma_16816_zero(ao[1], o0[2], o0[3], o1[2], o1[3], xb.z, xb.w);
+            } else {
+                mma_16816(ae[0], e0[0], e0[1], e1[0], e1[1], xb.x, xb.y);
+                mma_16816(ao[0], o0[0], o0[1], o1[0], o1[1], xb.z, xb.w);
+                mma_16816(ae[1], e0[2], e0[3], e1[2], e1[3], xb.x, xb.y);
+                mma_16816(ao[1], o0[2], o0[3], o1[2], o1[3], xb.z, xb.w);
+            }
         }
+        // accumulator elements (0, 1) = (hi, lo) of column c + 2s, (2, 3) of column c + 2s + 1
+        const float2 s01 = __half22float2(u32_as_h2(cur.s.x)), s23 = __half22float2(u32_as_h2(cur.s.y));
+        const float scale[4] = {s01.x, s01.y, s23.x, s23.y};
+        const uint32_t zw = cur.z >> zshift;
+        const float sx = xsum_t[ch - ch_begin];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int s = i >> 1, e = (i & 1) * 2;
+            const float q = fmaf(ao[s][e], 0.0625f, ae[s][e]) + fmaf(ao[s][e + 1], 0.0625f, ae[s][e + 1]);
+            const float zp = (float)(((zw >> (4 * i)) & 15u) + 1u);
+            tot[i] = fmaf(scale[i], fmaf(q, 16777216.f, -zp * sx), tot[i]);
+        }
+    };
 
-        // ---- reduce over the 8 warps (fixed order), then write / split-K through the workspace ----
+    // end of a column tile: reduce over the 8 warps (fixed order), then write / split-K through the workspace
+    auto tile_end = [&](int j, const float (&tot)[4]) {
+        const int tile = (int)blockIdx.x + j * (int)gridDim.x;
         *reinterpret_cast<float4 *>(red + (warp * 32 + lane) * 4) = make_float4(tot[0], tot[1], tot[2], tot[3]);
         __syncthreads();
         const int n_base = tile * 32;
@@ -250,6 +249,26 @@ __global__ void __launch_bounds__(256, 2) gptq_gemv_stream_kernel(const GemvPara
             }
         }
         __syncthreads();  // red and is_last are reused by the next tile
+    };
+
+    // Every warp of the CTA meets the same number of tile ends (one per tile), so the barriers inside tile_end match
+    // although each warp reaches them from its own place in the unrolled loop.
+    int j = 0, ch = ch_first;
+    float tot[4] = {0.f, 0.f, 0.f, 0.f};  // columns c .. c + 3 of batch row t
+    while (j < tiles_cta) {
+#pragma unroll
+        for (int u = 0; u < 3; u++) {
+            if (j >= tiles_cta) break;
+            chunk_step(buf[u], ch, tot);
+            if (pf_j < tiles_cta) fetch_at(pf_j, pf_ch, buf[u]);
+            pf_advance();
+            ch += 8;
+            if (ch >= ch_end) {
+                tile_end(j, tot);
+                tot[0] = tot[1] = tot[2] = tot[3] = 0.f;
+                ch = ch_first, j++;
+            }
+        }
     }
 }
 
