@@ -4,6 +4,8 @@
     python -m webllm_b200.probe gemm   K N M [--reps 2]
     python -m webllm_b200.probe decode [--steps 3] [--prompt 64] [--mode auto|graph|single] [--layers 24]
     python -m webllm_b200.probe sweep  [--which batch|big|all]
+    python -m webllm_b200.probe shard      [--m 4096]      (one process per GPU: run under torch.distributed.run)
+    python -m webllm_b200.probe dp-prefill [--seqs 256]    (one process per GPU: run under torch.distributed.run)
 
 ``gemv`` / ``gemm`` run one GPTQ-int4 linear (wb_linear) over ``copies`` separately registered copies of
 the same synthetic weight, so that consecutive launches read different memory (no L2 reuse between
@@ -13,6 +15,11 @@ only a sanity check (a profiler serialises kernels), the numbers that count come
 ``sweep`` is the timing table behind the batch-size sweep (M = 1 .. 64 over the seven 0.5B projection shapes)
 and the 7B-class shapes (M = 1 and M = 4096): each case is a command batch over weight copies larger than L2,
 replayed and timed with CUDA events (needs torch for the events).
+``shard`` times the 7B-class projections split by output columns over the ranks (decode M = 1 and prefill M = --m):
+the local product alone, and the local product followed by the NCCL all-gather of the ``[M, N/G]`` pieces.
+``dp-prefill`` runs independent 2048-token sequences through the 96 projections of the 0.5B-shaped model
+(q|k|v, o, gate|up, down per layer, fp16 activations), the sequences dealt round-robin to the ranks, weights
+replicated, no collective on the data path. Both time with CUDA events and report the slowest rank.
 """
 from __future__ import annotations
 
@@ -111,6 +118,130 @@ def _sweep(args) -> None:
                 case(name + "7b", K, N, (1, 4096))
 
 
+def _dist_init():
+    """Process group over the GPUs of one node: NCCL, one rank per GPU; a plain ``python -m`` run is world size 1."""
+    import os
+
+    import torch
+    import torch.distributed as dist
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29533")
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device(f"cuda:{local}"))
+    return torch, dist, rank, world, local
+
+
+def _timed_ranks(torch, dist, fn, reps: int) -> float:
+    """Device time of one call of ``fn`` in us: warm-up, barrier, CUDA events on the current stream, max over ranks."""
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        fn()
+    e1.record()
+    e1.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) * 1e3 / reps], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def _shard(args) -> None:
+    from . import parallel
+    torch, dist, rank, world, local = _dist_init()
+    stream = torch.cuda.Stream()  # kernels, collectives and events all go to this stream
+    torch.cuda.set_stream(stream)
+    host = parallel.TorchSlabGpu(local, weight_bytes=3 << 30, act_bytes=2 << 30)
+    gpu = host.gpu
+    try:
+        for name in ("q", "k", "gate", "down"):
+            K, N = synthetic.QWEN7B_SHAPES[name]
+            t = synthetic.random_gptq(K, N, 128, seed=1)
+            for M in (1, args.m):
+                # decode: rotate over copies so that a launch reads weights that are not in L2
+                copies = 1 if M > 1 else max(2, min(16, int(300e6 // (t.nbytes // world))))
+                lins = [parallel.ColumnShardedLinear(host, f"{name}7b_{M}_{i}", t) for i in range(copies)]
+                n_loc = lins[0].shard.count
+                gpu.arena.reset()
+                A = gpu.arena.alloc(M * K, [M, K], "f16")
+                Cl = gpu.arena.alloc(M * n_loc, [M, n_loc], "f16")
+                piece = host.view(Cl).view(M, n_loc)
+                out = torch.empty((world, M, n_loc), dtype=torch.float16, device=host.device)  # rank-major pieces
+
+                def local_only():
+                    for lin in lins:
+                        lin.local(A, Cl, M)
+
+                def with_gather():
+                    for lin in lins:
+                        lin.local(A, Cl, M)
+                        dist.all_gather_into_tensor(out, piece)
+
+                def with_gather_rowmajor():
+                    for lin in lins:
+                        lin.local(A, Cl, M)
+                        dist.all_gather_into_tensor(out, piece)
+                        out.permute(1, 0, 2).reshape(M, -1).contiguous()
+
+                reps = 5 if M > 1 else 3
+                us_l = _timed_ranks(torch, dist, local_only, reps) / copies
+                us_g = _timed_ranks(torch, dist, with_gather, reps) / copies
+                us_r = _timed_ranks(torch, dist, with_gather_rowmajor, reps) / copies if M > 1 else us_g
+                if rank == 0:
+                    tf = 2.0 * M * N * K / 1e6
+                    print(f"{name}7b K={K:5d} N={N:5d} M={M:4d} G={world}: local {us_l:8.2f} us, + all-gather {us_g:8.2f} us"
+                          f" ({tf / us_g:7.1f} TFLOP/s, {t.nbytes / us_g / 1e3:7.1f} GB/s of int4 weights over all ranks),"
+                          f" + row-major copy {us_r:8.2f} us; gathered {M * N * 2} bytes", flush=True)
+                for _ in lins:
+                    gpu.weight_pop()
+    finally:
+        host.close()
+        dist.destroy_process_group()
+
+
+def _dp_prefill(args) -> None:
+    from . import parallel
+    torch, dist, rank, world, local = _dist_init()
+    stream = torch.cuda.Stream()  # a command batch cannot be recorded on the default stream
+    torch.cuda.set_stream(stream)
+    host = parallel.TorchSlabGpu(local, weight_bytes=1 << 30, act_bytes=1 << 30)
+    gpu = host.gpu
+    try:
+        cfg = synthetic.QWEN25_05B
+        C, KV, I, M = cfg.n_embd, cfg.kv_dim, cfg.intermediate, 2048
+        shapes = (("qkv", C, C + 2 * KV), ("o", C, C), ("gateup", C, 2 * I), ("down", I, C))
+        tensors = {n: synthetic.random_gptq(K, N, 128, seed=3 + i) for i, (n, K, N) in enumerate(shapes)}
+        handles = []
+        for layer in range(cfg.n_layer):  # replicated weights, one registration per layer (186 MB > L2)
+            for n, K, N in shapes:
+                t = tensors[n]
+                handles.append((gpu.gptq_register(f"L{layer}.{n}", t.qweight, t.qzeros, t.scales, K, N, 128), K, N))
+        A = gpu.arena.alloc(M * max(C, I), dtype="f16")
+        Y = gpu.arena.alloc(M * 2 * I, dtype="f16")
+        mine = len(parallel.replica_share(args.seqs, rank, world))
+        with gpu.batch() as one_sequence:
+            for h, K, N in handles:
+                gpu.linear(h, A, Y, None, M)
+
+        def my_share():
+            for _ in range(mine):
+                one_sequence.submit()
+
+        us = _timed_ranks(torch, dist, my_share, 2)
+        if rank == 0:
+            flops = args.seqs * cfg.n_layer * 2.0 * M * (C * (C + 2 * KV) + C * C + C * 2 * I + I * C)
+            print(f"dp-prefill G={world}: {args.seqs} sequences x {M} tokens, {len(handles)} projections each: {us / 1e3:9.2f} ms,"
+                  f" {args.seqs * M / us * 1e6:12.0f} tokens/s, {flops / us / 1e6:8.1f} TFLOP/s over all ranks", flush=True)
+        one_sequence.destroy()
+    finally:
+        host.close()
+        dist.destroy_process_group()
+
+
 def main(argv=None) -> None:
     ap = argparse.ArgumentParser(prog="python -m webllm_b200.probe", description=__doc__.split("\n")[0])
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -127,8 +258,16 @@ def main(argv=None) -> None:
     d.add_argument("--layers", type=int, default=synthetic.QWEN25_05B.n_layer)
     w = sub.add_parser("sweep")
     w.add_argument("--which", choices=("batch", "big", "all"), default="all")
+    sh = sub.add_parser("shard")
+    sh.add_argument("--m", type=int, default=4096)
+    dp = sub.add_parser("dp-prefill")
+    dp.add_argument("--seqs", type=int, default=256)
     args = ap.parse_args(argv)
-    if args.cmd == "sweep":
+    if args.cmd == "shard":
+        _shard(args)
+    elif args.cmd == "dp-prefill":
+        _dp_prefill(args)
+    elif args.cmd == "sweep":
         _sweep(args)
     elif args.cmd == "gemv":
         _linear(args, args.m, args.act)
