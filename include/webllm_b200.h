@@ -156,6 +156,26 @@ WB_API int wb_gptq_dequant_f16(wb_context *ctx, wb_handle h, uint64_t out_offset
  *      to fp16 as the reference's tiled GEMM does (gemm_nt_f16_from_f32.wgsl:58-62). ---------------- */
 WB_API int wb_linear(wb_context *ctx, wb_handle weight, uint64_t a_offset, uint64_t c_offset, wb_handle bias,
                      int64_t M, int act_dtype, int out_dtype, int exact);
+/* ---- output-column shards over several GPUs, one process and one context per GPU. No counterpart in the
+ *      reference, which has one device; the call keeps QwenGpt.gemm's meaning (src/model/qwen.ts:568-618) for the
+ *      full [M, n_total] result. `weight` holds this GPU's columns [col_begin, col_begin + N) of the full matrix
+ *      (wb_gptq_register_cols). The product is stored at those columns of the [M, n_total] row-major tensor at
+ *      c_offset in this context's activation slab AND at the same offset in every peer slab: the all-gather is
+ *      the kernel's own stores over NVLink, issued tile by tile by the tensor-core kernel while other tiles are
+ *      still being multiplied (decode-size calls write a dense piece to the scratch tensor at tmp_offset,
+ *      [M, N], and one small launch spreads it). The call is stream-ordered like wb_linear and does NOT wait for
+ *      the peers: before any rank reads its full tensor, every rank's call must have completed (a barrier across
+ *      the ranks after the call, e.g. a one-element NCCL all-reduce on the same streams), and no rank may still
+ *      be reading the tensor when the next call writes it. Cannot be recorded into a command batch.
+ *      wb_arena_ipc_export writes WB_IPC_HANDLE_BYTES bytes that another process on the same node passes to
+ *      wb_peer_open to map this context's slab (only a slab made by wb_arena_create); wb_peer_close unmaps it. */
+#define WB_IPC_HANDLE_BYTES 64
+WB_API int wb_linear_gather(wb_context *ctx, wb_handle weight, uint64_t a_offset, uint64_t c_offset, uint64_t tmp_offset,
+                            wb_handle bias, int64_t M, int act_dtype, int out_dtype, int64_t n_total,
+                            int64_t col_begin, void *const *peer_bases, int n_peers);
+WB_API int wb_arena_ipc_export(wb_context *ctx, int arena, void *handle_out);
+WB_API int wb_peer_open(wb_context *ctx, const void *handle, void **base_out);
+WB_API int wb_peer_close(wb_context *ctx, void *base);
 /* planGemvSplit (src/model/qwen.ts:61-74) generalised: which kernel, how many K slices, what grid. */
 WB_API int wb_plan_query(wb_context *ctx, wb_handle weight, int64_t M, int act_dtype, int exact, wb_plan *out);
 /* Forces a kernel (wb_kernel_kind) and/or split for the next wb_linear calls; 0 = planner's choice.

@@ -40,6 +40,41 @@ def test_column_slices_reassemble_to_the_full_product(gpu, oracle, M):
         gpu.gptq_register("bad_slice", t.qweight, t.qzeros, t.scales, K, N, 128, 4, cols=(4, 64))
 
 
+@pytest.mark.parametrize("M", [1, 64, 300])
+def test_gather_placement_on_one_gpu(gpu, oracle, M):
+    """wb_linear_gather without peers: four column shards of a 3584 -> 512 projection each store their columns of one
+    [M, 512] tensor (scatter launch behind the GEMV at M=1, the tensor-core kernel's own epilogue at M=64, its split-K
+    reduce at M=300); the tensor equals the unsharded product and the columns next to a shard are left alone."""
+    K, N, G = 3584, 512, 4
+    t = synthetic.random_gptq(K, N, 128, seed=22, zeros="any")
+    W = oracle_weight(oracle, t)
+    x = np.random.default_rng(M).standard_normal((M, K)).astype(np.float16)
+    bias = np.random.default_rng(3).standard_normal(N).astype(np.float32)
+    gpu.arena.reset()
+    A = gpu.arena.alloc(M * K, [M, K], "f16")
+    Cf = gpu.arena.alloc(M * N, [M, N], "f32")
+    tmp = gpu.arena.alloc(M * (N // G), [M, N // G], "f32")
+    gpu.write(A, x)
+    gpu.write(Cf, np.full(M * N, -7.0, np.float32))
+    Wref = oracle.round_f16(W).reshape(N, K) if M > 16 else W
+    ref = oracle.gemm_nt_ref(x.astype(np.float32), Wref, M, N, K, bias, threads=oracle.max_threads())
+    for r in (2, 0, 3, 1):
+        sh = parallel.column_shard(N, r, G)
+        name = f"gshard{r}_of{G}"
+        try:
+            h, hb = gpu.weight(name), gpu.weight(name + ".bias")
+        except WebllmError:
+            h = gpu.gptq_register(name, t.qweight, t.qzeros, t.scales, K, N, 128, 4, cols=(sh.begin, sh.count))
+            hb = gpu.f32_upload(name + ".bias", bias[sh.begin:sh.begin + sh.count])
+        gpu.linear_gather(h, A, Cf, tmp, hb, M, N, sh.begin, [])
+        got = gpu.read(Cf).reshape(M, N)
+        if r == 2:  # first shard written: everything else still holds the fill value
+            assert np.all(got[:, :sh.begin] == -7.0) and np.all(got[:, sh.begin + sh.count:] == -7.0)
+    assert_close(oracle, got, ref, 1e-3, f"gather placement M={M}")
+    with pytest.raises(WebllmError, match="do not fit"):
+        gpu.linear_gather(h, A, Cf, tmp, None, M, N, N - 8, [])
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
@@ -76,6 +111,31 @@ def _nccl_rank(rank, world, port, tmp):
             rms = float(np.sqrt(np.mean(ref.astype(np.float64) ** 2)))
             r = oracle.check_tolerance(got, ref, 1e-3 * rms, 1e-3)
             assert got.shape == (M, N) and r.ok, (rank, M, r)
+        # the same products with the all-gather done by the kernels' own stores into the peers' slabs
+        peer = parallel.PeerSlabGpu(rank, weight_bytes=256 << 20, act_bytes=256 << 20)
+        try:
+            plin = parallel.ColumnShardedLinear(peer, "q7p", t, bias)
+            for M in (1, 48, 300):
+                peer.gpu.arena.reset()
+                A = peer.gpu.arena.alloc(M * K, [M, K], "f16")
+                Cf = peer.gpu.arena.alloc(M * N, [M, N], "f32")
+                tmpc = peer.gpu.arena.alloc(M * plin.shard.count, [M, plin.shard.count], "f32")
+                x = np.random.default_rng(10 + M).standard_normal((M, K)).astype(np.float16)
+                peer.gpu.write(A, x)
+                peer.gpu.write(Cf, np.zeros(M * N, np.float32))
+                torch.cuda.synchronize()
+                dist.barrier()  # every rank's tensor is cleared before any peer stores into it
+                plin.forward_fused(A, Cf, tmpc, M)
+                torch.cuda.synchronize()
+                got = peer.gpu.read(Cf).reshape(M, N)
+                Wref = oracle.round_f16(W).reshape(N, K) if M > 16 else W
+                ref = oracle.gemm_nt_ref(x.astype(np.float32), Wref, M, N, K, bias, threads=4)
+                rms = float(np.sqrt(np.mean(ref.astype(np.float64) ** 2)))
+                r = oracle.check_tolerance(got, ref, 1e-3 * rms, 1e-3)
+                assert r.ok, ("fused", rank, M, r)
+                dist.barrier()  # nobody clears its tensor for the next M while a peer is still storing
+        finally:
+            peer.close()
         Path(tmp, f"ok{rank}").write_text("ok")
     finally:
         host.close()

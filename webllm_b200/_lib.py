@@ -16,6 +16,7 @@ WB_ERR_BAD_ARG, WB_ERR_OOM, WB_ERR_CUDA, WB_ERR_NCCL = -1, -2, -3, -4
 WB_ERR_TIMEOUT, WB_ERR_NOT_FOUND, WB_ERR_EXISTS, WB_ERR_UNSUPPORTED = -5, -6, -7, -8
 WB_F32, WB_F16 = 0, 1
 WB_ARENA_WEIGHTS, WB_ARENA_ACT = 0, 1
+WB_IPC_HANDLE_BYTES = 64
 WB_KERNEL_GEMV_MMA, WB_KERNEL_GEMM_TC, WB_KERNEL_GENERIC, WB_KERNEL_DENSE_GEMV = 1, 2, 3, 4
 KERNEL_NAMES = {1: "gemv_mma", 2: "gemm_tc", 3: "generic", 4: "dense_gemv"}
 
@@ -82,6 +83,10 @@ SIGNATURES = {
     "wb_gptq_dequant_f32": [_vp, C.c_int32, _u64],
     "wb_gptq_dequant_f16": [_vp, C.c_int32, _u64],
     "wb_linear": [_vp, C.c_int32, _u64, _u64, C.c_int32, _i64, _i32, _i32, _i32],
+    "wb_linear_gather": [_vp, C.c_int32, _u64, _u64, _u64, C.c_int32, _i64, _i32, _i32, _i64, _i64, C.POINTER(_vp), _i32],
+    "wb_arena_ipc_export": [_vp, _i32, _vp],
+    "wb_peer_open": [_vp, _vp, C.POINTER(_vp)],
+    "wb_peer_close": [_vp, _vp],
     "wb_plan_query": [_vp, C.c_int32, _i64, _i32, _i32, C.POINTER(Plan)],
     "wb_plan_override": [_vp, _i32, _i32],
     "wb_linear_hint_next": [_vp, _i32],

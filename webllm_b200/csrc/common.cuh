@@ -64,6 +64,17 @@ inline uint64_t align_up(uint64_t n, uint64_t a = kAlign) { return (n + a - 1) /
 constexpr uint64_t kWorkspaceBytes = 96ull << 20;
 constexpr int kMaxCounters = 16384;
 
+// Where a linear's result goes when the output columns are sharded over GPUs (wb_linear_gather): element (m, n) of
+// the local [M, N] product is stored at dst[g] + (m * ld + col0 + n) elements for every g < n_dst. dst[0] is this
+// GPU's own slab, the others are peers' slabs mapped into this process (plain stores over NVLink).
+constexpr int kMaxGatherDst = 8;
+struct OutPlace {
+    int64_t ld = 0;
+    int col0 = 0;
+    int n_dst = 0;  // 0: not a gather call
+    void *dst[kMaxGatherDst] = {};
+};
+
 }  // namespace wb
 
 struct wb_context {
@@ -82,6 +93,7 @@ struct wb_context {
     int force_kernel = 0, force_split = 0;
     int prefetch_weight = -1;        // index of the weight the next linear should pull into L2 (-1: none)
     void *tmap_encode = nullptr;     // cuTensorMapEncodeTiled, resolved at context creation
+    wb::OutPlace place;              // set for the duration of one wb_linear_gather call (n_dst > 0)
     bool capturing = false;          // a command batch is being recorded (batch.cu)
     uint64_t launches_at_capture = 0;
 };
@@ -96,6 +108,7 @@ int get_weight(wb_context *ctx, wb_handle h, Weight **out);
 int launch_dequant(wb_context *ctx, const Weight &w, void *out, bool f16);
 int launch_f32_to_f16_ref(wb_context *ctx, const float *in, __half *out, int64_t n);
 int plan_linear(wb_context *ctx, const Weight &w, int64_t M, int act_dtype, int exact, wb_plan *plan);
+int launch_scatter_cols(wb_context *ctx, const void *src, int64_t M, int64_t N, bool f16);  // uses ctx->place
 // Work a decode-size int4 projection can do on its input while staging it (see GemvPrologue in gemv_core.cuh):
 // kind 1 = rmsnorm(x + delta) * norm_w with x + delta stored to x_out, kind 2 = silu(x) * up with row pitch ld.
 struct LinearFusion {

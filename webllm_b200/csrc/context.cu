@@ -552,6 +552,96 @@ int wb_linear(wb_context *ctx, wb_handle weight, uint64_t a_offset, uint64_t c_o
                          bias_ptr, M, act_dtype, out_dtype, exact);
 }
 
+int wb_linear_gather(wb_context *ctx, wb_handle weight, uint64_t a_offset, uint64_t c_offset, uint64_t tmp_offset,
+                     wb_handle bias, int64_t M, int act_dtype, int out_dtype, int64_t n_total, int64_t col_begin,
+                     void *const *peer_bases, int n_peers)
+{
+    WB_CTX(ctx);
+    Weight *w;
+    WB_CHECK(linear_args(ctx, weight, M, act_dtype, out_dtype, &w));
+    if (ctx->capturing) return fail(WB_ERR_BAD_ARG, "wb_linear_gather cannot be recorded into a command batch");
+    if (n_peers < 0 || n_peers > kMaxGatherDst - 1 || (n_peers > 0 && !peer_bases))
+        return fail(WB_ERR_BAD_ARG, "wb_linear_gather: at most %d peers", kMaxGatherDst - 1);
+    if (col_begin < 0 || n_total <= 0 || col_begin + w->N > n_total)
+        return fail(WB_ERR_BAD_ARG, "wb_linear_gather: columns [%lld, %lld) do not fit a row of %lld", (long long)col_begin,
+                    (long long)(col_begin + w->N), (long long)n_total);
+    const uint64_t esz = out_dtype == WB_F16 ? 2 : 4;
+    if (a_offset % kAlign || c_offset % kAlign || tmp_offset % kAlign) return fail(WB_ERR_BAD_ARG, "offsets must be 256-byte aligned");
+    WB_CHECK(check_range(ctx, WB_ARENA_ACT, a_offset, (uint64_t)M * w->K * (act_dtype == WB_F16 ? 2 : 4), "wb_linear_gather A"));
+    WB_CHECK(check_range(ctx, WB_ARENA_ACT, c_offset, (uint64_t)M * n_total * esz, "wb_linear_gather C"));
+    const float *bias_ptr = nullptr;
+    if (bias >= 0) {
+        Weight *b;
+        WB_CHECK(get_weight(ctx, bias, &b));
+        if (b->kind != WeightKind::F32) return fail(WB_ERR_NOT_FOUND, "缺少 f32 权重: %s", b->name.c_str());
+        if (b->N != w->N) return fail(WB_ERR_BAD_ARG, "bias %s has %lld elements, N=%lld", b->name.c_str(),
+                                      (long long)b->N, (long long)w->N);
+        bias_ptr = (const float *)(ctx->arena[WB_ARENA_WEIGHTS].base + b->off_main);
+    }
+    OutPlace pl;
+    pl.ld = n_total, pl.col0 = (int)col_begin, pl.n_dst = 1 + n_peers;
+    pl.dst[0] = arena_ptr(ctx, WB_ARENA_ACT, c_offset);
+    for (int g = 0; g < n_peers; g++) {
+        if (!peer_bases[g]) return fail(WB_ERR_BAD_ARG, "wb_linear_gather: peer %d is NULL", g);
+        pl.dst[1 + g] = (char *)peer_bases[g] + c_offset;
+    }
+    wb_plan plan;
+    WB_CHECK(plan_linear(ctx, *w, M, act_dtype, 0, &plan));
+    const void *A = arena_ptr(ctx, WB_ARENA_ACT, a_offset);
+    int rc;
+    if (plan.kernel == WB_KERNEL_GEMM_TC) {
+        // the tensor-core kernel (and its split-K reduce) stores every output tile straight to all destinations
+        ctx->place = pl;
+        rc = launch_linear(ctx, *w, A, pl.dst[0], bias_ptr, M, act_dtype, out_dtype, 0);
+        ctx->place = OutPlace();
+    } else {
+        // decode-size kernels write a dense [M, N] piece to the scratch tensor; one small launch spreads it
+        WB_CHECK(check_range(ctx, WB_ARENA_ACT, tmp_offset, (uint64_t)M * w->N * esz, "wb_linear_gather scratch"));
+        void *tmp = arena_ptr(ctx, WB_ARENA_ACT, tmp_offset);
+        rc = launch_linear(ctx, *w, A, tmp, bias_ptr, M, act_dtype, out_dtype, 0);
+        if (rc == WB_OK) {
+            ctx->place = pl;
+            rc = launch_scatter_cols(ctx, tmp, M, w->N, out_dtype == WB_F16);
+            ctx->place = OutPlace();
+        }
+    }
+    return rc;
+}
+
+int wb_arena_ipc_export(wb_context *ctx, int arena, void *handle_out)
+{
+    WB_CTX(ctx);
+    if (arena != 0 && arena != 1) return fail(WB_ERR_BAD_ARG, "bad arena %d", arena);
+    if (!handle_out) return fail(WB_ERR_BAD_ARG, "handle_out is NULL");
+    if (!ctx->arena[arena].base || !ctx->arena[arena].owned)
+        return fail(WB_ERR_BAD_ARG, "only a slab that the library allocated itself (wb_arena_create) can be exported");
+    static_assert(sizeof(cudaIpcMemHandle_t) == WB_IPC_HANDLE_BYTES, "handle size");
+    cudaIpcMemHandle_t h;
+    WB_CUDA(cudaIpcGetMemHandle(&h, ctx->arena[arena].base));
+    memcpy(handle_out, &h, sizeof h);
+    return WB_OK;
+}
+
+int wb_peer_open(wb_context *ctx, const void *handle, void **base_out)
+{
+    WB_CTX(ctx);
+    if (!handle || !base_out) return fail(WB_ERR_BAD_ARG, "wb_peer_open: NULL argument");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, sizeof h);
+    void *p = nullptr;
+    WB_CUDA(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+    *base_out = p;
+    return WB_OK;
+}
+
+int wb_peer_close(wb_context *ctx, void *base)
+{
+    WB_CTX(ctx);
+    if (!base) return WB_OK;
+    WB_CUDA(cudaIpcCloseMemHandle(base));
+    return WB_OK;
+}
+
 int wb_plan_query(wb_context *ctx, wb_handle weight, int64_t M, int act_dtype, int exact, wb_plan *out)
 {
     WB_CTX(ctx);

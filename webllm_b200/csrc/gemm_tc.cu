@@ -144,6 +144,12 @@ struct Params {
     int out_f16;
     int kb_per_slice;     // k-blocks per grid.z slice (split-K); the whole K when gridDim.z == 1
     float *partial;       // [slices][M][N] f32 partial sums when gridDim.z > 1
+    // Placement of the result of a column-sharded call (GATHER instantiation; n_dst = 0 otherwise): element (m, n)
+    // goes to dst[g] + m * ld_out + col0 + n for every g < n_dst, this GPU's slab first, then its peers' (the
+    // all-gather is these stores, issued tile by tile while other tiles are still being multiplied).
+    int64_t ld_out;
+    int col0, n_dst;
+    void *dst[kMaxGatherDst];
 };
 
 }  // namespace tc
@@ -163,7 +169,9 @@ struct Smem {
     
 };
 
-template <int MT, bool DENSE, bool SPLIT, int NH>
+// GATHER: the epilogue stores to the placement in Params (several destinations, row pitch ld_out) instead of to the
+// dense local result; a template parameter so that the plain kernel's code is untouched by it.
+template <int MT, bool DENSE, bool SPLIT, int NH, bool GATHER = false>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, const Params p)
 {
@@ -363,9 +371,34 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                         const int m = m0 + c + j;
                         if (m < p.M) {
                             const float v = __uint_as_float(r[j]) + bias;
-                            if (split) part[(int64_t)m * p.N + n] = v;  // this slice's partial sum, f32
-                            else if (p.out_f16) ((__half *)p.out)[(int64_t)m * p.N + n] = __float2half_rn(v);
-                            else ((float *)p.out)[(int64_t)m * p.N + n] = v;
+                            if (split) {
+                                part[(int64_t)m * p.N + n] = v;  // this slice's partial sum, f32
+                            } else {
+                                if constexpr (!GATHER) {
+                                if (p.out_f16) ((__half *)p.out)[(int64_t)m * p.N + n] = __float2half_rn(v);
+                                else ((float *)p.out)[(int64_t)m * p.N + n] = v;
+                                } else {
+                                // destinations are indexed statically (unrolled): a run-time index into the
+                                // kernel's parameters would move them to local memory
+                                const int64_t o = (int64_t)m * p.ld_out + p.col0 + n;
+                                if (p.out_f16) {
+                                    const __half hv = __float2half_rn(v);
+                                    ((__half *)p.dst[0])[o] = hv;
+                                    if (p.n_dst > 1) {
+#pragma unroll
+                                        for (int g = 1; g < kMaxGatherDst; g++)
+                                            if (g < p.n_dst) ((__half *)p.dst[g])[o] = hv;
+                                    }
+                                } else {
+                                    ((float *)p.dst[0])[o] = v;
+                                    if (p.n_dst > 1) {
+#pragma unroll
+                                        for (int g = 1; g < kMaxGatherDst; g++)
+                                            if (g < p.n_dst) ((float *)p.dst[g])[o] = v;
+                                    }
+                                }
+                                }
+                            }
                         }
                     }
                 }
@@ -392,17 +425,42 @@ __global__ void cast_f32_to_f16_kernel(const float *__restrict__ in, __half *__r
     }
 }
 
-// out[m, n] = bias[n] + sum over slices (in slice order) of partial[s][m][n]
-__global__ void splitk_reduce_kernel(const float *__restrict__ partial, const float *__restrict__ bias, void *__restrict__ out,
+// out[m, n] = bias[n] + sum over slices (in slice order) of partial[s][m][n], stored at every destination of `pl`
+__global__ void splitk_reduce_kernel(const float *__restrict__ partial, const float *__restrict__ bias, const OutPlace pl,
                                      int64_t MN, int N, int S, int out_f16)
 {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= MN) return;
     float v = 0.f;
     for (int s = 0; s < S; s++) v += partial[(int64_t)s * MN + i];
-    if (bias) v += bias[i % N];
-    if (out_f16) ((__half *)out)[i] = __float2half_rn(v);
-    else ((float *)out)[i] = v;
+    const int64_t m = i / N;
+    const int n = (int)(i - m * N);
+    if (bias) v += bias[n];
+    const int64_t o = m * pl.ld + pl.col0 + n;
+#pragma unroll
+    for (int g = 0; g < kMaxGatherDst; g++) {  // static indices into the parameter
+        if (g < pl.n_dst) {
+            if (out_f16) ((__half *)pl.dst[g])[o] = __float2half_rn(v);
+            else ((float *)pl.dst[g])[o] = v;
+        }
+    }
+}
+
+// Copies a dense local [M, N] result to its columns of every destination (the decode-size kernels write a dense
+// result; at those sizes the pieces are a few KB and a second small launch costs less than a collective).
+__global__ void scatter_cols_kernel(const void *__restrict__ src, const OutPlace pl, int64_t MN, int N, int f16)
+{
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= MN) return;
+    const int64_t m = i / N;
+    const int64_t o = m * pl.ld + pl.col0 + (i - m * N);
+#pragma unroll
+    for (int g = 0; g < kMaxGatherDst; g++) {  // static indices into the parameter
+        if (g < pl.n_dst) {
+            if (f16) ((__half *)pl.dst[g])[o] = ((const __half *)src)[i];
+            else ((float *)pl.dst[g])[o] = ((const float *)src)[i];
+        }
+    }
 }
 
 }  // namespace tc
@@ -507,16 +565,17 @@ template <int MT, bool DENSE, int NH>
 static cudaError_t launch_tc(const CUtensorMap &mx, const CUtensorMap &mw, const tc::Params &p, dim3 grid, cudaStream_t st)
 {
     constexpr int smem = tc::Smem<MT, DENSE, NH>::TOTAL;
-    if (grid.z > 1) {
-        cudaError_t e = cudaFuncSetAttribute(tc::gemm_tc_kernel<MT, DENSE, true, NH>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    auto go = [&](auto kernel) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return e;
-        tc::gemm_tc_kernel<MT, DENSE, true, NH><<<grid, tc::THREADS, smem, st>>>(mx, mw, p);
-    } else {
-        cudaError_t e = cudaFuncSetAttribute(tc::gemm_tc_kernel<MT, DENSE, false, NH>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e != cudaSuccess) return e;
-        tc::gemm_tc_kernel<MT, DENSE, false, NH><<<grid, tc::THREADS, smem, st>>>(mx, mw, p);
+        kernel<<<grid, tc::THREADS, smem, st>>>(mx, mw, p);
+        return cudaGetLastError();
+    };
+    if (grid.z > 1) return go(tc::gemm_tc_kernel<MT, DENSE, true, NH, false>);  // slices write partial sums: no placement
+    if constexpr (!DENSE) {
+        if (p.n_dst > 0) return go(tc::gemm_tc_kernel<MT, DENSE, false, NH, true>);
     }
-    return cudaGetLastError();
+    return go(tc::gemm_tc_kernel<MT, DENSE, false, NH, false>);
 }
 
 // tile_n = 256 (two accumulators per CTA) exists for the 128- and 256-token tiles only
@@ -561,6 +620,12 @@ int launch_gemm_tc(wb_context *ctx, const Weight &w, const void *A, void *C, con
     const int kblocks = (int)(w.K / tc::BK);
     p.kb_per_slice = (kblocks + S - 1) / S;
     p.partial = (float *)(ctx->workspace + (act_dtype == WB_F32 ? align_up((uint64_t)M * w.K * 2) : 0));
+    OutPlace place = ctx->place;  // n_dst > 0: a column-sharded call (wb_linear_gather)
+    if (place.n_dst > 0 && w.kind != WeightKind::Gptq)
+        return fail(WB_ERR_UNSUPPORTED, "wb_linear_gather takes GPTQ weights only");
+    p.ld_out = place.ld, p.col0 = place.col0, p.n_dst = place.n_dst;
+    for (int g = 0; g < kMaxGatherDst; g++) p.dst[g] = place.dst[g];
+    if (place.n_dst == 0) place.ld = w.N, place.col0 = 0, place.n_dst = 1, place.dst[0] = C;  // for the split-K reduce
     dim3 grid(plan.grid_x, plan.grid_y, S);
     cudaError_t e;
     if (w.kind == WeightKind::Gptq) {
@@ -581,11 +646,20 @@ int launch_gemm_tc(wb_context *ctx, const Weight &w, const void *A, void *C, con
     WB_CUDA(e);
     if (S > 1) {
         const int64_t MN = M * w.N;
-        tc::splitk_reduce_kernel<<<(unsigned)((MN + 255) / 256), 256, 0, ctx->stream>>>(p.partial, bias, C, MN, (int)w.N, S,
+        tc::splitk_reduce_kernel<<<(unsigned)((MN + 255) / 256), 256, 0, ctx->stream>>>(p.partial, bias, place, MN, (int)w.N, S,
                                                                                          out_dtype == WB_F16);
         ctx->launches++;
         WB_CUDA(cudaGetLastError());
     }
+    return WB_OK;
+}
+
+int launch_scatter_cols(wb_context *ctx, const void *src, int64_t M, int64_t N, bool f16)
+{
+    const int64_t MN = M * N;
+    tc::scatter_cols_kernel<<<(unsigned)((MN + 255) / 256), 256, 0, ctx->stream>>>(src, ctx->place, MN, (int)N, f16 ? 1 : 0);
+    ctx->launches++;
+    WB_CUDA(cudaGetLastError());
     return WB_OK;
 }
 

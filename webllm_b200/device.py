@@ -162,6 +162,31 @@ class Gpu:
                                     L.WB_F32 if A.dtype == "f32" else L.WB_F16,
                                     L.WB_F32 if Cout.dtype == "f32" else L.WB_F16, 1 if exact else 0))
 
+    def linear_gather(self, weight: int, A: Tensor, C_full: Tensor, tmp: Tensor, bias: int | None, M: int, n_total: int,
+                      col_begin: int, peer_bases: list[int]) -> None:
+        """Column-sharded linear whose kernel stores its columns of the ``[M, n_total]`` result into this GPU's
+        slab and into every peer slab (``wb_linear_gather``); the caller barriers across the ranks afterwards."""
+        arr = (C.c_void_p * max(1, len(peer_bases)))(*peer_bases)
+        L.check(self._lib.wb_linear_gather(self._ctx, weight, A.offset, C_full.offset, tmp.offset,
+                                           -1 if bias is None else bias, M,
+                                           L.WB_F32 if A.dtype == "f32" else L.WB_F16,
+                                           L.WB_F32 if C_full.dtype == "f32" else L.WB_F16, n_total, col_begin, arr,
+                                           len(peer_bases)))
+
+    def ipc_export(self, arena: int = L.WB_ARENA_ACT) -> bytes:
+        """Handle of a slab of this context for another process on the same node (``wb_arena_ipc_export``)."""
+        buf = C.create_string_buffer(L.WB_IPC_HANDLE_BYTES)
+        L.check(self._lib.wb_arena_ipc_export(self._ctx, arena, buf))
+        return buf.raw
+
+    def peer_open(self, handle: bytes) -> int:
+        base = C.c_void_p()
+        L.check(self._lib.wb_peer_open(self._ctx, C.c_char_p(handle), C.byref(base)))
+        return base.value
+
+    def peer_close(self, base: int) -> None:
+        L.check(self._lib.wb_peer_close(self._ctx, C.c_void_p(base)))
+
     def hint_next(self, weight: int | None) -> None:
         """The next ``linear`` call also asks the L2 to fetch ``weight``, which a later call will stream."""
         L.check(self._lib.wb_linear_hint_next(self._ctx, -1 if weight is None else weight))

@@ -90,6 +90,41 @@ class TorchSlabGpu:
         self.gpu.close()
 
 
+class PeerSlabGpu:
+    """A ``Gpu`` whose activation slab the library allocated itself and that has every other rank's activation slab
+    mapped (CUDA IPC, one node), so that ``ColumnShardedLinear.forward_fused`` can store results straight into the
+    peers. Tensors are ``(slab, byte offset)`` on every rank: the ranks must make the same sequence of arena
+    allocations, so that one offset names the same tensor everywhere. Kernels go to torch's current stream, which
+    is also where the barrier's collective is enqueued."""
+
+    def __init__(self, device: int, weight_bytes: int, act_bytes: int, group=None):
+        import torch
+        import torch.distributed as dist
+
+        from .device import Gpu
+        self.torch, self.group = torch, group
+        self.device = torch.device(f"cuda:{device}")
+        torch.cuda.set_device(self.device)
+        self.gpu = Gpu(device, weight_bytes=weight_bytes, act_bytes=act_bytes)
+        self.gpu.set_stream(torch.cuda.current_stream(self.device).cuda_stream)
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        handles = [None] * self.world
+        dist.all_gather_object(handles, self.gpu.ipc_export(), group=group)
+        self.peer_bases = [self.gpu.peer_open(h) for r, h in enumerate(handles) if r != self.rank]
+        self._flag = torch.zeros(1, dtype=torch.int32, device=self.device)
+
+    def barrier(self) -> None:
+        """Stream-ordered barrier across the ranks: a one-element all-reduce behind the kernels already enqueued."""
+        import torch.distributed as dist
+        dist.all_reduce(self._flag, group=self.group)
+
+    def close(self) -> None:
+        for b in self.peer_bases:
+            self.gpu.peer_close(b)
+        self.peer_bases = []
+        self.gpu.close()
+
+
 class ColumnShardedLinear:
     """One GPTQ linear split by output columns over the ranks of a process group.
 
@@ -112,6 +147,15 @@ class ColumnShardedLinear:
 
     def local(self, A, C_local, M: int, exact: bool = False) -> None:
         self.host.gpu.linear(self.weight, A, C_local, self.bias, M, exact=exact)
+
+    def forward_fused(self, A, C_full, tmp, M: int) -> None:
+        """A: arena tensor [M, K] (replicated); C_full: arena tensor [M, N] at the same offset on every rank; tmp:
+        arena tensor [M, N/G] (used by decode-size calls only). ``host`` must be a ``PeerSlabGpu``. The kernel of
+        every rank stores its columns into all ranks' C_full; after the barrier every rank holds the full, row-major
+        [M, N]. The caller must not let any rank reuse C_full for another result before all ranks have read it."""
+        self.host.gpu.linear_gather(self.weight, A, C_full, tmp, self.bias, M, self.N, self.shard.begin,
+                                    self.host.peer_bases)
+        self.host.barrier()
 
     def forward(self, A, C_local, M: int, exact: bool = False):
         """A: arena tensor [M, K] (replicated), C_local: arena tensor [M, N/G]. Returns a torch tensor [M, N]."""

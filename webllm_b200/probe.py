@@ -16,7 +16,9 @@ only a sanity check (a profiler serialises kernels), the numbers that count come
 and the 7B-class shapes (M = 1 and M = 4096): each case is a command batch over weight copies larger than L2,
 replayed and timed with CUDA events (needs torch for the events).
 ``shard`` times the 7B-class projections split by output columns over the ranks (decode M = 1 and prefill M = --m):
-the local product alone, and the local product followed by the NCCL all-gather of the ``[M, N/G]`` pieces.
+the local product alone, the local product followed by the NCCL all-gather of the ``[M, N/G]`` pieces (rank-major,
+and copied to row-major), and the variant whose kernel stores its tiles into every rank's slab itself
+(``wb_linear_gather``) followed by a one-element all-reduce as the barrier.
 ``dp-prefill`` runs independent 2048-token sequences through the 96 projections of the 0.5B-shaped model
 (q|k|v, o, gate|up, down per layer, fp16 activations), the sequences dealt round-robin to the ranks, weights
 replicated, no collective on the data path. Both time with CUDA events and report the slowest rank.
@@ -156,6 +158,7 @@ def _shard(args) -> None:
     stream = torch.cuda.Stream()  # kernels, collectives and events all go to this stream
     torch.cuda.set_stream(stream)
     host = parallel.TorchSlabGpu(local, weight_bytes=3 << 30, act_bytes=2 << 30)
+    peer = parallel.PeerSlabGpu(local, weight_bytes=3 << 30, act_bytes=2 << 30)  # for the store-to-peers variant
     gpu = host.gpu
     try:
         for name in ("q", "k", "gate", "down"):
@@ -187,7 +190,20 @@ def _shard(args) -> None:
                         dist.all_gather_into_tensor(out, piece)
                         out.permute(1, 0, 2).reshape(M, -1).contiguous()
 
+                plins = [parallel.ColumnShardedLinear(peer, f"{name}7b_{M}_{i}", t) for i in range(copies)]
+                peer.gpu.arena.reset()
+                A2 = peer.gpu.arena.alloc(M * K, [M, K], "f16")
+                Cfull = peer.gpu.arena.alloc(M * N, [M, N], "f16")
+                tmp2 = peer.gpu.arena.alloc(M * n_loc, [M, n_loc], "f16")
+
+                def fused():
+                    for lin in plins:
+                        lin.forward_fused(A2, Cfull, tmp2, M)
+
                 reps = 5 if M > 1 else 3
+                us_f = _timed_ranks(torch, dist, fused, reps) / copies
+                for _ in plins:
+                    peer.gpu.weight_pop()
                 us_l = _timed_ranks(torch, dist, local_only, reps) / copies
                 us_g = _timed_ranks(torch, dist, with_gather, reps) / copies
                 us_r = _timed_ranks(torch, dist, with_gather_rowmajor, reps) / copies if M > 1 else us_g
@@ -195,10 +211,12 @@ def _shard(args) -> None:
                     tf = 2.0 * M * N * K / 1e6
                     print(f"{name}7b K={K:5d} N={N:5d} M={M:4d} G={world}: local {us_l:8.2f} us, + all-gather {us_g:8.2f} us"
                           f" ({tf / us_g:7.1f} TFLOP/s, {t.nbytes / us_g / 1e3:7.1f} GB/s of int4 weights over all ranks),"
-                          f" + row-major copy {us_r:8.2f} us; gathered {M * N * 2} bytes", flush=True)
+                          f" + row-major copy {us_r:8.2f} us; stores to peers + barrier {us_f:8.2f} us"
+                          f" ({tf / us_f:7.1f} TFLOP/s); gathered {M * N * 2} bytes", flush=True)
                 for _ in lins:
                     gpu.weight_pop()
     finally:
+        peer.close()
         host.close()
         dist.destroy_process_group()
 
