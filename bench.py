@@ -228,6 +228,8 @@ def kernel_sections(gpu, torch, stream, cfg, G, args) -> dict:
                 "bytes_per_launch": nbytes}
     extras["int4_gemv_896x4864_m1"] = rotating_gemv("c1", 896, 4864, 64)
     extras["int4_gemv_3584x18944_m1"] = rotating_gemv("g7", 3584, 18944, 8)
+    # the same projection as the decode path runs it, gate|up as one matrix (70 MB per launch)
+    extras["int4_gemv_3584x37888_m1"] = rotating_gemv("gu7", 3584, 37888, 4)
 
     # prefill GEMM, M = 2048 tokens x the four distinct 0.5B projection shapes, fp16 activations
     tf = {}
@@ -250,6 +252,24 @@ def kernel_sections(gpu, torch, stream, cfg, G, args) -> dict:
         total_ms += ms_ * count
     tf["layer_aggregate_TFLOP/s"] = total_flops / (total_ms * 1e-3) / 1e12
     extras["prefill_gemm_m2048"] = tf
+    # the same layer as the model launches it: q|k|v and gate|up as one projection each (4 launches per layer)
+    C_, KV_, I_ = cfg.n_embd, cfg.kv_dim, cfg.intermediate
+    fused_flops, fused_ms = 0.0, 0.0
+    for tag, (K, N) in (("qkv", (C_, C_ + 2 * KV_)), ("o", (C_, C_)), ("gateup", (C_, 2 * I_)), ("down", (I_, C_))):
+        t = synthetic.random_gptq(K, N, 128, seed=2)
+        h = gpu.gptq_register(f"bench_pff_{tag}", t.qweight, t.qzeros, t.scales, K, N, 128)
+        gpu.arena.reset()
+        A = gpu.arena.alloc(2048 * K, dtype="f16")
+        Cc = gpu.arena.alloc(2048 * N, dtype="f16")
+        with gpu.batch() as bb:
+            for _ in range(8):
+                gpu.linear(h, A, Cc, None, 2048)
+        ms_ = time_batch(gpu, torch, stream, bb, reps=5) / 8
+        bb.destroy()
+        fused_flops += 2.0 * 2048 * N * K
+        fused_ms += ms_
+    extras["prefill_gemm_m2048_fused_projections"] = {"us_per_layer": fused_ms * 1e3,
+                                                      "layer_aggregate_TFLOP/s": fused_flops / (fused_ms * 1e-3) / 1e12}
     out["extras"] = extras
     return out
 
@@ -275,7 +295,7 @@ def run_ours(args) -> None:
     K, W = args.steps, max(args.warmup, 3)
     e2e_steps = min(K, 64)
     max_t = PROMPT_LEN + W + K + e2e_steps + 8
-    gpu = Gpu(local, weight_bytes=(1 << 30) + (512 << 20), act_bytes=256 << 20)
+    gpu = Gpu(local, weight_bytes=2 << 30, act_bytes=256 << 20)
     stream = torch.cuda.ExternalStream(gpu.stream, device=torch.device(f"cuda:{local}"))
     model = QwenGpt(gpu, cfg, max_t=max_t, kv_dtype="f16")
     model.upload_gptq_model(G, fuse=True)

@@ -176,6 +176,10 @@ WB_API int wb_linear_gather(wb_context *ctx, wb_handle weight, uint64_t a_offset
 WB_API int wb_arena_ipc_export(wb_context *ctx, int arena, void *handle_out);
 WB_API int wb_peer_open(wb_context *ctx, const void *handle, void **base_out);
 WB_API int wb_peer_close(wb_context *ctx, void *base);
+/* Diagnostic with no counterpart in the reference: one kernel of `ctas` x 256 threads reads `bytes` of a slab once
+ * (128-bit streaming loads) and computes nothing. It measures the rate that any single pass over that many bytes
+ * reaches when launched like the int4 GEMV, the figure that kernel's bandwidth is compared with. */
+WB_API int wb_read_sweep(wb_context *ctx, int arena, uint64_t offset, uint64_t bytes, int ctas);
 /* planGemvSplit (src/model/qwen.ts:61-74) generalised: which kernel, how many K slices, what grid. */
 WB_API int wb_plan_query(wb_context *ctx, wb_handle weight, int64_t M, int act_dtype, int exact, wb_plan *out);
 /* Forces a kernel (wb_kernel_kind) and/or split for the next wb_linear calls; 0 = planner's choice.

@@ -171,20 +171,29 @@ def test_planner_picks_tile_and_slices_together(gpu, oracle):
     for name, K, N in (("gate", 896, 4864), ("down", 4864, 896)):
         h, _ = _weight(gpu, oracle, name, K, N)
         p = gpu.plan(h, 2048, "f16")
-        assert p["tile_n"] in (128, 256) and p["tile_m"] in (128, 256)
+        assert p["tile_n"] in (128, 256) and p["tile_m"] in (128, 192, 256)
         assert p["grid_y"] == -(-N // p["tile_n"]) and p["grid_x"] == -(-2048 // p["tile_m"])
         assert (p["split_k"] > 1) == (name == "down") and p["grid_z"] == p["split_k"]
-    if os.environ.get("WEBLLM_B200_GEMM_NH") is None:
+    if os.environ.get("WEBLLM_B200_GEMM_NH") is None and os.environ.get("WEBLLM_B200_GEMM_MT") is None:
         h, _ = _weight(gpu, oracle, "q7", 3584, 3584, zeros="7or8")
         p = gpu.plan(h, 4096, "f16")
         assert (p["tile_m"], p["tile_n"], p["split_k"]) == (256, 256, 1)
 
 
-@pytest.mark.skipif(os.environ.get("WEBLLM_B200_GEMM_NH") is not None, reason="already the forced run")
-def test_every_tile_shape_with_two_accumulators():
-    """The tile switches are read once per process, so the ragged-M, dense and split-K cases above run again in a
-    child process with the 256-column tile forced for every token count from 100 up (128 x 256 and 256 x 256)."""
-    env = dict(os.environ, WEBLLM_B200_GEMM_NH="2")
-    r = subprocess.run([sys.executable, "-m", "pytest", __file__, "-q", "-x", "-k", "ragged or dense or split_k_gemm or 7b"],
+_FORCED = any(os.environ.get(v) is not None for v in ("WEBLLM_B200_GEMM_NH", "WEBLLM_B200_GEMM_MT", "WEBLLM_B200_GEMM_PERSIST"))
+
+
+@pytest.mark.skipif(_FORCED, reason="already the forced run")
+@pytest.mark.parametrize("var,value", [("WEBLLM_B200_GEMM_NH", "2"), ("WEBLLM_B200_GEMM_MT", "192"),
+                                       ("WEBLLM_B200_GEMM_PERSIST", "1")])
+def test_every_tile_shape_forced(var, value):
+    """The tile switches are read once per process, so the ragged-M, dense and split-K cases above run again in child
+    processes: once with the 256-column tile forced for every token count from 100 up (128 x 256 and 256 x 256), and
+    once with the 192-token tile (the one the planner picks to fit the waves, 256 or 512 TMEM columns) forced for
+    every token count, and once with the persistent tile loop switched on (it is opt-in), which the prefill sizes (more
+    tiles than SMs) then take."""
+    env = dict(os.environ)
+    env[var] = value
+    r = subprocess.run([sys.executable, "-m", "pytest", __file__, "-q", "-x", "-k", "ragged or dense or split_k_gemm or 7b or m2048"],
                        env=env, capture_output=True, text=True, timeout=900)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]

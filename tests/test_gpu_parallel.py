@@ -75,6 +75,33 @@ def test_gather_placement_on_one_gpu(gpu, oracle, M):
         gpu.linear_gather(h, A, Cf, tmp, None, M, N, N - 8, [])
 
 
+def test_gather_from_the_persistent_tile_loop(gpu, oracle):
+    """Two column shards of the 0.5B gate projection at M = 2048, enough tiles per shard for the planner to consider
+    the persistent tensor-core kernel, whose epilogue warps then do the placement into the [2048, 4864] tensor."""
+    K, N, G, M = 896, 4864, 2, 2048
+    t = synthetic.random_gptq(K, N, 128, seed=23, zeros="any")
+    W = oracle.round_f16(oracle_weight(oracle, t)).reshape(N, K)
+    x = np.random.default_rng(7).standard_normal((M, K)).astype(np.float16)
+    gpu.arena.reset()
+    A = gpu.arena.alloc(M * K, [M, K], "f16")
+    Cf = gpu.arena.alloc(M * N, [M, N], "f16")
+    tmp = gpu.arena.alloc(M * (N // G), [M, N // G], "f16")
+    gpu.write(A, x)
+    for r in range(G):
+        sh = parallel.column_shard(N, r, G)
+        h = gpu.gptq_register(f"pshard{r}", t.qweight, t.qzeros, t.scales, K, N, 128, 4, cols=(sh.begin, sh.count))
+        p = gpu.plan(h, M, "f16")
+        assert p["kernel_name"] == "gemm_tc" and p["split_k"] == 1
+        gpu.linear_gather(h, A, Cf, tmp, None, M, N, sh.begin, [])
+    rows = sorted(set(np.random.default_rng(1).integers(0, M, 94).tolist()) | {0, M - 1})  # sampled: the host is slow
+    got = gpu.read(Cf).reshape(M, N)[rows].astype(np.float32)
+    ref = oracle.gemm_nt_ref(np.ascontiguousarray(x[rows]).astype(np.float32), W, len(rows), N, K, threads=oracle.max_threads())
+    ref16 = ref.astype(np.float16).astype(np.float32)  # the output tensor is fp16: round both sides
+    assert_close(oracle, got, ref16, 1e-3, "gather from the persistent kernel")
+    for _ in range(G):
+        gpu.weight_pop()
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))

@@ -87,6 +87,7 @@ SIGNATURES = {
     "wb_arena_ipc_export": [_vp, _i32, _vp],
     "wb_peer_open": [_vp, _vp, C.POINTER(_vp)],
     "wb_peer_close": [_vp, _vp],
+    "wb_read_sweep": [_vp, _i32, _u64, _u64, _i32],
     "wb_plan_query": [_vp, C.c_int32, _i64, _i32, _i32, C.POINTER(Plan)],
     "wb_plan_override": [_vp, _i32, _i32],
     "wb_linear_hint_next": [_vp, _i32],

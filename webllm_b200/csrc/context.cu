@@ -102,6 +102,29 @@ using namespace wb;
         WB_CUDA(cudaSetDevice((ctx)->device));                             \
     } while (0)
 
+namespace wb {
+// Reads a byte range once and does nothing else (an XOR that is never stored): the rate that ANY single pass over that
+// many bytes can reach when launched like the GEMV, which is what its roofline fraction is read against.
+__global__ void __launch_bounds__(256) read_sweep_kernel(const uint4 *__restrict__ src, size_t n16, uint32_t *sink)
+{
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    uint32_t acc = 0;
+    for (; i + 3 * stride < n16; i += 4 * stride) {
+        uint4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) v[u] = ldg_stream_v4(reinterpret_cast<const uint32_t *>(src + i + u * stride));
+#pragma unroll
+        for (int u = 0; u < 4; u++) acc ^= v[u].x ^ v[u].y ^ v[u].z ^ v[u].w;
+    }
+    for (; i < n16; i += stride) {
+        const uint4 v = ldg_stream_v4(reinterpret_cast<const uint32_t *>(src + i));
+        acc ^= v.x ^ v.y ^ v.z ^ v.w;
+    }
+    if (acc == 0x9e3779b9u) *sink = acc;  // keeps the loads alive; practically never true
+}
+}  // namespace wb
+
 extern "C" {
 
 const char *wb_last_error(void) { return g_error; }
@@ -639,6 +662,20 @@ int wb_peer_close(wb_context *ctx, void *base)
     WB_CTX(ctx);
     if (!base) return WB_OK;
     WB_CUDA(cudaIpcCloseMemHandle(base));
+    return WB_OK;
+}
+
+int wb_read_sweep(wb_context *ctx, int arena, uint64_t offset, uint64_t bytes, int ctas)
+{
+    WB_CTX(ctx);
+    if (arena != 0 && arena != 1) return fail(WB_ERR_BAD_ARG, "bad arena %d", arena);
+    if (offset % 16 || bytes % 16 || bytes == 0 || ctas <= 0) return fail(WB_ERR_BAD_ARG, "wb_read_sweep: 16-byte units, ctas > 0");
+    if (!ctx->arena[arena].base || offset + bytes > ctx->arena[arena].capacity)
+        return fail(WB_ERR_BAD_ARG, "wb_read_sweep: range outside the slab");
+    read_sweep_kernel<<<ctas, 256, 0, ctx->stream>>>((const uint4 *)(ctx->arena[arena].base + offset), bytes / 16,
+                                                     (uint32_t *)ctx->counters + (kMaxCounters - 1));
+    ctx->launches++;
+    WB_CUDA(cudaGetLastError());
     return WB_OK;
 }
 

@@ -73,6 +73,20 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
     return false;
 }
 
+// The same for a warp that waits through a whole k-loop (the persistent kernel's epilogue): it sleeps between polls so
+// that it does not take issue slots from the unpack warps. 2^18 polls of >= 64 ns bound the wait at some tens of ms.
+__device__ __forceinline__ bool mbar_wait_idle(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int *status, int code)
+{
+    for (uint32_t it = 0; it < (1u << 18); it++) {
+        if (mbar_try(bar, parity)) return true;
+        __nanosleep(64);
+        if ((it & 255u) == 255u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    if (status) *(volatile int *)status = code;
+    return false;
+}
+
 __device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int x, int y, uint64_t *bar)
 {
     asm volatile(
@@ -179,7 +193,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     constexpr int STAGES = S::STAGES;
     constexpr int COLS = S::COLS;
     constexpr uint32_t ACC_COLS = MT < 32 ? 32 : MT;  // TMEM columns of one accumulator
-    constexpr uint32_t TMEM_COLS = ACC_COLS * NH;
+    // TMEM is allocated in powers of two (the 192-token tile takes 256 or 512 columns)
+    constexpr uint32_t TMEM_COLS = ACC_COLS * NH <= 32 ? 32 : ACC_COLS * NH <= 64 ? 64 : ACC_COLS * NH <= 128 ? 128
+                                   : ACC_COLS * NH <= 256 ? 256 : 512;
+    static_assert(ACC_COLS * NH <= 512, "accumulators exceed the tensor memory");
     // The unpack warps form KG sets of one thread per column; set g unpacks k-blocks g, g + KG, ... so that KG
     // k-blocks are in the works at once and a warp pays the waits and the fence of a block once per 8 packed rows.
     constexpr int KG = 32 * UNPACK_WARPS / COLS;
@@ -411,6 +428,280 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
+// ----------------------------------------------------------------------------------------------------
+// Persistent variant, for launches with more tiles than SMs and no K split: one CTA per SM walks the tiles
+// t = blockIdx.x, + gridDim.x, ... (tile t covers token tile t % tiles_m of weight-column tile t / tiles_m, so the
+// CTAs that run at the same time share weight columns in L2). The TMA ring and the unpack run on across tile
+// boundaries, the accumulators are double-buffered in TMEM wherever two sets fit its 512 columns, and four warps of
+// their own drain a finished accumulator while the MMAs of the next tile are issued: pipeline fill, TMEM drain and
+// the stores (to peers too, in a column-sharded call) leave the critical path of every tile but the last.
+// Roles, 22 warps: 0 = TMA, 1 = MMA, 2-17 = unpack (as above), 18-21 = epilogue (TMEM lane quarter warp % 4).
+constexpr int EPI_WARPS = 4;
+constexpr int THREADS_P = THREADS + 32 * EPI_WARPS;
+
+template <int MT, bool DENSE, int NH, bool GATHER>
+__global__ void __launch_bounds__(THREADS_P, 1)
+gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, const Params p,
+                       const int tiles_m, const int n_tiles)
+{
+    using S = Smem<MT, DENSE, NH>;
+    constexpr int STAGES = S::STAGES;
+    constexpr int COLS = S::COLS;
+    constexpr uint32_t ACC_COLS = MT < 32 ? 32 : MT;
+    constexpr uint32_t ACC_ALL = ACC_COLS * NH;             // TMEM columns of one tile's accumulators
+    constexpr int NBUF = 2 * ACC_ALL <= 512 ? 2 : 1;        // accumulator sets
+    constexpr uint32_t USED = ACC_ALL * NBUF;
+    constexpr uint32_t TMEM_COLS = USED <= 32 ? 32 : USED <= 64 ? 64 : USED <= 128 ? 128 : USED <= 256 ? 256 : 512;
+    static_assert(USED <= 512, "accumulators exceed the tensor memory");
+    constexpr int KG = 32 * UNPACK_WARPS / COLS;
+    static_assert(KG <= STAGES && UNPACK_WARPS % KG == 0 && (32 * UNPACK_WARPS / KG) % COLS == 0, "unpack sets");
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t *bars = (uint64_t *)(smem + STAGES * S::STAGE_BYTES);
+    uint64_t *full = bars, *deq = bars + STAGES, *empty = bars + 2 * STAGES;
+    uint64_t *acc_full = bars + 3 * STAGES, *acc_empty = bars + 3 * STAGES + 2;
+    uint32_t *tmem_slot = (uint32_t *)(bars + 3 * STAGES + 4);
+    volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
+    static_assert((3 * STAGES + 4) * 8 + 8 <= 256, "barrier area");
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int KBt = p.K / BK;  // k-blocks per tile
+    const int tiles_cta = (int)blockIdx.x < n_tiles ? (n_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+    auto tile_m0 = [&](int ti) { return (((int)blockIdx.x + ti * (int)gridDim.x) % tiles_m) * MT; };
+    auto tile_n0 = [&](int ti) { return (((int)blockIdx.x + ti * (int)gridDim.x) / tiles_m) * COLS; };
+
+    auto xs = [&](int s) { return smem + s * S::STAGE_BYTES; };
+    auto wd = [&](int s) { return smem + s * S::STAGE_BYTES + S::X_BYTES; };
+    auto wp = [&](int s) { return (uint32_t *)(smem + s * S::STAGE_BYTES + S::X_BYTES + S::WD_BYTES); };
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&deq[s], UNPACK_WARPS / KG);
+            mbar_init(&empty[s], 1);
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], EPI_WARPS);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int s = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            for (int ti = 0; ti < tiles_cta && ok; ti++) {
+                const int m0 = tile_m0(ti), n0 = tile_n0(ti);
+                for (int kb = 0; kb < KBt; kb++) {
+                    ok = mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 1);
+                    if (!ok) break;
+                    mbar_expect_tx(&full[s], S::X_BYTES + (DENSE ? S::WD_BYTES : S::WP_BYTES));
+                    tma_load_2d(xs(s), &map_x, kb * BK, m0, &full[s]);
+                    if constexpr (DENSE) tma_load_2d(wd(s), &map_w, kb * BK, n0, &full[s]);
+                    else tma_load_2d(wp(s), &map_w, n0, kb * 8, &full[s]);
+                    if (++s == STAGES) s = 0, ph ^= 1;
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = idesc_f16(BN, MT);
+            bool ok = true;
+            int s = 0;
+            uint32_t ph = 0;
+            for (int ti = 0; ti < tiles_cta && ok; ti++) {
+                const int buf = ti % NBUF, use = ti / NBUF;  // `use` earlier tiles went through this accumulator set
+                if (use > 0) ok = mbar_wait(&acc_empty[buf], (uint32_t)(use - 1) & 1u, abort_flag, p.status, 6);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t acc = tmem_base + (uint32_t)buf * ACC_ALL;
+                for (int kb = 0; kb < KBt; kb++) {
+                    ok = mbar_wait(&full[s], ph, abort_flag, p.status, 2);
+                    if (ok && !DENSE) ok = mbar_wait(&deq[s], ph, abort_flag, p.status, 3);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint64_t a0 = smem_desc_sw128(smem_u32(wd(s)));
+                    const uint64_t b0 = smem_desc_sw128(smem_u32(xs(s)));
+#pragma unroll
+                    for (int k = 0; k < BK / 16; k++) {
+#pragma unroll
+                        for (int h = 0; h < NH; h++)
+                            umma_f16(acc + h * ACC_COLS, a0 + 1024 * h + 2 * k, b0 + 2 * k, idesc, (kb | k) != 0);
+                    }
+                    umma_commit(&empty[s]);
+                    if (++s == STAGES) s = 0, ph ^= 1;
+                }
+                if (ok) umma_commit(&acc_full[buf]);
+            }
+        }
+        __syncwarp();
+    } else if (warp < 2 + UNPACK_WARPS) {
+        // ------------------------------------------------------------------ unpack: the sets take the k-blocks of the
+        // CTA's whole sequence (tile after tile) in turn
+        if constexpr (!DENSE) {
+            constexpr int SET_THREADS = 32 * UNPACK_WARPS / KG;
+            constexpr int RPT = 8 * COLS / SET_THREADS;
+            const int kg = (threadIdx.x - 64) / SET_THREADS;
+            const int tn = (threadIdx.x - 64) % SET_THREADS % COLS;
+            const int rhalf = (threadIdx.x - 64) % SET_THREADS / COLS;
+            const __half2 sixteenth = __float2half2_rn(0.0625f);
+            const int src_off = S::X_BYTES + S::WD_BYTES + (tn + rhalf * RPT * COLS) * 4;
+            int dst_off[RPT];
+#pragma unroll
+            for (int rr = 0; rr < RPT; rr++) dst_off[rr] = S::X_BYTES + tn * 128 + (((rhalf * RPT + rr) ^ (tn & 7)) << 4);
+            // position of the set's current item: tile index in the CTA's sequence, k-block in the tile, its group
+            int ti = 0, kb = kg;
+            while (kb >= KBt) kb -= KBt, ti++;
+            int group = kb / p.group_blocks, in_group = kb % p.group_blocks;
+            // scale and zero point are requested one item ahead, and only when the item's tile or group differs
+            __half next_scale = __float2half_rn(0.f);
+            uint32_t next_zeros = 0x77777777u;
+            int n = tile_n0(ti) + tn;  // this thread's column in the current tile
+            auto request = [&]() {
+                next_scale = __float2half_rn(0.f), next_zeros = 0x77777777u;
+                if (ti < tiles_cta && n < p.N) {
+                    next_scale = p.sc[(int64_t)group * p.N + n];
+                    if (p.qz) next_zeros = p.qz[(int64_t)group * p.zcols + (n >> 3)] >> ((n & 7) * 4);
+                }
+            };
+            request();
+            bool fresh = true;
+            __half2 scale2 = __float2half2_rn(0.f), zsub = scale2, zfma = scale2;
+            int s = kg;
+            uint32_t ph = 0;
+            bool ok = true;
+            while (ti < tiles_cta && ok) {
+                if (fresh) {
+                    const float z = (float)((next_zeros & 15u) + 1u);
+                    scale2 = __half2half2(next_scale);
+                    zsub = __float2half2_rn(1024.f + z);
+                    zfma = __float2half2_rn(-(64.f + z));
+                    fresh = false;
+                }
+                // advance to the set's next item; a new tile or group is requested now and lands during this unpack
+                kb += KG, in_group += KG;
+                if (kb >= KBt) {
+                    do kb -= KBt, ti++;
+                    while (kb >= KBt);
+                    n = tile_n0(ti) + tn;
+                    group = kb / p.group_blocks, in_group = kb % p.group_blocks;
+                    request();
+                    fresh = true;
+                } else if (in_group >= p.group_blocks) {
+                    do in_group -= p.group_blocks, group++;
+                    while (in_group >= p.group_blocks);
+                    request();
+                    fresh = true;
+                }
+                ok = mbar_wait(&full[s], ph, abort_flag, p.status, 4);
+                if (!ok) break;
+                uint8_t *stage = smem + s * S::STAGE_BYTES;
+                const uint32_t *src = (const uint32_t *)(stage + src_off);
+#pragma unroll
+                for (int rr = 0; rr < RPT; rr++) {
+                    uint32_t w = src[rr * COLS];
+                    const uint32_t lo0 = (w & 0x000f000fu) | 0x64006400u;
+                    const uint32_t hi0 = (w & 0x00f000f0u) | 0x64006400u;
+                    w >>= 8;
+                    const uint32_t lo1 = (w & 0x000f000fu) | 0x64006400u;
+                    const uint32_t hi1 = (w & 0x00f000f0u) | 0x64006400u;
+                    const __half2 a = __hmul2(__hsub2(*(const __half2 *)&lo0, zsub), scale2);
+                    const __half2 b = __hmul2(__hfma2(*(const __half2 *)&hi0, sixteenth, zfma), scale2);
+                    const __half2 c = __hmul2(__hsub2(*(const __half2 *)&lo1, zsub), scale2);
+                    const __half2 d = __hmul2(__hfma2(*(const __half2 *)&hi1, sixteenth, zfma), scale2);
+                    const uint32_t ua = *(const uint32_t *)&a, ub = *(const uint32_t *)&b;
+                    const uint32_t uc = *(const uint32_t *)&c, ud = *(const uint32_t *)&d;
+                    uint4 o;
+                    o.x = __byte_perm(ua, ub, 0x5410);
+                    o.y = __byte_perm(uc, ud, 0x5410);
+                    o.z = __byte_perm(ua, ub, 0x7632);
+                    o.w = __byte_perm(uc, ud, 0x7632);
+                    *(uint4 *)(stage + dst_off[rr]) = o;
+                }
+                fence_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&deq[s]);
+                s += KG;
+                if (s >= STAGES) s -= STAGES, ph ^= 1;
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue: warp w drains TMEM lanes 32 * (w % 4) ..
+        const int q = warp & 3;
+        bool ok = true;
+        for (int ti = 0; ti < tiles_cta && ok; ti++) {
+            const int buf = ti % NBUF, use = ti / NBUF;
+            ok = mbar_wait_idle(&acc_full[buf], (uint32_t)use & 1u, abort_flag, p.status, 5);
+            if (!ok) break;
+            tc_fence_after();
+            const int m0 = tile_m0(ti), n0 = tile_n0(ti);
+            const uint32_t acc = tmem_base + (uint32_t)buf * ACC_ALL + ((uint32_t)(q * 32) << 16);
+#pragma unroll 1
+            for (int h = 0; h < NH; h++) {
+                const int n = n0 + h * BN + q * 32 + lane;
+                const float bias = (p.bias && n < p.N) ? p.bias[n] : 0.f;
+                auto store16 = [&](const uint32_t (&r)[16], int c) {
+                    if (n < p.N) {
+#pragma unroll
+                        for (int j = 0; j < 16; j++) {
+                            const int m = m0 + c + j;
+                            if (m < p.M) {
+                                const float v = __uint_as_float(r[j]) + bias;
+                                if constexpr (!GATHER) {
+                                    if (p.out_f16) ((__half *)p.out)[(int64_t)m * p.N + n] = __float2half_rn(v);
+                                    else ((float *)p.out)[(int64_t)m * p.N + n] = v;
+                                } else {
+                                    const int64_t o = (int64_t)m * p.ld_out + p.col0 + n;
+                                    if (p.out_f16) {
+                                        const __half hv = __float2half_rn(v);
+                                        ((__half *)p.dst[0])[o] = hv;
+                                        if (p.n_dst > 1) {
+#pragma unroll
+                                            for (int g = 1; g < kMaxGatherDst; g++)
+                                                if (g < p.n_dst) ((__half *)p.dst[g])[o] = hv;
+                                        }
+                                    } else {
+                                        ((float *)p.dst[0])[o] = v;
+                                        if (p.n_dst > 1) {
+#pragma unroll
+                                            for (int g = 1; g < kMaxGatherDst; g++)
+                                                if (g < p.n_dst) ((float *)p.dst[g])[o] = v;
+                                        }
+                                    }
+                                }
+                            }
+                        }
+                    }
+                };
+#pragma unroll 1
+                for (int c = 0; c < MT; c += 16) {
+                    uint32_t r[16];
+                    tmem_ld_32x32b_x16(acc + (uint32_t)(h * ACC_COLS + c), r);
+                    tmem_ld_wait();
+                    store16(r, c);
+                }
+            }
+            // the accumulator set may be overwritten once all four warps have read it
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
 __global__ void cast_f32_to_f16_kernel(const float *__restrict__ in, __half *__restrict__ out, int64_t n)
 {
     int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
@@ -501,6 +792,15 @@ static int env_int(const char *name)
     return v ? atoi(v) : 0;
 }
 
+// WEBLLM_B200_GEMM_PERSIST=1 sends launches with more tiles than SMs to the persistent tile loop. Off by default: as
+// measured, its four epilogue warps drain a tile more slowly than the sixteen unpack warps of the one-tile kernel do,
+// and that drain did not hide behind the next tile's MMAs.
+static bool persist_enabled()
+{
+    static const bool on = [] { const char *e = getenv("WEBLLM_B200_GEMM_PERSIST"); return e && e[0] == '1'; }();
+    return on;
+}
+
 // Tile (mt tokens x 128 * nh output columns) and number of K slices, by a small cost model in microseconds whose
 // constants are measurements: the time of one 64-k block of a tile (the unpack of the weight tile bounds it, so it
 // depends on the columns far more than on the tokens), a fixed time per tile (pipeline fill, TMEM drain and stores),
@@ -511,7 +811,7 @@ static void pick_plan(int64_t M, int64_t N, int kblocks, int sms, int force_spli
     static const int force_mt = env_int("WEBLLM_B200_GEMM_MT"), force_nh = env_int("WEBLLM_B200_GEMM_NH"),
                      env_split = env_int("WEBLLM_B200_GEMM_SPLIT");
     if (force_split <= 0) force_split = env_split;
-    static const int mts[5] = {16, 32, 64, 128, 256};
+    static const int mts[6] = {16, 32, 64, 128, 192, 256};  // 192 exists to fit the waves (e.g. 11 x 38 tiles on 148 SMs)
     double best = -1.;
     *mt_out = 128, *nh_out = 1, *s_out = 1;
     for (int mt : mts) {
@@ -521,7 +821,7 @@ static void pick_plan(int64_t M, int64_t N, int kblocks, int sms, int force_spli
         for (int nh = 1; nh <= 2; nh++) {
             if (force_nh && nh != force_nh && mt >= 128 && N >= 256) continue;  // pinned wherever it exists
             if (nh == 2 && (mt < 128 || N < 256)) continue;
-            const double t_kb = nh == 2 ? (mt == 256 ? 0.91 : 0.80) : (mt == 256 ? 0.62 : 0.55);
+            const double t_kb = nh == 2 ? (mt == 256 ? 0.91 : mt == 192 ? 0.855 : 0.80) : (mt == 256 ? 0.62 : mt == 192 ? 0.585 : 0.55);
             const double t_tile = 1.5 + 2.7 * nh * mt / 256.;
             const int64_t tiles = ((M + mt - 1) / mt) * ((N + 128 * nh - 1) / (128 * nh));
             for (int S = 1; S <= 16; S++) {
@@ -531,6 +831,9 @@ static void pick_plan(int64_t M, int64_t N, int kblocks, int sms, int force_spli
                 if (S > 1 && (double)S * M * N * 4. > 64e6) continue;  // partial sums must fit the workspace
                 const int64_t waves = (tiles * S + sms - 1) / sms;
                 double t = 2.0 + waves * (per * t_kb + t_tile);
+                // persistent CTAs (where TMEM holds two accumulator sets): fill, drain and stores are paid once
+                if (S == 1 && tiles > sms && persist_enabled() && 2 * (mt < 32 ? 32 : mt) * nh <= 512)
+                    t = 2.0 + t_tile + waves * per * t_kb;
                 if (S > 1) t += 2.5 + (S + 1) * (double)M * N * 4. / 4e6;
                 if (best < 0. || t < best) best = t, *mt_out = mt, *nh_out = nh, *s_out = S;
             }
@@ -562,7 +865,7 @@ int plan_gemm_tc(wb_context *ctx, const Weight &w, int64_t M, int act_dtype, int
 }
 
 template <int MT, bool DENSE, int NH>
-static cudaError_t launch_tc(const CUtensorMap &mx, const CUtensorMap &mw, const tc::Params &p, dim3 grid, cudaStream_t st)
+static cudaError_t launch_tc(const CUtensorMap &mx, const CUtensorMap &mw, const tc::Params &p, dim3 grid, cudaStream_t st, int sms)
 {
     constexpr int smem = tc::Smem<MT, DENSE, NH>::TOTAL;
     auto go = [&](auto kernel) {
@@ -571,24 +874,40 @@ static cudaError_t launch_tc(const CUtensorMap &mx, const CUtensorMap &mw, const
         kernel<<<grid, tc::THREADS, smem, st>>>(mx, mw, p);
         return cudaGetLastError();
     };
+    // more tiles than SMs and no K split: one persistent CTA per SM walks the tiles (opt-in, see persist_enabled)
+    const bool persist_on = persist_enabled();
+    const int n_tiles = (int)(grid.x * grid.y);
+    auto go_persist = [&](auto kernel) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return e;
+        kernel<<<dim3((unsigned)sms), tc::THREADS_P, smem, st>>>(mx, mw, p, (int)grid.x, n_tiles);
+        return cudaGetLastError();
+    };
     if (grid.z > 1) return go(tc::gemm_tc_kernel<MT, DENSE, true, NH, false>);  // slices write partial sums: no placement
+    // only where TMEM holds two accumulator sets: with one set the MMAs would wait for four warps to drain it
+    constexpr bool two_sets = 2 * (MT < 32 ? 32 : MT) * NH <= 512;
+    const bool persist = persist_on && two_sets && n_tiles > sms;
     if constexpr (!DENSE) {
-        if (p.n_dst > 0) return go(tc::gemm_tc_kernel<MT, DENSE, false, NH, true>);
+        if (p.n_dst > 0)
+            return persist ? go_persist(tc::gemm_tc_persist_kernel<MT, DENSE, NH, true>)
+                           : go(tc::gemm_tc_kernel<MT, DENSE, false, NH, true>);
     }
-    return go(tc::gemm_tc_kernel<MT, DENSE, false, NH, false>);
+    return persist ? go_persist(tc::gemm_tc_persist_kernel<MT, DENSE, NH, false>)
+                   : go(tc::gemm_tc_kernel<MT, DENSE, false, NH, false>);
 }
 
-// tile_n = 256 (two accumulators per CTA) exists for the 128- and 256-token tiles only
+// tile_n = 256 (two accumulators per CTA) exists for the 128-, 192- and 256-token tiles only
 template <bool DENSE>
 static cudaError_t launch_tc_mt(int mt, int nh, const CUtensorMap &mx, const CUtensorMap &mw, const tc::Params &p, dim3 grid,
-                                cudaStream_t st)
+                                cudaStream_t st, int sms)
 {
     switch (mt) {
-    case 16: return launch_tc<16, DENSE, 1>(mx, mw, p, grid, st);
-    case 32: return launch_tc<32, DENSE, 1>(mx, mw, p, grid, st);
-    case 64: return launch_tc<64, DENSE, 1>(mx, mw, p, grid, st);
-    case 128: return nh == 2 ? launch_tc<128, DENSE, 2>(mx, mw, p, grid, st) : launch_tc<128, DENSE, 1>(mx, mw, p, grid, st);
-    default: return nh == 2 ? launch_tc<256, DENSE, 2>(mx, mw, p, grid, st) : launch_tc<256, DENSE, 1>(mx, mw, p, grid, st);
+    case 16: return launch_tc<16, DENSE, 1>(mx, mw, p, grid, st, sms);
+    case 32: return launch_tc<32, DENSE, 1>(mx, mw, p, grid, st, sms);
+    case 64: return launch_tc<64, DENSE, 1>(mx, mw, p, grid, st, sms);
+    case 128: return nh == 2 ? launch_tc<128, DENSE, 2>(mx, mw, p, grid, st, sms) : launch_tc<128, DENSE, 1>(mx, mw, p, grid, st, sms);
+    case 192: return nh == 2 ? launch_tc<192, DENSE, 2>(mx, mw, p, grid, st, sms) : launch_tc<192, DENSE, 1>(mx, mw, p, grid, st, sms);
+    default: return nh == 2 ? launch_tc<256, DENSE, 2>(mx, mw, p, grid, st, sms) : launch_tc<256, DENSE, 1>(mx, mw, p, grid, st, sms);
     }
 }
 
@@ -635,12 +954,12 @@ int launch_gemm_tc(wb_context *ctx, const Weight &w, const void *A, void *C, con
         p.sc = (const __half *)(base + w.off_scales);
         p.zcols = (int)w.zcols;
         p.group_blocks = (int)(w.group / 64);
-        e = launch_tc_mt<false>(mt, nh, mx, mw, p, grid, ctx->stream);
+        e = launch_tc_mt<false>(mt, nh, mx, mw, p, grid, ctx->stream, ctx->sm_count);
     } else {
         WB_CHECK(make_map_2d(ctx, &mw, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, base + w.off_main, (uint64_t)w.K, (uint64_t)w.N,
                              tc::BK, tc::BN * nh, true));
         p.qz = nullptr, p.sc = nullptr, p.zcols = 0, p.group_blocks = 1;
-        e = launch_tc_mt<true>(mt, nh, mx, mw, p, grid, ctx->stream);
+        e = launch_tc_mt<true>(mt, nh, mx, mw, p, grid, ctx->stream, ctx->sm_count);
     }
     ctx->launches++;
     WB_CUDA(e);

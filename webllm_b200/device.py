@@ -187,6 +187,10 @@ class Gpu:
     def peer_close(self, base: int) -> None:
         L.check(self._lib.wb_peer_close(self._ctx, C.c_void_p(base)))
 
+    def read_sweep(self, offset: int, nbytes: int, ctas: int, arena: int = L.WB_ARENA_WEIGHTS) -> None:
+        """One pass of plain reads over a byte range of a slab (``wb_read_sweep``), for bandwidth comparisons."""
+        L.check(self._lib.wb_read_sweep(self._ctx, arena, offset, nbytes, ctas))
+
     def hint_next(self, weight: int | None) -> None:
         """The next ``linear`` call also asks the L2 to fetch ``weight``, which a later call will stream."""
         L.check(self._lib.wb_linear_hint_next(self._ctx, -1 if weight is None else weight))

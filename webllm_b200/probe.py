@@ -4,6 +4,7 @@
     python -m webllm_b200.probe gemm   K N M [--reps 2]
     python -m webllm_b200.probe decode [--steps 3] [--prompt 64] [--mode auto|graph|single] [--layers 24]
     python -m webllm_b200.probe sweep  [--which batch|big|all]
+    python -m webllm_b200.probe read   [--mb 35.3]         (plain read of that many bytes, the GEMV's yardstick)
     python -m webllm_b200.probe shard      [--m 4096]      (one process per GPU: run under torch.distributed.run)
     python -m webllm_b200.probe dp-prefill [--seqs 256]    (one process per GPU: run under torch.distributed.run)
 
@@ -118,6 +119,32 @@ def _sweep(args) -> None:
         for name, (K, N) in synthetic.QWEN7B_SHAPES.items():
             if name in ("q", "k", "gate", "down"):
                 case(name + "7b", K, N, (1, 4096))
+
+
+def _read(args) -> None:
+    """A kernel that only reads: `copies` ranges of --mb megabytes in rotation (more than L2 in all), replayed as a
+    command batch like the GEMV timings, for several grid sizes."""
+    import torch
+    nbytes = int(args.mb * 1e6) // 256 * 256
+    copies = max(2, int(300e6 // nbytes) + 1)
+    gpu = Gpu(0, weight_bytes=copies * nbytes + (1 << 20), act_bytes=1 << 20)
+    stream = torch.cuda.Stream()
+    gpu.set_stream(stream.cuda_stream)
+    for ctas in (148, 296, 592, 1184):
+        with gpu.batch() as b:
+            for i in range(copies):
+                gpu.read_sweep(i * nbytes, nbytes, ctas)
+        for _ in range(3):
+            b.submit()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(10):
+            b.submit()
+        e1.record(stream)
+        e1.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / 10 / copies
+        b.destroy()
+        print(f"read {nbytes} bytes, {ctas:4d} CTAs x 256: {us:7.2f} us per launch, {nbytes / us / 1e3:7.1f} GB/s", flush=True)
 
 
 def _dist_init():
@@ -276,12 +303,16 @@ def main(argv=None) -> None:
     d.add_argument("--layers", type=int, default=synthetic.QWEN25_05B.n_layer)
     w = sub.add_parser("sweep")
     w.add_argument("--which", choices=("batch", "big", "all"), default="all")
+    rd = sub.add_parser("read")
+    rd.add_argument("--mb", type=float, default=35.273728)
     sh = sub.add_parser("shard")
     sh.add_argument("--m", type=int, default=4096)
     dp = sub.add_parser("dp-prefill")
     dp.add_argument("--seqs", type=int, default=256)
     args = ap.parse_args(argv)
-    if args.cmd == "shard":
+    if args.cmd == "read":
+        _read(args)
+    elif args.cmd == "shard":
         _shard(args)
     elif args.cmd == "dp-prefill":
         _dp_prefill(args)
