@@ -185,13 +185,13 @@ _FORCED = any(os.environ.get(v) is not None for v in ("WEBLLM_B200_GEMM_NH", "WE
 
 @pytest.mark.skipif(_FORCED, reason="already the forced run")
 @pytest.mark.parametrize("var,value", [("WEBLLM_B200_GEMM_NH", "2"), ("WEBLLM_B200_GEMM_MT", "192"),
-                                       ("WEBLLM_B200_GEMM_PERSIST", "1")])
+                                       ("WEBLLM_B200_GEMM_PERSIST", "0")])
 def test_every_tile_shape_forced(var, value):
     """The tile switches are read once per process, so the ragged-M, dense and split-K cases above run again in child
     processes: once with the 256-column tile forced for every token count from 100 up (128 x 256 and 256 x 256), and
     once with the 192-token tile (the one the planner picks to fit the waves, 256 or 512 TMEM columns) forced for
-    every token count, and once with the persistent tile loop switched on (it is opt-in), which the prefill sizes (more
-    tiles than SMs) then take."""
+    every token count, and once with the persistent tile loop switched off, so that the prefill sizes (more tiles than
+    SMs), which otherwise take the persistent kernel, also go through the one-tile-per-CTA kernel."""
     env = dict(os.environ)
     env[var] = value
     r = subprocess.run([sys.executable, "-m", "pytest", __file__, "-q", "-x", "-k", "ragged or dense or split_k_gemm or 7b or m2048"],

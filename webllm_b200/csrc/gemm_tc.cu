@@ -166,6 +166,127 @@ struct Params {
     void *dst[kMaxGatherDst];
 };
 
+
+// ---- epilogue stores. After tcgen05.ld a lane holds ONE output column (its TMEM lane) of 16 token rows, so a plain
+// store instruction writes 2 or 4 bytes per lane, 64 or 128 bytes of one row per warp. Measured on the 0.5B gate
+// projection at M = 2048, those stores cost as much as the whole k-loop (20 MB of fp16 output left at ~1 TB/s, and
+// the same time for f32: the cost is per store instruction, not per byte). So the lanes first transpose among
+// themselves with shuffles (xor 1, 2, 4) until each holds 16 bytes of consecutive columns of one row: 2 (fp16) or 4
+// (f32) store instructions per 16 rows instead of 16.
+struct StoreDst {
+    void *dst[kMaxGatherDst];
+    int n_dst;
+    int64_t ld;   // row pitch in elements
+    int col0;     // column of the tile's column 0 in the destination row
+};
+
+template <bool MULTI>
+__device__ __forceinline__ void store_u4(const StoreDst &d, int64_t off_bytes, const uint4 &v)
+{
+    *(uint4 *)((char *)d.dst[0] + off_bytes) = v;
+    if constexpr (MULTI) {
+        if (d.n_dst > 1) {
+#pragma unroll
+            for (int g = 1; g < kMaxGatherDst; g++)  // static indices: a run-time index would move the array to local memory
+                if (g < d.n_dst) *(uint4 *)((char *)d.dst[g] + off_bytes) = v;
+        }
+    }
+}
+
+// r: this lane's column n_warp + lane, token rows m_base .. m_base + 15 (f32 bits); bias already per lane.
+template <bool MULTI>
+__device__ __forceinline__ void store_block16_f16(const StoreDst &d, const uint32_t (&r)[16], float bias, int m_base, int M,
+                                                  int n_warp, int N, int lane)
+{
+    const bool b = lane & 1, c = lane & 2, e = lane & 4;
+    uint32_t h[8];  // h[i]: columns (n & ~1, + 1) of row 2 i + b
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const float v0 = __uint_as_float(r[2 * i]) + bias, v1 = __uint_as_float(r[2 * i + 1]) + bias;
+        const float got = __shfl_xor_sync(0xffffffffu, b ? v0 : v1, 1);
+        const __half2 pr = b ? __floats2half2_rn(got, v1) : __floats2half2_rn(v0, got);
+        h[i] = *(const uint32_t *)&pr;
+    }
+    uint2 o[4];  // o[k]: four consecutive columns of row 4 k + 2 c + b
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+        const uint32_t got = __shfl_xor_sync(0xffffffffu, c ? h[2 * k] : h[2 * k + 1], 2);
+        o[k] = c ? make_uint2(got, h[2 * k + 1]) : make_uint2(h[2 * k], got);
+    }
+    const int n8 = n_warp + (lane >> 3) * 8;
+#pragma unroll
+    for (int k = 0; k < 2; k++) {  // eight consecutive columns of row 8 k + (lane & 7)
+        const uint2 snd = e ? o[2 * k] : o[2 * k + 1];
+        const uint32_t gx = __shfl_xor_sync(0xffffffffu, snd.x, 4), gy = __shfl_xor_sync(0xffffffffu, snd.y, 4);
+        const uint4 f = e ? make_uint4(gx, gy, o[2 * k + 1].x, o[2 * k + 1].y) : make_uint4(o[2 * k].x, o[2 * k].y, gx, gy);
+        const int m = m_base + 8 * k + (lane & 7);
+        if (m < M && n8 < N) store_u4<MULTI>(d, ((int64_t)m * d.ld + d.col0 + n8) * 2, f);
+    }
+}
+
+template <bool MULTI>
+__device__ __forceinline__ void store_block16_f32(const StoreDst &d, const uint32_t (&r)[16], float bias, int m_base, int M,
+                                                  int n_warp, int N, int lane)
+{
+    const bool b = lane & 1, c = lane & 2;
+    float2 pr[8];  // pr[i]: columns (n & ~1, + 1) of row 2 i + b
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const float v0 = __uint_as_float(r[2 * i]) + bias, v1 = __uint_as_float(r[2 * i + 1]) + bias;
+        const float got = __shfl_xor_sync(0xffffffffu, b ? v0 : v1, 1);
+        pr[i] = b ? make_float2(got, v1) : make_float2(v0, got);
+    }
+    const int n4 = n_warp + (lane >> 2) * 4;
+#pragma unroll
+    for (int k = 0; k < 4; k++) {  // four consecutive columns of row 4 k + (lane & 3)
+        const float2 snd = c ? pr[2 * k] : pr[2 * k + 1];
+        const float gx = __shfl_xor_sync(0xffffffffu, snd.x, 2), gy = __shfl_xor_sync(0xffffffffu, snd.y, 2);
+        const float4 f = c ? make_float4(gx, gy, pr[2 * k + 1].x, pr[2 * k + 1].y) : make_float4(pr[2 * k].x, pr[2 * k].y, gx, gy);
+        const int m = m_base + 4 * k + (lane & 3);
+        if (m < M && n4 < N)
+            store_u4<MULTI>(d, ((int64_t)m * d.ld + d.col0 + n4) * 4,
+                            make_uint4(__float_as_uint(f.x), __float_as_uint(f.y), __float_as_uint(f.z), __float_as_uint(f.w)));
+    }
+}
+
+// One 16-row block of a warp's 32 columns to its destination(s): transposed 16-byte stores where rows and column
+// groups are 16-byte aligned (N, pitch and column offset multiples of 8), else one element per lane.
+template <bool MULTI>
+__device__ __forceinline__ void store_block16(const StoreDst &d, bool f16, bool vec, const uint32_t (&r)[16], float bias, int m_base,
+                                              int M, int n_warp, int N, int lane)
+{
+    if (vec) {
+        if (f16) store_block16_f16<MULTI>(d, r, bias, m_base, M, n_warp, N, lane);
+        else store_block16_f32<MULTI>(d, r, bias, m_base, M, n_warp, N, lane);
+        return;
+    }
+    const int n = n_warp + lane;
+    if (n >= N) return;
+#pragma unroll
+    for (int j = 0; j < 16; j++) {
+        const int m = m_base + j;
+        if (m < M) {
+            const float v = __uint_as_float(r[j]) + bias;
+            const int64_t o = (int64_t)m * d.ld + d.col0 + n;
+            if (f16) {
+                const __half hv = __float2half_rn(v);
+                ((__half *)d.dst[0])[o] = hv;
+                if constexpr (MULTI) {
+#pragma unroll
+                    for (int g = 1; g < kMaxGatherDst; g++)
+                        if (g < d.n_dst) ((__half *)d.dst[g])[o] = hv;
+                }
+            } else {
+                ((float *)d.dst[0])[o] = v;
+                if constexpr (MULTI) {
+#pragma unroll
+                    for (int g = 1; g < kMaxGatherDst; g++)
+                        if (g < d.n_dst) ((float *)d.dst[g])[o] = v;
+                }
+            }
+        }
+    }
+}
 }  // namespace tc
 
 namespace tc {
@@ -373,53 +494,32 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             constexpr int CSPAN = MT / NSPLIT;
             const int c_begin = ((warp - 2) >> 2) * CSPAN;
             const int c_end = ((warp - 2) >> 2) < NSPLIT ? c_begin + CSPAN : c_begin;
+            // where the block goes: this slice's f32 partial sums, the dense local result, or the placement of a
+            // column-sharded call
+            StoreDst d;
+            bool out16;
+            if (split) {
+                d.dst[0] = part, d.n_dst = 1, d.ld = p.N, d.col0 = 0, out16 = false;
+            } else if constexpr (GATHER) {
+#pragma unroll
+                for (int g = 0; g < kMaxGatherDst; g++) d.dst[g] = p.dst[g];
+                d.n_dst = p.n_dst, d.ld = p.ld_out, d.col0 = p.col0, out16 = p.out_f16 != 0;
+            } else {
+                d.dst[0] = p.out, d.n_dst = 1, d.ld = p.N, d.col0 = 0, out16 = p.out_f16 != 0;
+            }
+            const bool vec = (p.N & 7) == 0 && (d.ld & 7) == 0 && (d.col0 & 7) == 0;
 #pragma unroll 1
             for (int h = 0; h < NH; h++) {
-            const int n = n0 + h * BN + q * 32 + lane;
-            const float bias = (!split && p.bias && n < p.N) ? p.bias[n] : 0.f;
+                const int n_warp = n0 + h * BN + q * 32;
+                const int n = n_warp + lane;
+                const float bias = (!split && p.bias && n < p.N) ? p.bias[n] : 0.f;
 #pragma unroll 1
-            for (int c = c_begin; c < c_end; c += 16) {
-                uint32_t r[16];
-                tmem_ld_32x32b_x16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(h * ACC_COLS + c), r);
-                tmem_ld_wait();
-                if (n < p.N) {
-#pragma unroll
-                    for (int j = 0; j < 16; j++) {
-                        const int m = m0 + c + j;
-                        if (m < p.M) {
-                            const float v = __uint_as_float(r[j]) + bias;
-                            if (split) {
-                                part[(int64_t)m * p.N + n] = v;  // this slice's partial sum, f32
-                            } else {
-                                if constexpr (!GATHER) {
-                                if (p.out_f16) ((__half *)p.out)[(int64_t)m * p.N + n] = __float2half_rn(v);
-                                else ((float *)p.out)[(int64_t)m * p.N + n] = v;
-                                } else {
-                                // destinations are indexed statically (unrolled): a run-time index into the
-                                // kernel's parameters would move them to local memory
-                                const int64_t o = (int64_t)m * p.ld_out + p.col0 + n;
-                                if (p.out_f16) {
-                                    const __half hv = __float2half_rn(v);
-                                    ((__half *)p.dst[0])[o] = hv;
-                                    if (p.n_dst > 1) {
-#pragma unroll
-                                        for (int g = 1; g < kMaxGatherDst; g++)
-                                            if (g < p.n_dst) ((__half *)p.dst[g])[o] = hv;
-                                    }
-                                } else {
-                                    ((float *)p.dst[0])[o] = v;
-                                    if (p.n_dst > 1) {
-#pragma unroll
-                                        for (int g = 1; g < kMaxGatherDst; g++)
-                                            if (g < p.n_dst) ((float *)p.dst[g])[o] = v;
-                                    }
-                                }
-                                }
-                            }
-                        }
-                    }
+                for (int c = c_begin; c < c_end; c += 16) {
+                    uint32_t r[16];
+                    tmem_ld_32x32b_x16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(h * ACC_COLS + c), r);
+                    tmem_ld_wait();
+                    store_block16<GATHER>(d, out16, vec, r, bias, m0 + c, p.M, n_warp, p.N, lane);
                 }
-            }
             }
         }
     }
@@ -646,49 +746,27 @@ gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
             tc_fence_after();
             const int m0 = tile_m0(ti), n0 = tile_n0(ti);
             const uint32_t acc = tmem_base + (uint32_t)buf * ACC_ALL + ((uint32_t)(q * 32) << 16);
+            StoreDst d;
+            if constexpr (GATHER) {
+#pragma unroll
+                for (int g = 0; g < kMaxGatherDst; g++) d.dst[g] = p.dst[g];
+                d.n_dst = p.n_dst, d.ld = p.ld_out, d.col0 = p.col0;
+            } else {
+                d.dst[0] = p.out, d.n_dst = 1, d.ld = p.N, d.col0 = 0;
+            }
+            const bool out16 = p.out_f16 != 0;
+            const bool vec = (p.N & 7) == 0 && (d.ld & 7) == 0 && (d.col0 & 7) == 0;
 #pragma unroll 1
             for (int h = 0; h < NH; h++) {
-                const int n = n0 + h * BN + q * 32 + lane;
+                const int n_warp = n0 + h * BN + q * 32;
+                const int n = n_warp + lane;
                 const float bias = (p.bias && n < p.N) ? p.bias[n] : 0.f;
-                auto store16 = [&](const uint32_t (&r)[16], int c) {
-                    if (n < p.N) {
-#pragma unroll
-                        for (int j = 0; j < 16; j++) {
-                            const int m = m0 + c + j;
-                            if (m < p.M) {
-                                const float v = __uint_as_float(r[j]) + bias;
-                                if constexpr (!GATHER) {
-                                    if (p.out_f16) ((__half *)p.out)[(int64_t)m * p.N + n] = __float2half_rn(v);
-                                    else ((float *)p.out)[(int64_t)m * p.N + n] = v;
-                                } else {
-                                    const int64_t o = (int64_t)m * p.ld_out + p.col0 + n;
-                                    if (p.out_f16) {
-                                        const __half hv = __float2half_rn(v);
-                                        ((__half *)p.dst[0])[o] = hv;
-                                        if (p.n_dst > 1) {
-#pragma unroll
-                                            for (int g = 1; g < kMaxGatherDst; g++)
-                                                if (g < p.n_dst) ((__half *)p.dst[g])[o] = hv;
-                                        }
-                                    } else {
-                                        ((float *)p.dst[0])[o] = v;
-                                        if (p.n_dst > 1) {
-#pragma unroll
-                                            for (int g = 1; g < kMaxGatherDst; g++)
-                                                if (g < p.n_dst) ((float *)p.dst[g])[o] = v;
-                                        }
-                                    }
-                                }
-                            }
-                        }
-                    }
-                };
 #pragma unroll 1
                 for (int c = 0; c < MT; c += 16) {
                     uint32_t r[16];
                     tmem_ld_32x32b_x16(acc + (uint32_t)(h * ACC_COLS + c), r);
                     tmem_ld_wait();
-                    store16(r, c);
+                    store_block16<GATHER>(d, out16, vec, r, bias, m0 + c, p.M, n_warp, p.N, lane);
                 }
             }
             // the accumulator set may be overwritten once all four warps have read it
@@ -792,12 +870,11 @@ static int env_int(const char *name)
     return v ? atoi(v) : 0;
 }
 
-// WEBLLM_B200_GEMM_PERSIST=1 sends launches with more tiles than SMs to the persistent tile loop. Off by default: as
-// measured, its four epilogue warps drain a tile more slowly than the sixteen unpack warps of the one-tile kernel do,
-// and that drain did not hide behind the next tile's MMAs.
+// WEBLLM_B200_GEMM_PERSIST=0 keeps every launch on the one-tile-per-CTA kernel (for comparisons). Otherwise launches
+// with more tiles than SMs whose accumulators fit TMEM twice take the persistent tile loop.
 static bool persist_enabled()
 {
-    static const bool on = [] { const char *e = getenv("WEBLLM_B200_GEMM_PERSIST"); return e && e[0] == '1'; }();
+    static const bool on = [] { const char *e = getenv("WEBLLM_B200_GEMM_PERSIST"); return !(e && e[0] == '0'); }();
     return on;
 }
 
@@ -874,7 +951,7 @@ static cudaError_t launch_tc(const CUtensorMap &mx, const CUtensorMap &mw, const
         kernel<<<grid, tc::THREADS, smem, st>>>(mx, mw, p);
         return cudaGetLastError();
     };
-    // more tiles than SMs and no K split: one persistent CTA per SM walks the tiles (opt-in, see persist_enabled)
+    // more tiles than SMs and no K split: one persistent CTA per SM walks the tiles
     const bool persist_on = persist_enabled();
     const int n_tiles = (int)(grid.x * grid.y);
     auto go_persist = [&](auto kernel) {
