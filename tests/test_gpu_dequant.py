@@ -109,3 +109,21 @@ def test_f16_upload_matches_reference_conversion(gpu, oracle, golden):
     # chunked writes (writeF16Chunk) land at their element offset
     gpu.f16_write_chunk(h, 10, np.array([1.0, -0.5], np.float32))
     assert gpu.read_weight_f16(h, 10, 2).tolist() == [0x3C00, 0xB800]
+
+
+def test_read_sweep_diagnostic_runs_and_checks_its_range(gpu):
+    """wb_read_sweep (the bandwidth yardstick of `probe read`) launches one kernel over a slab range and refuses
+    ranges outside the slab or not in 16-byte units; it never writes, so the slab is unchanged afterwards."""
+    from webllm_b200 import _lib
+    data = np.arange(1 << 16, dtype=np.float32)
+    t = gpu.arena.alloc(data.size)
+    gpu.write(t, data)
+    before = gpu.launch_count
+    gpu.read_sweep(t.offset, data.nbytes, 148, arena=_lib.WB_ARENA_ACT)
+    gpu.synchronize()
+    assert np.array_equal(gpu.read(t), data)
+    assert gpu.launch_count == before + 1
+    with pytest.raises(WebllmError):
+        gpu.read_sweep(t.offset + 8, 1024, 148, arena=_lib.WB_ARENA_ACT)
+    with pytest.raises(WebllmError, match="outside the slab"):
+        gpu.read_sweep(0, 1 << 40, 148, arena=_lib.WB_ARENA_ACT)
