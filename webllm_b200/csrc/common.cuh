@@ -72,6 +72,7 @@ struct OutPlace {
     int64_t ld = 0;
     int col0 = 0;
     int n_dst = 0;  // 0: not a gather call
+    int elem_bytes = 4;  // size of an output element (what the planner needs to price the stores to the peers)
     void *dst[kMaxGatherDst] = {};
 };
 

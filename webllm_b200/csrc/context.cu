@@ -602,7 +602,7 @@ int wb_linear_gather(wb_context *ctx, wb_handle weight, uint64_t a_offset, uint6
         bias_ptr = (const float *)(ctx->arena[WB_ARENA_WEIGHTS].base + b->off_main);
     }
     OutPlace pl;
-    pl.ld = n_total, pl.col0 = (int)col_begin, pl.n_dst = 1 + n_peers;
+    pl.ld = n_total, pl.col0 = (int)col_begin, pl.n_dst = 1 + n_peers, pl.elem_bytes = (int)esz;
     pl.dst[0] = arena_ptr(ctx, WB_ARENA_ACT, c_offset);
     for (int g = 0; g < n_peers; g++) {
         if (!peer_bases[g]) return fail(WB_ERR_BAD_ARG, "wb_linear_gather: peer %d is NULL", g);

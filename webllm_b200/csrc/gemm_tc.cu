@@ -883,7 +883,7 @@ static bool persist_enabled()
 // depends on the columns far more than on the tokens), a fixed time per tile (pipeline fill, TMEM drain and stores),
 // and for split-K the reduce launch, which moves slices + 1 copies of the output.
 // WEBLLM_B200_GEMM_MT / _NH / _SPLIT pin one of the three for experiments.
-static void pick_plan(int64_t M, int64_t N, int kblocks, int sms, int force_split, int *mt_out, int *nh_out, int *s_out)
+static void pick_plan(int64_t M, int64_t N, int kblocks, int sms, int force_split, double t_remote, int *mt_out, int *nh_out, int *s_out)
 {
     static const int force_mt = env_int("WEBLLM_B200_GEMM_MT"), force_nh = env_int("WEBLLM_B200_GEMM_NH"),
                      env_split = env_int("WEBLLM_B200_GEMM_SPLIT");
@@ -909,8 +909,11 @@ static void pick_plan(int64_t M, int64_t N, int kblocks, int sms, int force_spli
                 const int64_t waves = (tiles * S + sms - 1) / sms;
                 double t = 2.0 + waves * (per * t_kb + t_tile);
                 // persistent CTAs (where TMEM holds two accumulator sets): fill, drain and stores are paid once
-                if (S == 1 && tiles > sms && persist_enabled() && 2 * (mt < 32 ? 32 : mt) * nh <= 512)
-                    t = 2.0 + t_tile + waves * per * t_kb;
+                const bool persist = S == 1 && tiles > sms && persist_enabled() && 2 * (mt < 32 ? 32 : mt) * nh <= 512;
+                if (persist) t = 2.0 + t_tile + waves * per * t_kb;
+                // a column-sharded call also stores the result into the peers: under the next tile's MMAs in the
+                // persistent loop, at the end of every CTA (on top of the arithmetic) otherwise
+                if (t_remote > 0.) t = persist ? (t > t_remote ? t : t_remote) : t + t_remote;
                 if (S > 1) t += 2.5 + (S + 1) * (double)M * N * 4. / 4e6;
                 if (best < 0. || t < best) best = t, *mt_out = mt, *nh_out = nh, *s_out = S;
             }
@@ -923,7 +926,9 @@ int plan_gemm_tc(wb_context *ctx, const Weight &w, int64_t M, int act_dtype, int
     (void)exact;
     const int kblocks = (int)(w.K / 64);
     int mt, nh, S;
-    pick_plan(M, w.N, kblocks, ctx->sm_count, ctx->force_split, &mt, &nh, &S);
+    // microseconds that the stores to the peers of a column-sharded call take at ~700 GB/s per direction
+    const double t_remote = ctx->place.n_dst > 1 ? (double)(ctx->place.n_dst - 1) * M * w.N * ctx->place.elem_bytes / 700e3 : 0.;
+    pick_plan(M, w.N, kblocks, ctx->sm_count, ctx->force_split, t_remote, &mt, &nh, &S);
     plan->kernel = WB_KERNEL_GEMM_TC;
     plan->grid_x = (int)((M + mt - 1) / mt);
     plan->grid_y = (int)((w.N + 128 * nh - 1) / (128 * nh));
