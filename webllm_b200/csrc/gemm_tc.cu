@@ -355,6 +355,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // Everything above (barriers, TMEM) ran under the tail of the previous kernel when this one was launched with
+    // programmatic stream serialization; nothing that the previous kernel writes or reads is touched before this point.
+    pdl_sync();
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
@@ -592,6 +595,9 @@ gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // Everything above (barriers, TMEM) ran under the tail of the previous kernel when this one was launched with
+    // programmatic stream serialization; nothing that the previous kernel writes or reads is touched before this point.
+    pdl_sync();
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
@@ -953,8 +959,7 @@ static cudaError_t launch_tc(const CUtensorMap &mx, const CUtensorMap &mw, const
     auto go = [&](auto kernel) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return e;
-        kernel<<<grid, tc::THREADS, smem, st>>>(mx, mw, p);
-        return cudaGetLastError();
+        return launch_pdl(kernel, grid, dim3(tc::THREADS), (size_t)smem, st, mx, mw, p);
     };
     // more tiles than SMs and no K split: one persistent CTA per SM walks the tiles
     const bool persist_on = persist_enabled();
@@ -962,8 +967,7 @@ static cudaError_t launch_tc(const CUtensorMap &mx, const CUtensorMap &mw, const
     auto go_persist = [&](auto kernel) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return e;
-        kernel<<<dim3((unsigned)sms), tc::THREADS_P, smem, st>>>(mx, mw, p, (int)grid.x, n_tiles);
-        return cudaGetLastError();
+        return launch_pdl(kernel, dim3((unsigned)sms), dim3(tc::THREADS_P), (size_t)smem, st, mx, mw, p, (int)grid.x, n_tiles);
     };
     if (grid.z > 1) return go(tc::gemm_tc_kernel<MT, DENSE, true, NH, false>);  // slices write partial sums: no placement
     // only where TMEM holds two accumulator sets: with one set the MMAs would wait for four warps to drain it
