@@ -474,8 +474,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                     request_group(group);
                     fresh = true;
                 }
+#ifdef WB_TC_TRACE
+                const bool tr = threadIdx.x == 64 && kb == kb0 + 2 * KG;  // set 0's third k-block
+                if (tr) TC_STAMP(10);
+#endif
                 ok = mbar_wait(&full[s], ph, abort_flag, p.status, 4);
                 if (!ok) break;
+#ifdef WB_TC_TRACE
+                if (tr) TC_STAMP(11);
+#endif
                 uint8_t *stage = smem + s * S::STAGE_BYTES;
                 const uint32_t *src = (const uint32_t *)(stage + src_off);
 #pragma unroll
@@ -502,12 +509,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 fence_async_smem();  // make the generic-proxy stores visible to the tensor core's reads
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&deq[s]);
+#ifdef WB_TC_TRACE
+                if (tr) TC_STAMP(7);
+#endif
                 s += KG;
                 if (s >= STAGES) s -= STAGES, ph ^= 1;
             }
         }
         // epilogue: warp w may touch TMEM lanes 32*(w%4) .. +31
-        if (threadIdx.x == 64) TC_STAMP(7);
         if (ok) ok = mbar_wait(acc_full, 0, abort_flag, p.status, 5);
         if (threadIdx.x == 64) TC_STAMP(8);
         if (ok) {
@@ -559,9 +568,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     __syncthreads();
     if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
         const unsigned long long t10 = tc_now(), b = tc_trace[0];
-        printf("tc trace ns: setup %llu pdl %llu tma0 %llu tma_all %llu mma0 %llu mma_all %llu unpack_done %llu acc_full %llu stores %llu end %llu\n",
-               tc_trace[1] - b, tc_trace[2] - b, tc_trace[3] - b, tc_trace[4] - b, tc_trace[5] - b, tc_trace[6] - b, tc_trace[7] - b,
-               tc_trace[8] - b, tc_trace[9] - b, t10 - b);
+        printf("tc trace ns: setup %llu pdl %llu tma0 %llu tma_all %llu mma0 %llu mma_all %llu acc_full %llu stores %llu end %llu | set 0, third k-block: wait from %llu to %llu, unpacked and signalled %llu\n",
+               tc_trace[1] - b, tc_trace[2] - b, tc_trace[3] - b, tc_trace[4] - b, tc_trace[5] - b, tc_trace[6] - b,
+               tc_trace[8] - b, tc_trace[9] - b, t10 - b, tc_trace[10] - b, tc_trace[11] - b, tc_trace[7] - b);
     }
 #endif
 }
