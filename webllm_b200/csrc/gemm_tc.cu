@@ -390,9 +390,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 if constexpr (DENSE) tma_load_2d(wd(s), &map_w, kb * BK, n0, &full[s]);
                 else tma_load_2d(wp(s), &map_w, n0, kb * 8, &full[s]);
                 if (kb == kb0) TC_STAMP(3);
+                if (kb == kb0 + STAGES - 1) TC_STAMP(4);  // the last copy that did not have to wait for a free stage
                 if (++s == STAGES) s = 0, ph ^= 1;
             }
-            TC_STAMP(4);
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
@@ -568,7 +568,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     __syncthreads();
     if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
         const unsigned long long t10 = tc_now(), b = tc_trace[0];
-        printf("tc trace ns: setup %llu pdl %llu tma0 %llu tma_all %llu mma0 %llu mma_all %llu acc_full %llu stores %llu end %llu | set 0, third k-block: wait from %llu to %llu, unpacked and signalled %llu\n",
+        printf("tc trace ns: setup %llu pdl %llu tma0 %llu tma_ring_filled %llu mma0 %llu mma_all %llu acc_full %llu stores %llu end %llu | set 0, third k-block: wait from %llu to %llu, unpacked and signalled %llu\n",
                tc_trace[1] - b, tc_trace[2] - b, tc_trace[3] - b, tc_trace[4] - b, tc_trace[5] - b, tc_trace[6] - b,
                tc_trace[8] - b, tc_trace[9] - b, t10 - b, tc_trace[10] - b, tc_trace[11] - b, tc_trace[7] - b);
     }
