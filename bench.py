@@ -66,7 +66,33 @@ class ClockSampler:
     def __init__(self, index: int):
         self.index, self.rows, self._stop, self._thread = index, [], threading.Event(), None
 
+    def _run_nvml(self) -> bool:
+        """Reads clocks and throttle reasons through NVML every 5 ms (read-only calls). False if NVML is unusable."""
+        try:
+            import pynvml as nv
+            nv.nvmlInit()
+            h = nv.nvmlDeviceGetHandleByIndex(self.index)
+            mx = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+            nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)
+        except Exception:
+            return False
+        bits = ((nv.nvmlClocksThrottleReasonHwSlowdown, 2), (nv.nvmlClocksThrottleReasonHwThermalSlowdown, 3),
+                (nv.nvmlClocksThrottleReasonSwThermalSlowdown, 4), (nv.nvmlClocksThrottleReasonSwPowerCap, 5))
+        while not self._stop.is_set():
+            try:
+                row = [str(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)), str(mx), "", "", "", ""]
+                reasons = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                for bit, col in bits:
+                    row[col] = "Active" if reasons & bit else "Not Active"
+                self.rows.append(row)
+            except Exception:
+                pass
+            self._stop.wait(0.005)
+        return True
+
     def _run(self):
+        if self._run_nvml():
+            return
         while not self._stop.is_set():
             try:
                 out = subprocess.run(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
