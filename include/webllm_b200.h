@@ -54,7 +54,9 @@ typedef enum {
     WB_KERNEL_GEMV_MMA = 1,   /* M <= 32: weights streamed once, register unpack, warp-level MMA, split-K */
     WB_KERNEL_GEMM_TC = 2,    /* tcgen05 / TMEM GEMM, TMA-fed, dequant in shared memory */
     WB_KERNEL_GENERIC = 3,    /* shape-agnostic CUDA kernel for ragged sizes (K%8, N%4, group%32 != 0) */
-    WB_KERNEL_DENSE_GEMV = 4  /* fp16 [N,K] weight, M <= 8 */
+    WB_KERNEL_DENSE_GEMV = 4, /* fp16 [N,K] weight, M <= 8 */
+    WB_KERNEL_GEMV_STREAM = 5 /* M <= 4 on bandwidth-bound shapes (whole 128-k chunks, N % 32 == 0, >= 20 chunks per K
+                                 slice): same arithmetic as GEMV_MMA, weights straight into registers, persistent CTAs */
 } wb_kernel_kind;
 
 typedef struct {
@@ -165,7 +167,7 @@ WB_API int wb_linear(wb_context *ctx, wb_handle weight, uint64_t a_offset, uint6
  *      still being multiplied (decode-size calls write a dense piece to the scratch tensor at tmp_offset,
  *      [M, N], and one small launch spreads it). The call is stream-ordered like wb_linear and does NOT wait for
  *      the peers: before any rank reads its full tensor, every rank's call must have completed (a barrier across
- *      the ranks after the call, e.g. a one-element NCCL all-reduce on the same streams), and no rank may still
+ *      the ranks after the call: wb_peer_barrier below, or any collective on the same streams), and no rank may still
  *      be reading the tensor when the next call writes it. Cannot be recorded into a command batch.
  *      wb_arena_ipc_export writes WB_IPC_HANDLE_BYTES bytes that another process on the same node passes to
  *      wb_peer_open to map this context's slab (only a slab made by wb_arena_create); wb_peer_close unmaps it. */
@@ -176,13 +178,52 @@ WB_API int wb_linear_gather(wb_context *ctx, wb_handle weight, uint64_t a_offset
 WB_API int wb_arena_ipc_export(wb_context *ctx, int arena, void *handle_out);
 WB_API int wb_peer_open(wb_context *ctx, const void *handle, void **base_out);
 WB_API int wb_peer_close(wb_context *ctx, void *base);
+/* The barrier that wb_linear_gather needs, done by a kernel of this library instead of a collective (no counterpart in
+ * the reference). `flags_offset` names WB_PEER_FLAG_BYTES bytes of the activation slab, the same offset on every rank;
+ * `rank` is this process's index among the n_peers + 1 ranks. wb_peer_barrier_init zeroes the flags and the context's
+ * epoch counter: every rank calls it once, and the ranks must meet on the host (any host-side barrier) between the
+ * last init and the first wb_peer_barrier. wb_peer_barrier is stream-ordered: the kernel stores an increasing epoch word
+ * into slot `rank` of every peer's flags (behind a system-scope fence, so everything this stream stored into the peers
+ * before it is visible first) and waits until every other slot of its own flags has reached the epoch. The wait is
+ * bounded: after timeout_us (0 = 2 s) the kernel records a code and returns, and the next wb_synchronize / wb_download
+ * returns WB_ERR_TIMEOUT; nothing hangs when a peer never arrives. Every rank must issue the same sequence of barriers.
+ * wb_linear_gather_barrier is wb_linear_gather followed by that barrier; for decode-size calls the copy into the peers
+ * and the barrier are one launch. */
+#define WB_PEER_FLAG_BYTES 256
+WB_API int wb_peer_barrier_init(wb_context *ctx, uint64_t flags_offset);
+WB_API int wb_peer_barrier(wb_context *ctx, uint64_t flags_offset, int rank, void *const *peer_bases, int n_peers,
+                           uint32_t timeout_us);
+WB_API int wb_linear_gather_barrier(wb_context *ctx, wb_handle weight, uint64_t a_offset, uint64_t c_offset,
+                                    uint64_t tmp_offset, wb_handle bias, int64_t M, int act_dtype, int out_dtype,
+                                    int64_t n_total, int64_t col_begin, void *const *peer_bases, int n_peers,
+                                    uint64_t flags_offset, int rank, uint32_t timeout_us);
+/* The same exchange as an NCCL all-gather over NVLink (no counterpart in the reference). NCCL is loaded with dlopen
+ * when one of these is first called (WEBLLM_B200_NCCL_LIB names the file, else libnccl.so.2), so the library links
+ * only the CUDA runtime. wb_comm_unique_id fills WB_COMM_ID_BYTES bytes on one rank; the host hands them to the
+ * others (any channel) and every rank calls wb_comm_init(rank, nranks, id). Creation is polled on the host for at most
+ * timeout_ms (<= 0: 30 s): if a rank never joins, the others get WB_ERR_TIMEOUT and the half-built communicator is
+ * aborted. wb_linear_colshard: `weight` holds this rank's N columns (wb_gptq_register_cols, equal widths on all
+ * ranks); the local [M, N] product goes to scratch_offset, the all-gather of the pieces to c_offset as rank-major
+ * [nranks, M, N] (for M == 1 that IS the row [1, nranks * N]); with row_major != 0 and M > 1 the pieces are gathered
+ * into the scratch and a kernel of this library rearranges them to row-major [M, nranks * N] at c_offset. Scratch
+ * size: align256(M * N * elem) bytes, plus nranks * M * N * elem when rearranging. Stream-ordered like wb_linear;
+ * cannot be recorded into a command batch. */
+#define WB_COMM_ID_BYTES 128
+WB_API int wb_comm_unique_id(void *id_out);
+WB_API int wb_comm_init(wb_context *ctx, int rank, int nranks, const void *unique_id, int timeout_ms);
+WB_API int wb_comm_destroy(wb_context *ctx);
+WB_API int wb_linear_colshard(wb_context *ctx, wb_handle weight, uint64_t a_offset, uint64_t c_offset,
+                              uint64_t scratch_offset, wb_handle bias, int64_t M, int act_dtype, int out_dtype,
+                              int row_major);
 /* Diagnostic with no counterpart in the reference: one kernel of `ctas` x 256 threads reads `bytes` of a slab once
  * (128-bit streaming loads) and computes nothing. It measures the rate that any single pass over that many bytes
  * reaches when launched like the int4 GEMV, the figure that kernel's bandwidth is compared with. */
 WB_API int wb_read_sweep(wb_context *ctx, int arena, uint64_t offset, uint64_t bytes, int ctas);
 /* planGemvSplit (src/model/qwen.ts:61-74) generalised: which kernel, how many K slices, what grid. */
 WB_API int wb_plan_query(wb_context *ctx, wb_handle weight, int64_t M, int act_dtype, int exact, wb_plan *out);
-/* Forces a kernel (wb_kernel_kind) and/or split for the next wb_linear calls; 0 = planner's choice.
+/* Forces a kernel (wb_kernel_kind) and/or split for the next wb_linear calls; 0 = planner's choice. A forced kind
+ * means that kernel and no other (WB_KERNEL_GEMV_MMA never falls through to GEMV_STREAM and vice versa; a shape or split
+ * the kernel does not take is refused with WB_ERR_UNSUPPORTED).
  * Used by tests to cover every path at every shape, as the reference's tests drive the split kernel with
  * explicit S (src/tests/kernels.ts:1378-1400). */
 WB_API int wb_plan_override(wb_context *ctx, int kernel, int split_k);
@@ -236,11 +277,6 @@ WB_API int wb_qwen_decode_step(wb_qwen *model, uint32_t token, uint64_t *logits_
  * in a CUDA graph on first use and replayed; out_tokens receives the n_steps sampled tokens. Replaces the
  * per-token logits readback of generateQwen (src/infer/qwen-generate.ts:66-74). */
 WB_API int wb_qwen_decode_greedy(wb_qwen *model, uint32_t first_token, int64_t n_steps, uint32_t *out_tokens);
-/* How wb_qwen_decode_greedy runs a step: 0 = automatic (currently 1), 1 = one kernel per operation replayed as a
- * CUDA graph (the CommandBatch form of the reference, src/gpu/pipeline.ts:55-117), 2 = one persistent cooperative
- * kernel per step with grid-wide barriers between its phases (needs the fused GPTQ projections). Both give the
- * same tokens. */
-WB_API int wb_qwen_set_decode_mode(wb_qwen *model, int mode);
 /* Logits of the last step run by wb_qwen_decode_greedy, [V] f32, copied to the host. */
 WB_API int wb_qwen_last_logits(wb_qwen *model, float *out);
 
@@ -258,6 +294,11 @@ WB_API int wb_qwen_last_logits(wb_qwen *model, float *out);
  *      Limits: M <= 32, K % 8 == 0, N % 4 == 0, group % 128 == 0, N <= 131072 * (1, 2 or 4 for M <= 2, 4, 32),
  *      and split_k * M * N * 4 bytes <= 4 MiB; anything beyond is refused with WB_ERR_UNSUPPORTED and a
  *      message, never truncated.
+ *      Alignment of the caller's pointers (a view into the middle of a larger buffer may break it): qweight, x and
+ *      y 16 bytes, scales_f16 8 bytes, qzeros and bias 4 bytes; anything else is refused with WB_ERR_BAD_ARG
+ *      before any launch. The kernel is ordered behind everything enqueued earlier on the stream (it is launched
+ *      without programmatic stream serialization), so a kernel of the caller that writes the tensors may
+ *      directly precede the call.
  *      The first call on a device looks up the array's device address (cudaGetSymbolAddress): make that
  *      call before any stream capture. All calls on a device share the array, which keeps the previous
  *      call's contents; each call re-zeroes the counters it uses on its stream, so calls that run one after

@@ -123,7 +123,10 @@ def test_dense_f16_gemm(gpu, oracle, M):
 
 
 def test_7b_shapes(gpu, oracle):
-    for name, K, N, M in (("q7", 3584, 3584, 4096), ("kv7", 3584, 512, 4096), ("down7", 18944, 3584, 512)):
+    """7B-class projections at prefill size, sampled rows against the oracle: q and k/v, the gate / up shape
+    3584 -> 18944 at M = 4096 (the 256 x 256 tile) and down 18944 -> 3584 at M = 512 and M = 4096 (the long-K GEMM)."""
+    for name, K, N, M in (("q7", 3584, 3584, 4096), ("kv7", 3584, 512, 4096), ("down7", 18944, 3584, 512),
+                          ("gate7", 3584, 18944, 4096), ("down7", 18944, 3584, 4096)):
         h, W16 = _weight(gpu, oracle, name, K, N, zeros="7or8")
         x16 = np.random.default_rng(K).standard_normal((M, K)).astype(np.float16)
         got = run_linear(gpu, h, x16, M, N, None, act="f16")

@@ -208,18 +208,19 @@ def test_hint_next_prefetches_without_changing_results(gpu, oracle):
 @pytest.mark.parametrize("M", [1, 2, 3, 4])
 @pytest.mark.parametrize("zeros", ["any", "none"])
 def test_streaming_kernel_matches_oracle(gpu, oracle, K, N, S, M, zeros):
-    """The streaming variant of the int4 GEMV (M <= 4, >= 20 whole chunks per K slice, N % 32 == 0): both
-    activation types against the oracle, bias once, split-K through the workspace, and bitwise agreement between
-    repeated launches. The same shapes with WEBLLM_B200_NO_STREAM=1 run the general kernel."""
+    """The streaming variant of the int4 GEMV (M <= 4, >= 20 whole chunks per K slice, N % 32 == 0), forced so that
+    nothing else can take the call: both activation types against the oracle, bias once, split-K through the
+    workspace, and bitwise agreement between repeated launches. The general kernel on the same shapes agrees."""
     t = synthetic.random_gptq(K, N, 128, seed=K + N + M, zeros=zeros)
     W = oracle_weight(oracle, t)
     h = register(gpu, f"stream_{K}x{N}_{M}_{zeros}", t)
     bias = np.random.default_rng(N + M).standard_normal(N).astype(np.float32)
     hb = gpu.f32_upload(f"streamb_{K}x{N}_{M}_{zeros}", bias)
     x = _x(M, K, 7 * M + K)
-    gpu.plan_override(_lib.WB_KERNEL_GEMV_MMA, S)
+    gpu.plan_override(_lib.WB_KERNEL_GEMV_STREAM, S)
     try:
-        assert gpu.plan(h, M, "f32")["split_k"] == S
+        p = gpu.plan(h, M, "f32")
+        assert p["kernel_name"] == "gemv_stream" and p["split_k"] == S and p["block"] == 256
         ref = oracle.gemm_nt_ref(x, W, M, N, K, bias, threads=oracle.max_threads())
         got = run_linear(gpu, h, x, M, N, hb)
         assert_close(oracle, got, ref, F32_RTOL, f"stream K={K} N={N} M={M} S={S} f32")
@@ -228,5 +229,53 @@ def test_streaming_kernel_matches_oracle(gpu, oracle, K, N, S, M, zeros):
         x16 = x.astype(np.float16)
         ref16 = oracle.gemm_nt_ref(x16.astype(np.float32), W, M, N, K, bias, threads=oracle.max_threads())
         assert_close(oracle, run_linear(gpu, h, x16, M, N, hb, act="f16"), ref16, F16_RTOL, f"stream K={K} N={N} M={M} S={S} f16")
+        # a forced kind means that kernel and no other: the general kernel on the same shape and split
+        gpu.plan_override(_lib.WB_KERNEL_GEMV_MMA, S)
+        assert gpu.plan(h, M, "f32")["kernel_name"] == "gemv_mma"
+        assert_close(oracle, run_linear(gpu, h, x, M, N, hb), ref, F32_RTOL, f"general kernel K={K} N={N} M={M} S={S}")
+    finally:
+        gpu.plan_override(0, 0)
+
+
+@pytest.mark.parametrize("K,N", [(3584, 18944), (3584, 37888)])
+def test_7b_gate_up_decode_takes_the_streaming_kernel(gpu, oracle, K, N):
+    """The 7B-class gate / up projection (3584 -> 18944) and gate|up as one matrix (3584 -> 37888), the shapes behind
+    the GEMV bandwidth figures: the planner's own choice is the streaming kernel; M = 1 and M = 4, f32 activations
+    (1e-5) and fp16 activations (1e-3), against the oracle on every output."""
+    t = synthetic.random_gptq(K, N, 128, seed=N, zeros="any")
+    W = oracle_weight(oracle, t)
+    h = register(gpu, f"gate7b_{N}", t)
+    try:
+        for M in ((1, 4) if N == 18944 else (1,)):
+            for act in ("f32", "f16"):
+                p = gpu.plan(h, M, act)
+                assert p["kernel_name"] == "gemv_stream", p
+                x = _x(M, K, 11 * M + N, f16=(act == "f16"))
+                ref = oracle.gemm_nt_ref(x.astype(np.float32), W, M, N, K, threads=oracle.max_threads())
+                got = run_linear(gpu, h, x, M, N, None, act=act)
+                assert_close(oracle, got, ref, F32_RTOL if act == "f32" else F16_RTOL, f"7B gate N={N} M={M} {act}")
+    finally:
+        gpu.weight_pop()  # 35 / 70 MB: hand the space back to the module's arena
+
+
+def test_streaming_kernel_refuses_a_last_slice_without_a_chunk_per_warp(gpu, oracle):
+    """K = 34176 is 267 chunks of 128: 14 slices of 20 leave a last slice of 7 chunks, fewer than the kernel's 8 warps.
+    The streaming kernel refuses that split (the general kernel takes it); 13 slices (21 + ... + 15) run and match."""
+    K, N = 34176, 64
+    t = synthetic.random_gptq(K, N, 128, seed=77, zeros="any")
+    W = oracle_weight(oracle, t)
+    h = register(gpu, "stream_longk", t)
+    x = _x(1, K, 3)
+    ref = oracle.gemm_nt_ref(x, W, 1, N, K, threads=oracle.max_threads())
+    try:
+        gpu.plan_override(_lib.WB_KERNEL_GEMV_STREAM, 14)
+        with pytest.raises(WebllmError) as e:
+            gpu.plan(h, 1, "f32")
+        assert e.value.status == _lib.WB_ERR_UNSUPPORTED
+        gpu.plan_override(_lib.WB_KERNEL_GEMV_MMA, 14)
+        assert_close(oracle, run_linear(gpu, h, x, 1, N), ref, F32_RTOL, "general kernel, 14 slices")
+        gpu.plan_override(_lib.WB_KERNEL_GEMV_STREAM, 13)
+        assert gpu.plan(h, 1, "f32")["kernel_name"] == "gemv_stream"
+        assert_close(oracle, run_linear(gpu, h, x, 1, N), ref, F32_RTOL, "streaming kernel, 13 slices")
     finally:
         gpu.plan_override(0, 0)

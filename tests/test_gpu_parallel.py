@@ -117,52 +117,39 @@ def _nccl_rank(rank, world, port, tmp):
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device(f"cuda:{rank}"))
-    host = parallel.TorchSlabGpu(rank, weight_bytes=256 << 20, act_bytes=256 << 20)
+    host = parallel.ShardGroup(rank, weight_bytes=256 << 20, act_bytes=256 << 20)
+    gpu = host.gpu
     try:
         K, N = 3584, 3584
         t = synthetic.random_gptq(K, N, 128, seed=5, zeros="any")
         bias = np.random.default_rng(2).standard_normal(N).astype(np.float32)
         lin = parallel.ColumnShardedLinear(host, "q7", t, bias)
         W = oracle.dequantize_gptq_int4(t.qweight, t.qzeros, oracle.f16_bits_to_f32(t.scales.view(np.uint16)), K, N, 128)
-        for M in (1, 48):
-            host.gpu.arena.reset()
-            A = host.gpu.arena.alloc(M * K, [M, K], "f16")
-            Cl = host.gpu.arena.alloc(M * lin.shard.count, [M, lin.shard.count], "f32")
+        for M in (1, 48, 300):
             x = np.random.default_rng(10 + M).standard_normal((M, K)).astype(np.float16)  # same on every rank
-            host.gpu.write(A, x)
-            y = lin.forward(A, Cl, M)
-            torch.cuda.synchronize()
-            got = y.cpu().numpy()
             Wref = oracle.round_f16(W).reshape(N, K) if M > 16 else W
             ref = oracle.gemm_nt_ref(x.astype(np.float32), Wref, M, N, K, bias, threads=4)
             rms = float(np.sqrt(np.mean(ref.astype(np.float64) ** 2)))
+            gpu.arena.reset()
+            A = gpu.arena.alloc(M * K, [M, K], "f16")
+            Cf = gpu.arena.alloc(M * N, [M, N], "f32")
+            scratch = gpu.arena.alloc(lin.scratch_elems(M), dtype="f32")
+            tmpc = gpu.arena.alloc(M * lin.shard.count, [M, lin.shard.count], "f32")
+            gpu.write(A, x)
+            # (1) local product + NCCL all-gather enqueued by the library (wb_linear_colshard), row-major result
+            lin.forward(A, Cf, scratch, M)
+            got = gpu.read(Cf).reshape(M, N)
             r = oracle.check_tolerance(got, ref, 1e-3 * rms, 1e-3)
-            assert got.shape == (M, N) and r.ok, (rank, M, r)
-        # the same products with the all-gather done by the kernels' own stores into the peers' slabs
-        peer = parallel.PeerSlabGpu(rank, weight_bytes=256 << 20, act_bytes=256 << 20)
-        try:
-            plin = parallel.ColumnShardedLinear(peer, "q7p", t, bias)
-            for M in (1, 48, 300):
-                peer.gpu.arena.reset()
-                A = peer.gpu.arena.alloc(M * K, [M, K], "f16")
-                Cf = peer.gpu.arena.alloc(M * N, [M, N], "f32")
-                tmpc = peer.gpu.arena.alloc(M * plin.shard.count, [M, plin.shard.count], "f32")
-                x = np.random.default_rng(10 + M).standard_normal((M, K)).astype(np.float16)
-                peer.gpu.write(A, x)
-                peer.gpu.write(Cf, np.zeros(M * N, np.float32))
-                torch.cuda.synchronize()
-                dist.barrier()  # every rank's tensor is cleared before any peer stores into it
-                plin.forward_fused(A, Cf, tmpc, M)
-                torch.cuda.synchronize()
-                got = peer.gpu.read(Cf).reshape(M, N)
-                Wref = oracle.round_f16(W).reshape(N, K) if M > 16 else W
-                ref = oracle.gemm_nt_ref(x.astype(np.float32), Wref, M, N, K, bias, threads=4)
-                rms = float(np.sqrt(np.mean(ref.astype(np.float64) ** 2)))
-                r = oracle.check_tolerance(got, ref, 1e-3 * rms, 1e-3)
-                assert r.ok, ("fused", rank, M, r)
-                dist.barrier()  # nobody clears its tensor for the next M while a peer is still storing
-        finally:
-            peer.close()
+            assert r.ok, ("colshard", rank, M, r)
+            # (2) the all-gather as the kernels' own stores into the peers' slabs + the library's barrier kernel
+            gpu.write(Cf, np.zeros(M * N, np.float32))
+            gpu.synchronize()
+            dist.barrier()  # every rank's tensor is cleared before any peer stores into it
+            lin.forward_fused(A, Cf, tmpc, M)
+            got = gpu.read(Cf).reshape(M, N)
+            r = oracle.check_tolerance(got, ref, 1e-3 * rms, 1e-3)
+            assert r.ok, ("fused", rank, M, r)
+            dist.barrier()  # nobody clears its tensor for the next M while a peer is still storing
         Path(tmp, f"ok{rank}").write_text("ok")
     finally:
         host.close()
@@ -180,3 +167,65 @@ def test_column_sharded_linear_over_nccl(tmp_path, built_lib, oracle):
     import torch.multiprocessing as mp
     mp.spawn(_nccl_rank, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
     assert all((tmp_path / f"ok{r}").exists() for r in range(world))
+
+
+def test_peer_barrier_gives_up_instead_of_hanging(gpu):
+    """The wait of the library's barrier kernel is bounded: with a flag word that nobody writes (this GPU stands in for
+    its own peer, so only slot 0 is ever stored) it records its code after the time limit, the kernel returns, the next
+    synchronize reports WB_ERR_TIMEOUT, and the context keeps working. With both slots served it passes."""
+    from webllm_b200 import _lib
+    gpu.arena.reset()
+    flags = gpu.arena.alloc(_lib.WB_PEER_FLAG_BYTES // 4)
+    gpu.peer_barrier_init(flags)
+    own = gpu.arena_base()
+    gpu.peer_barrier(flags, 0, [own], timeout_us=2000)  # waits for rank 1, which does not exist
+    with pytest.raises(WebllmError) as e:
+        gpu.synchronize()
+    assert e.value.status == _lib.WB_ERR_TIMEOUT
+    gpu.synchronize()  # the status word was consumed; the context is usable
+    # both "ranks" played by this GPU in turn: rank 1 stores its epoch first, then rank 0 finds it and passes
+    gpu.peer_barrier_init(flags)
+    words = np.zeros(_lib.WB_PEER_FLAG_BYTES // 4, np.uint32)
+    words[1] = 1  # what rank 1's barrier number 1 would have stored into this GPU's flags
+    gpu.write_bytes(flags.offset, words)
+    gpu.peer_barrier(flags, 0, [own], timeout_us=200000)
+    gpu.synchronize()
+    with pytest.raises(WebllmError, match="rank"):
+        gpu.peer_barrier(flags, 3, [own])
+
+
+@pytest.mark.parametrize("M", [1, 48])
+def test_colshard_entry_point_on_a_one_rank_communicator(gpu, oracle, M):
+    """wb_comm_init / wb_linear_colshard through the C ABI with a communicator of one rank (NCCL loaded with dlopen,
+    the all-gather of one piece is a copy): the call's bookkeeping, scratch layout and result against the oracle."""
+    from webllm_b200 import _lib
+    K, N = 3584, 512
+    t = synthetic.random_gptq(K, N, 128, seed=31, zeros="any")
+    try:
+        h = gpu.weight("cs1")
+    except WebllmError:
+        h = gpu.gptq_register("cs1", t.qweight, t.qzeros, t.scales, K, N, 128)
+    with pytest.raises(WebllmError, match="wb_comm_init first"):
+        gpu.arena.reset()
+        A = gpu.arena.alloc(M * K, [M, K], "f16")
+        Cf = gpu.arena.alloc(M * N, [M, N], "f32")
+        gpu.linear_colshard(h, A, Cf, Cf, None, M)
+    gpu.comm_init(0, 1, gpu.comm_unique_id(), 20000)
+    try:
+        with pytest.raises(WebllmError) as e:
+            gpu.comm_init(0, 1, gpu.comm_unique_id())
+        assert e.value.status == _lib.WB_ERR_EXISTS
+        W = oracle_weight(oracle, t)
+        x = np.random.default_rng(M).standard_normal((M, K)).astype(np.float16)
+        gpu.arena.reset()
+        A = gpu.arena.alloc(M * K, [M, K], "f16")
+        Cf = gpu.arena.alloc(M * N, [M, N], "f32")
+        scratch = gpu.arena.alloc(M * N + 64)
+        gpu.write(A, x)
+        gpu.linear_colshard(h, A, Cf, scratch, None, M)
+        got = gpu.read(Cf).reshape(M, N)
+        Wref = oracle.round_f16(W).reshape(N, K) if M > 16 else W
+        ref = oracle.gemm_nt_ref(x.astype(np.float32), Wref, M, N, K, threads=oracle.max_threads())
+        assert_close(oracle, got, ref, 1e-3, f"colshard one rank M={M}")
+    finally:
+        gpu.comm_destroy()

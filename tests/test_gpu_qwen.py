@@ -148,8 +148,9 @@ def test_gptq_model_prefill_decode_and_greedy(built_lib, oracle, fuse, kv):
             lr = ref.decode_step(t)
             t = oracle.sample_greedy(lr)
             want.append(t)
-        got = model.decode_greedy(tok, steps)
-        assert got.tolist() == want
+        got = model.decode_greedy(tok, steps - 5).tolist()
+        got += model.decode_greedy(got[-1], 5).tolist()  # a second call continues from the device-resident state
+        assert got == want
         assert model.cache_len == 40 + steps
         assert oracle.check_tolerance(model.last_logits(), lr, 5e-4 * rms, 5e-4).ok
         # the reference's host loop (generateQwen) gives the same ids as the device loop
@@ -209,27 +210,3 @@ def test_full_size_decode_token_identical(built_lib, oracle):
         assert first_diff is None, (f"diverged at step {first_diff}: top-2 margin there {margins[first_diff]:.3e} "
                                     f"(logit rms {rms:.3e})")
         model.close()
-
-
-@pytest.mark.parametrize("kv", ["f16", "f32"])
-def test_single_kernel_decode_matches_graph_of_kernels(built_lib, oracle, kv):
-    """The persistent one-kernel-per-step decode path against the one-kernel-per-operation path on the same
-    model and cache: same greedy tokens, logits within fp32 rounding, cache length advanced identically."""
-    G = synthetic.random_qwen_gptq(SMALL, seed=5, std=0.05)
-    prompt = np.random.default_rng(2).integers(0, SMALL.vocab_size, 33).astype(np.uint32)
-    steps = 20
-    out = {}
-    for mode in ("graph", "single"):
-        with Gpu(0, weight_bytes=64 << 20, act_bytes=64 << 20) as gpu:
-            model = QwenGpt(gpu, SMALL, max_t=64, kv_dtype=kv)
-            model.upload_gptq_model(G, fuse=True)
-            model.set_decode_mode(mode)
-            row = model.read_tensor(model.prefill(prompt, last_only=True))
-            toks = model.decode_greedy(int(row.argmax()), steps)
-            more = model.decode_greedy(int(toks[-1]), 3)  # a second call continues from the device-resident state
-            out[mode] = (toks.tolist() + more.tolist(), model.last_logits(), model.cache_len)
-            model.close()
-    assert out["single"][0] == out["graph"][0]
-    assert out["single"][2] == out["graph"][2] == 33 + steps + 3
-    rms = float(np.sqrt(np.mean(out["graph"][1].astype(np.float64) ** 2)))
-    assert oracle.check_tolerance(out["single"][1], out["graph"][1], 1e-4 * rms, 1e-4).ok

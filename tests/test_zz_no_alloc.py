@@ -8,15 +8,16 @@ other test. The test needs nothing from the others and also passes alone in a fr
 
 It stages the tensors in device memory owned by the test (torch, standing in for the host application),
 calls the entry point through the C ABI twice in a row, and compares each result with the regular
-context-based entry point (wb_linear) on the same inputs, within the tolerance the other linear tests use
-(the two run the same kernel with the same split, so they normally agree bit for bit).
+context-based entry point (wb_linear) on the same inputs and with the CPU oracle, within the tolerance the
+other linear tests use (the two GPU paths run the same kernel with the same split, so they normally agree bit
+for bit). The second call must leave the amount of free device memory unchanged.
 """
 import ctypes as C
 
 import numpy as np
 import pytest
 
-from helpers import assert_close, register, run_linear
+from helpers import assert_close, oracle_weight, register, run_linear
 from webllm_b200 import _lib, synthetic
 
 pytestmark = pytest.mark.gpu
@@ -37,6 +38,9 @@ def test_static_scratch_gemv_matches_context_path(gpu, oracle, K, N, M, split, a
     np_act = np.float32 if act == "f32" else np.float16
     xs = [np.random.default_rng(s).standard_normal((M, K)).astype(np_act) for s in (1, 2)]
 
+    W = oracle_weight(oracle, t)
+    oracle_ref = [oracle.gemm_nt_ref(x.astype(np.float32), W, M, N, K, bias, threads=oracle.max_threads()) for x in xs]
+
     # regular path: context, registered weight, workspace scratch, same split
     h = register(gpu, f"static_ref_{K}x{N}x{M}", t)
     hb = gpu.f32_upload(f"static_refb_{K}x{N}x{M}", bias)
@@ -51,17 +55,22 @@ def test_static_scratch_gemv_matches_context_path(gpu, oracle, K, N, M, split, a
     d_qw, d_qz, d_sc, d_b = _dev(torch, t.qweight), _dev(torch, t.qzeros), _dev(torch, t.scales.view(np.int16)), _dev(torch, bias)
     d_y = torch.empty((M, N), dtype=torch.float32, device="cuda")
     torch.cuda.synchronize()
-    for x, ref in zip(xs, want):  # two calls in a row share (and must each re-initialise) the scratch
+    free_after_first = None
+    for call, (x, ref, oref) in enumerate(zip(xs, want, oracle_ref)):  # two calls in a row share (and must each re-initialise) the scratch
         d_x = _dev(torch, x.view(np.int16) if act == "f16" else x)
         d_y.fill_(float("nan"))
         torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
         rc = lib.wb_gptq_gemv_static(d_qw.data_ptr(), d_qz.data_ptr(), d_sc.data_ptr(), d_x.data_ptr(), d_y.data_ptr(),
                                      d_b.data_ptr(), K, N, 128, M, _lib.WB_F32 if act == "f32" else _lib.WB_F16,
                                      _lib.WB_F32, used_split, None)
         assert rc == 0, lib.wb_last_error().decode()
         torch.cuda.synchronize()
+        if call == 1:  # the first call on a device may set up the module; from then on nothing is allocated
+            assert torch.cuda.mem_get_info()[0] == free_before
         got = d_y.cpu().numpy()
         assert_close(oracle, got, ref, F32_RTOL, f"static K={K} N={N} M={M} split={used_split}")
+        assert_close(oracle, got, oref, F32_RTOL if act == "f32" else 1e-3, f"static vs oracle K={K} N={N} M={M}")
 
 
 def test_static_scratch_limits_are_refused_not_truncated(built_lib):
@@ -76,3 +85,12 @@ def test_static_scratch_limits_are_refused_not_truncated(built_lib):
     assert rc == _lib.WB_ERR_UNSUPPORTED and b"M <= 32" in lib.wb_last_error()
     rc = lib.wb_gptq_gemv_static(None, None, p, p, p, None, 896, 4864, 128, 1, _lib.WB_F16, _lib.WB_F32, 0, None)
     assert rc == _lib.WB_ERR_BAD_ARG
+    # pointers into the middle of a buffer that break the kernel's vector accesses are refused on the host:
+    # (argument index, byte offset that breaks its rule) for qweight, qzeros, scales, x, y, bias
+    for arg, off, word in ((0, 4, b"16-byte"), (3, 8, b"16-byte"), (4, 4, b"16-byte"), (2, 4, b"8-byte"), (1, 2, b"4-byte"),
+                           (5, 2, b"4-byte")):
+        ptrs = [p, p, p, p, p, p]
+        ptrs[arg] = p + off
+        rc = lib.wb_gptq_gemv_static(ptrs[0], ptrs[1], ptrs[2], ptrs[3], ptrs[4], ptrs[5], 896, 4864, 128, 1, _lib.WB_F16,
+                                     _lib.WB_F32, 0, None)
+        assert rc == _lib.WB_ERR_BAD_ARG and word in lib.wb_last_error(), (arg, off, lib.wb_last_error())

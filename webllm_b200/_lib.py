@@ -17,8 +17,10 @@ WB_ERR_TIMEOUT, WB_ERR_NOT_FOUND, WB_ERR_EXISTS, WB_ERR_UNSUPPORTED = -5, -6, -7
 WB_F32, WB_F16 = 0, 1
 WB_ARENA_WEIGHTS, WB_ARENA_ACT = 0, 1
 WB_IPC_HANDLE_BYTES = 64
-WB_KERNEL_GEMV_MMA, WB_KERNEL_GEMM_TC, WB_KERNEL_GENERIC, WB_KERNEL_DENSE_GEMV = 1, 2, 3, 4
-KERNEL_NAMES = {1: "gemv_mma", 2: "gemm_tc", 3: "generic", 4: "dense_gemv"}
+WB_PEER_FLAG_BYTES = 256
+WB_COMM_ID_BYTES = 128
+WB_KERNEL_GEMV_MMA, WB_KERNEL_GEMM_TC, WB_KERNEL_GENERIC, WB_KERNEL_DENSE_GEMV, WB_KERNEL_GEMV_STREAM = 1, 2, 3, 4, 5
+KERNEL_NAMES = {1: "gemv_mma", 2: "gemm_tc", 3: "generic", 4: "dense_gemv", 5: "gemv_stream"}
 
 
 class WebllmError(RuntimeError):
@@ -87,6 +89,14 @@ SIGNATURES = {
     "wb_arena_ipc_export": [_vp, _i32, _vp],
     "wb_peer_open": [_vp, _vp, C.POINTER(_vp)],
     "wb_peer_close": [_vp, _vp],
+    "wb_peer_barrier_init": [_vp, _u64],
+    "wb_peer_barrier": [_vp, _u64, _i32, C.POINTER(_vp), _i32, C.c_uint32],
+    "wb_linear_gather_barrier": [_vp, C.c_int32, _u64, _u64, _u64, C.c_int32, _i64, _i32, _i32, _i64, _i64, C.POINTER(_vp), _i32,
+                                 _u64, _i32, C.c_uint32],
+    "wb_comm_unique_id": [_vp],
+    "wb_comm_init": [_vp, _i32, _i32, _vp, _i32],
+    "wb_comm_destroy": [_vp],
+    "wb_linear_colshard": [_vp, C.c_int32, _u64, _u64, _u64, C.c_int32, _i64, _i32, _i32, _i32],
     "wb_read_sweep": [_vp, _i32, _u64, _u64, _i32],
     "wb_plan_query": [_vp, C.c_int32, _i64, _i32, _i32, C.POINTER(Plan)],
     "wb_plan_override": [_vp, _i32, _i32],
@@ -104,7 +114,6 @@ SIGNATURES = {
     "wb_qwen_prefill": [_vp, _vp, _i64, _i32, C.POINTER(_u64)],
     "wb_qwen_decode_step": [_vp, C.c_uint32, C.POINTER(_u64)],
     "wb_qwen_decode_greedy": [_vp, C.c_uint32, _i64, _vp],
-    "wb_qwen_set_decode_mode": [_vp, _i32],
     "wb_qwen_last_logits": [_vp, _vp],
     "wb_gptq_gemv_static": [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i32, _i32, _i32, _vp],
 }

@@ -32,6 +32,15 @@ int fail(int code, const char *fmt, ...);
         if (_s != WB_OK) return _s; \
     } while (0)
 
+// Transfers, registrations and anything else that blocks on the stream are refused while a command batch is being
+// recorded (the stream is capturing: they would fail inside CUDA and invalidate the recording).
+#define WB_NOT_RECORDING(ctx, what)                                                                              \
+    do {                                                                                                         \
+        if ((ctx)->capturing)                                                                                    \
+            return wb::fail(WB_ERR_BAD_ARG, "%s is not allowed while a command batch is being recorded "         \
+                                            "(between wb_batch_begin and wb_batch_end)", what);                 \
+    } while (0)
+
 // ---------------------------------------------------------------- weights
 enum class WeightKind : int { Gptq = 1, DenseF16 = 2, F32 = 3 };
 
@@ -48,6 +57,7 @@ struct Weight {
     uint64_t off_scales = 0;  // fp16 scales
     bool has_zeros = false;
     uint64_t bytes = 0;
+    uint64_t arena_top = 0;   // `used` of the weight arena right after this registration (what wb_weight_pop checks)
 };
 
 struct ArenaState {
@@ -97,6 +107,9 @@ struct wb_context {
     wb::OutPlace place;              // set for the duration of one wb_linear_gather call (n_dst > 0)
     bool capturing = false;          // a command batch is being recorded (batch.cu)
     uint64_t launches_at_capture = 0;
+    void *nccl_comm = nullptr;       // ncclComm_t of the column-sharded group (comm.cu); nullptr until wb_comm_init
+    int comm_rank = 0, comm_size = 1;
+    unsigned peer_epoch = 0;         // barriers issued by wb_peer_barrier since wb_peer_barrier_init
 };
 
 namespace wb {
@@ -110,6 +123,10 @@ int launch_dequant(wb_context *ctx, const Weight &w, void *out, bool f16);
 int launch_f32_to_f16_ref(wb_context *ctx, const float *in, __half *out, int64_t n);
 int plan_linear(wb_context *ctx, const Weight &w, int64_t M, int act_dtype, int exact, wb_plan *plan);
 int launch_scatter_cols(wb_context *ctx, const void *src, int64_t M, int64_t N, bool f16);  // uses ctx->place
+// comm.cu: the same copy with the peer barrier in the same launch (one CTA), and the release of the communicator
+int launch_scatter_barrier(wb_context *ctx, const void *src, int64_t M, int64_t N, bool f16, uint64_t flags_offset, int rank,
+                           void *const *peer_bases, int n_peers, uint32_t timeout_us);
+void comm_release(wb_context *ctx);
 // Work a decode-size int4 projection can do on its input while staging it (see GemvPrologue in gemv_core.cuh):
 // kind 1 = rmsnorm(x + delta) * norm_w with x + delta stored to x_out, kind 2 = silu(x) * up with row pitch ld.
 struct LinearFusion {
@@ -182,15 +199,18 @@ inline bool pdl_enabled()
 }
 
 // `cluster_y` > 1 launches thread-block clusters of (1, cluster_y, 1) CTAs (grid.y must be a multiple of it).
+// `pdl` = false launches fully serialised behind the stream's earlier work: for entry points that read caller-owned
+// buffers which the caller's previous kernel on that stream may still be writing (a kernel launched with the
+// attribute requests its weights BEFORE it waits for its predecessor).
 template <typename... P, typename... A>
-inline cudaError_t launch_pdl_cluster(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
-                                      unsigned cluster_y, A &&...args)
+inline cudaError_t launch_cluster_ex(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                     unsigned cluster_y, bool pdl, A &&...args)
 {
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = grid, cfg.blockDim = block, cfg.dynamicSmemBytes = smem, cfg.stream = stream;
     cudaLaunchAttribute attr[2];
     unsigned n = 0;
-    if (pdl_enabled()) {
+    if (pdl && pdl_enabled()) {
         attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[n].val.programmaticStreamSerializationAllowed = 1;
         n++;
@@ -203,6 +223,13 @@ inline cudaError_t launch_pdl_cluster(void (*kernel)(P...), dim3 grid, dim3 bloc
     cfg.attrs = attr;
     cfg.numAttrs = n;
     return cudaLaunchKernelEx(&cfg, kernel, P(args)...);
+}
+
+template <typename... P, typename... A>
+inline cudaError_t launch_pdl_cluster(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                      unsigned cluster_y, A &&...args)
+{
+    return launch_cluster_ex(kernel, grid, block, smem, stream, cluster_y, true, static_cast<A &&>(args)...);
 }
 
 template <typename... P, typename... A>

@@ -61,6 +61,7 @@ static int arena_alloc(wb_context *ctx, int arena, uint64_t bytes, uint64_t *off
 static int add_weight(wb_context *ctx, Weight &&w, wb_handle *out)
 {
     int idx = (int)ctx->weights.size();
+    w.arena_top = ctx->arena[WB_ARENA_WEIGHTS].used;
     ctx->by_name[w.name] = idx;
     ctx->weights.push_back(std::move(w));
     if (out) *out = idx;
@@ -148,18 +149,25 @@ int wb_context_create(int device, wb_context **out)
     wb_context *ctx = new wb_context();
     ctx->device = device;
     ctx->sm_count = prop.multiProcessorCount;
-    WB_CUDA(cudaStreamCreateWithFlags(&ctx->own_stream, cudaStreamNonBlocking));
-    ctx->stream = ctx->own_stream;
-    WB_CUDA(cudaMalloc(&ctx->workspace, kWorkspaceBytes));
-    WB_CUDA(cudaMalloc(&ctx->counters, kMaxCounters * sizeof(unsigned)));
-    WB_CUDA(cudaMemset(ctx->counters, 0, kMaxCounters * sizeof(unsigned)));
-    WB_CUDA(cudaHostAlloc(&ctx->status_host, sizeof(int), cudaHostAllocMapped));
-    *ctx->status_host = 0;
-    WB_CUDA(cudaHostGetDevicePointer(&ctx->status_word, ctx->status_host, 0));
-    cudaDriverEntryPointQueryResult qres;
-    WB_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ctx->tmap_encode, cudaEnableDefault, &qres));
-    if (qres != cudaDriverEntryPointSuccess || !ctx->tmap_encode)
-        return fail(WB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    const int rc = [&]() -> int {
+        WB_CUDA(cudaStreamCreateWithFlags(&ctx->own_stream, cudaStreamNonBlocking));
+        ctx->stream = ctx->own_stream;
+        WB_CUDA(cudaMalloc(&ctx->workspace, kWorkspaceBytes));
+        WB_CUDA(cudaMalloc(&ctx->counters, kMaxCounters * sizeof(unsigned)));
+        WB_CUDA(cudaMemset(ctx->counters, 0, kMaxCounters * sizeof(unsigned)));
+        WB_CUDA(cudaHostAlloc(&ctx->status_host, sizeof(int), cudaHostAllocMapped));
+        *ctx->status_host = 0;
+        WB_CUDA(cudaHostGetDevicePointer(&ctx->status_word, ctx->status_host, 0));
+        cudaDriverEntryPointQueryResult qres;
+        WB_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ctx->tmap_encode, cudaEnableDefault, &qres));
+        if (qres != cudaDriverEntryPointSuccess || !ctx->tmap_encode)
+            return fail(WB_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+        return WB_OK;
+    }();
+    if (rc != WB_OK) {
+        wb_context_destroy(ctx);  // frees whatever was built; keeps the error text
+        return rc;
+    }
     *out = ctx;
     return WB_OK;
 }
@@ -168,13 +176,14 @@ int wb_context_destroy(wb_context *ctx)
 {
     if (!ctx) return WB_OK;
     cudaSetDevice(ctx->device);
-    cudaStreamSynchronize(ctx->stream);
+    if (ctx->stream) cudaStreamSynchronize(ctx->stream);
+    comm_release(ctx);
     for (int i = 0; i < 2; i++)
         if (ctx->arena[i].owned && ctx->arena[i].base) cudaFree(ctx->arena[i].base);
-    cudaFree(ctx->workspace);
-    cudaFree(ctx->counters);
-    cudaFreeHost(ctx->status_host);
-    cudaStreamDestroy(ctx->own_stream);
+    if (ctx->workspace) cudaFree(ctx->workspace);
+    if (ctx->counters) cudaFree(ctx->counters);
+    if (ctx->status_host) cudaFreeHost(ctx->status_host);
+    if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
     delete ctx;
     return WB_OK;
 }
@@ -196,6 +205,7 @@ int wb_get_stream(wb_context *ctx, void **cuda_stream)
 int wb_synchronize(wb_context *ctx)
 {
     WB_CTX(ctx);
+    WB_NOT_RECORDING(ctx, "wb_synchronize");
     WB_CUDA(cudaStreamSynchronize(ctx->stream));
     if (*ctx->status_host != 0) {
         int code = *ctx->status_host;
@@ -290,6 +300,7 @@ int wb_arena_base(wb_context *ctx, int arena, void **device_ptr)
 int wb_upload(wb_context *ctx, int arena, uint64_t offset, const void *host, uint64_t bytes)
 {
     WB_CTX(ctx);
+    WB_NOT_RECORDING(ctx, "wb_upload");
     WB_CHECK(check_range(ctx, arena, offset, bytes, "wb_upload"));
     if (bytes == 0) return WB_OK;
     if (!host) return fail(WB_ERR_BAD_ARG, "wb_upload: host pointer is NULL");
@@ -303,6 +314,7 @@ int wb_upload(wb_context *ctx, int arena, uint64_t offset, const void *host, uin
 int wb_download(wb_context *ctx, int arena, uint64_t offset, void *host, uint64_t bytes)
 {
     WB_CTX(ctx);
+    WB_NOT_RECORDING(ctx, "wb_download");
     WB_CHECK(check_range(ctx, arena, offset, bytes, "wb_download"));
     if (bytes == 0) return WB_OK;
     if (!host) return fail(WB_ERR_BAD_ARG, "wb_download: host pointer is NULL");
@@ -317,6 +329,7 @@ static int gptq_register_impl(wb_context *ctx, const char *name, const void *qwe
                               int64_t inF, int64_t outF, int64_t group, int bits, int64_t col_begin,
                               int64_t col_count, wb_handle *out)
 {
+    WB_NOT_RECORDING(ctx, "wb_gptq_register");
     WB_CHECK(check_new_name(ctx, name));
     // The validation list and message texts of dequantizeGptqInt4 (src/weights/quant.ts:46-79).
     if (bits != 4) return fail(WB_ERR_BAD_ARG, "GPTQ: 当前仅支持 4bit，收到 bits=%d", bits);
@@ -358,26 +371,34 @@ static int gptq_register_impl(wb_context *ctx, const char *name, const void *qwe
     const uint64_t qw_bytes = (uint64_t)pack_rows * col_count * 4;
     const uint64_t qz_bytes = (uint64_t)groups * w.zcols * 4;
     const uint64_t sc_bytes = (uint64_t)groups * col_count * 2;
-    WB_CHECK(arena_alloc(ctx, WB_ARENA_WEIGHTS, qw_bytes, &w.off_main));
-    WB_CHECK(arena_alloc(ctx, WB_ARENA_WEIGHTS, sc_bytes, &w.off_scales));
-    if (w.has_zeros) WB_CHECK(arena_alloc(ctx, WB_ARENA_WEIGHTS, qz_bytes, &w.off_zeros));
     w.bytes = align_up(qw_bytes) + align_up(sc_bytes) + (w.has_zeros ? align_up(qz_bytes) : 0);
 
-    char *base = ctx->arena[WB_ARENA_WEIGHTS].base;
     // The device keeps the checkpoint's own packing: qweight rows are already contiguous along the
     // output dimension, which is what both the streaming kernel (128-bit loads of 4 columns) and the
     // TMA box of the tensor-core kernel want. A column slice is a strided 2-D copy.
-    WB_CUDA(cudaMemcpy2DAsync(base + w.off_main, (size_t)col_count * 4, (const char *)qweight + col_begin * 4,
-                              (size_t)outF * 4, (size_t)col_count * 4, (size_t)pack_rows, cudaMemcpyHostToDevice,
-                              ctx->stream));
-    WB_CUDA(cudaMemcpy2DAsync(base + w.off_scales, (size_t)col_count * 2, (const char *)scales + col_begin * 2,
-                              (size_t)outF * 2, (size_t)col_count * 2, (size_t)groups, cudaMemcpyHostToDevice,
-                              ctx->stream));
-    if (w.has_zeros)
-        WB_CUDA(cudaMemcpy2DAsync(base + w.off_zeros, (size_t)w.zcols * 4, (const char *)qzeros + col_begin / 8 * 4,
-                                  (size_t)pack_cols * 4, (size_t)w.zcols * 4, (size_t)groups, cudaMemcpyHostToDevice,
+    const uint64_t mark = ctx->arena[WB_ARENA_WEIGHTS].used;
+    const int rc = [&]() -> int {
+        WB_CHECK(arena_alloc(ctx, WB_ARENA_WEIGHTS, qw_bytes, &w.off_main));
+        WB_CHECK(arena_alloc(ctx, WB_ARENA_WEIGHTS, sc_bytes, &w.off_scales));
+        if (w.has_zeros) WB_CHECK(arena_alloc(ctx, WB_ARENA_WEIGHTS, qz_bytes, &w.off_zeros));
+        char *base = ctx->arena[WB_ARENA_WEIGHTS].base;
+        WB_CUDA(cudaMemcpy2DAsync(base + w.off_main, (size_t)col_count * 4, (const char *)qweight + col_begin * 4,
+                                  (size_t)outF * 4, (size_t)col_count * 4, (size_t)pack_rows, cudaMemcpyHostToDevice,
                                   ctx->stream));
-    WB_CUDA(cudaStreamSynchronize(ctx->stream));
+        WB_CUDA(cudaMemcpy2DAsync(base + w.off_scales, (size_t)col_count * 2, (const char *)scales + col_begin * 2,
+                                  (size_t)outF * 2, (size_t)col_count * 2, (size_t)groups, cudaMemcpyHostToDevice,
+                                  ctx->stream));
+        if (w.has_zeros)
+            WB_CUDA(cudaMemcpy2DAsync(base + w.off_zeros, (size_t)w.zcols * 4, (const char *)qzeros + col_begin / 8 * 4,
+                                      (size_t)pack_cols * 4, (size_t)w.zcols * 4, (size_t)groups, cudaMemcpyHostToDevice,
+                                      ctx->stream));
+        WB_CUDA(cudaStreamSynchronize(ctx->stream));
+        return WB_OK;
+    }();
+    if (rc != WB_OK) {
+        ctx->arena[WB_ARENA_WEIGHTS].used = mark;  // a failed registration leaves the arena as it found it
+        return rc;
+    }
     return add_weight(ctx, std::move(w), out);
 }
 
@@ -428,6 +449,7 @@ static int dense_f16_target(wb_context *ctx, wb_handle h, int64_t elem_offset, i
 int wb_f16_write_chunk(wb_context *ctx, wb_handle h, int64_t elem_offset, const float *data, int64_t n)
 {
     WB_CTX(ctx);
+    WB_NOT_RECORDING(ctx, "wb_f16_write_chunk");
     Weight *w;
     WB_CHECK(dense_f16_target(ctx, h, elem_offset, n, &w));
     if (n == 0) return WB_OK;
@@ -447,6 +469,7 @@ int wb_f16_write_chunk(wb_context *ctx, wb_handle h, int64_t elem_offset, const 
 int wb_f16_write_bits(wb_context *ctx, wb_handle h, int64_t elem_offset, const uint16_t *bits, int64_t n)
 {
     WB_CTX(ctx);
+    WB_NOT_RECORDING(ctx, "wb_f16_write_bits");
     Weight *w;
     WB_CHECK(dense_f16_target(ctx, h, elem_offset, n, &w));
     if (n == 0) return WB_OK;
@@ -460,6 +483,7 @@ int wb_f16_write_bits(wb_context *ctx, wb_handle h, int64_t elem_offset, const u
 int wb_f32_upload(wb_context *ctx, const char *name, const float *data, int64_t n, wb_handle *out)
 {
     WB_CTX(ctx);
+    WB_NOT_RECORDING(ctx, "wb_f32_upload");
     WB_CHECK(check_new_name(ctx, name));
     if (n <= 0 || !data) return fail(WB_ERR_BAD_ARG, "wb_f32_upload: empty data");
     Weight w;
@@ -468,10 +492,13 @@ int wb_f32_upload(wb_context *ctx, const char *name, const float *data, int64_t 
     w.N = n;
     w.K = 1;
     w.bytes = align_up((uint64_t)n * 4);
+    const uint64_t mark = ctx->arena[WB_ARENA_WEIGHTS].used;
     WB_CHECK(arena_alloc(ctx, WB_ARENA_WEIGHTS, (uint64_t)n * 4, &w.off_main));
-    WB_CUDA(cudaMemcpyAsync(ctx->arena[WB_ARENA_WEIGHTS].base + w.off_main, data, (size_t)n * 4,
-                            cudaMemcpyHostToDevice, ctx->stream));
-    WB_CUDA(cudaStreamSynchronize(ctx->stream));
+    cudaError_t e = cudaMemcpyAsync(ctx->arena[WB_ARENA_WEIGHTS].base + w.off_main, data, (size_t)n * 4,
+                                    cudaMemcpyHostToDevice, ctx->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    if (e != cudaSuccess) ctx->arena[WB_ARENA_WEIGHTS].used = mark;
+    WB_CUDA(e);
     return add_weight(ctx, std::move(w), out);
 }
 
@@ -488,10 +515,17 @@ int wb_weight_lookup(wb_context *ctx, const char *name, wb_handle *out)
 int wb_weight_pop(wb_context *ctx)
 {
     WB_CTX(ctx);
+    WB_NOT_RECORDING(ctx, "wb_weight_pop");
     if (ctx->weights.empty()) return fail(WB_ERR_NOT_FOUND, "no weight is registered");
-    WB_CUDA(cudaStreamSynchronize(ctx->stream));
     const Weight &w = ctx->weights.back();
-    // A weight's pieces were the last allocations of the weight arena when it was registered.
+    // A weight's pieces were the last allocations of the weight arena when it was registered. If anything was taken
+    // from the arena since (a model's KV cache and decode buffers, a raw wb_arena_alloc), rewinding would hand that
+    // memory to the next registration while it is still in use.
+    if (ctx->arena[WB_ARENA_WEIGHTS].used != w.arena_top)
+        return fail(WB_ERR_BAD_ARG, "wb_weight_pop: %llu bytes were taken from the weight arena after %s was registered "
+                                    "(a model created on this context?); the weight cannot be dropped",
+                    (unsigned long long)(ctx->arena[WB_ARENA_WEIGHTS].used - w.arena_top), w.name.c_str());
+    WB_CUDA(cudaStreamSynchronize(ctx->stream));
     ctx->arena[WB_ARENA_WEIGHTS].used = w.off_main;
     ctx->by_name.erase(w.name);
     ctx->weights.pop_back();
@@ -502,6 +536,7 @@ int wb_read_weight_f16(wb_context *ctx, wb_handle h, int64_t elem_offset, int64_
 {
     WB_CTX(ctx);
     Weight *w;
+    WB_NOT_RECORDING(ctx, "wb_read_weight_f16");
     WB_CHECK(dense_f16_target(ctx, h, elem_offset, n, &w));
     if (n == 0) return WB_OK;
     WB_CUDA(cudaMemcpyAsync(out_bits, ctx->arena[WB_ARENA_WEIGHTS].base + w->off_main + elem_offset * 2,
@@ -575,9 +610,16 @@ int wb_linear(wb_context *ctx, wb_handle weight, uint64_t a_offset, uint64_t c_o
                          bias_ptr, M, act_dtype, out_dtype, exact);
 }
 
-int wb_linear_gather(wb_context *ctx, wb_handle weight, uint64_t a_offset, uint64_t c_offset, uint64_t tmp_offset,
-                     wb_handle bias, int64_t M, int act_dtype, int out_dtype, int64_t n_total, int64_t col_begin,
-                     void *const *peer_bases, int n_peers)
+// `sync` != nullptr: the call also runs the peer barrier (wb_linear_gather_barrier).
+struct GatherSync {
+    uint64_t flags_offset;
+    int rank;
+    uint32_t timeout_us;
+};
+
+static int linear_gather_impl(wb_context *ctx, wb_handle weight, uint64_t a_offset, uint64_t c_offset, uint64_t tmp_offset,
+                              wb_handle bias, int64_t M, int act_dtype, int out_dtype, int64_t n_total, int64_t col_begin,
+                              void *const *peer_bases, int n_peers, const GatherSync *sync)
 {
     WB_CTX(ctx);
     Weight *w;
@@ -608,27 +650,56 @@ int wb_linear_gather(wb_context *ctx, wb_handle weight, uint64_t a_offset, uint6
         if (!peer_bases[g]) return fail(WB_ERR_BAD_ARG, "wb_linear_gather: peer %d is NULL", g);
         pl.dst[1 + g] = (char *)peer_bases[g] + c_offset;
     }
+    ctx->place = pl;  // the planner prices the stores to the peers
     wb_plan plan;
-    WB_CHECK(plan_linear(ctx, *w, M, act_dtype, 0, &plan));
+    int rc = plan_linear(ctx, *w, M, act_dtype, 0, &plan);
+    ctx->place = OutPlace();
+    WB_CHECK(rc);
     const void *A = arena_ptr(ctx, WB_ARENA_ACT, a_offset);
-    int rc;
+    bool barrier_done = false;
     if (plan.kernel == WB_KERNEL_GEMM_TC) {
         // the tensor-core kernel (and its split-K reduce) stores every output tile straight to all destinations
         ctx->place = pl;
         rc = launch_linear(ctx, *w, A, pl.dst[0], bias_ptr, M, act_dtype, out_dtype, 0);
         ctx->place = OutPlace();
     } else {
-        // decode-size kernels write a dense [M, N] piece to the scratch tensor; one small launch spreads it
+        // decode-size kernels write a dense [M, N] piece to the scratch tensor; one small launch spreads it (and, with
+        // `sync`, signals and waits for the peers in that same launch while the piece is small enough for one CTA)
         WB_CHECK(check_range(ctx, WB_ARENA_ACT, tmp_offset, (uint64_t)M * w->N * esz, "wb_linear_gather scratch"));
         void *tmp = arena_ptr(ctx, WB_ARENA_ACT, tmp_offset);
         rc = launch_linear(ctx, *w, A, tmp, bias_ptr, M, act_dtype, out_dtype, 0);
         if (rc == WB_OK) {
             ctx->place = pl;
-            rc = launch_scatter_cols(ctx, tmp, M, w->N, out_dtype == WB_F16);
+            if (sync && (uint64_t)M * w->N * esz <= (256u << 10)) {
+                rc = launch_scatter_barrier(ctx, tmp, M, w->N, out_dtype == WB_F16, sync->flags_offset, sync->rank, peer_bases,
+                                            n_peers, sync->timeout_us);
+                barrier_done = true;
+            } else {
+                rc = launch_scatter_cols(ctx, tmp, M, w->N, out_dtype == WB_F16);
+            }
             ctx->place = OutPlace();
         }
     }
+    if (rc == WB_OK && sync && !barrier_done)
+        rc = wb_peer_barrier(ctx, sync->flags_offset, sync->rank, peer_bases, n_peers, sync->timeout_us);
     return rc;
+}
+
+int wb_linear_gather(wb_context *ctx, wb_handle weight, uint64_t a_offset, uint64_t c_offset, uint64_t tmp_offset,
+                     wb_handle bias, int64_t M, int act_dtype, int out_dtype, int64_t n_total, int64_t col_begin,
+                     void *const *peer_bases, int n_peers)
+{
+    return linear_gather_impl(ctx, weight, a_offset, c_offset, tmp_offset, bias, M, act_dtype, out_dtype, n_total, col_begin,
+                              peer_bases, n_peers, nullptr);
+}
+
+int wb_linear_gather_barrier(wb_context *ctx, wb_handle weight, uint64_t a_offset, uint64_t c_offset, uint64_t tmp_offset,
+                             wb_handle bias, int64_t M, int act_dtype, int out_dtype, int64_t n_total, int64_t col_begin,
+                             void *const *peer_bases, int n_peers, uint64_t flags_offset, int rank, uint32_t timeout_us)
+{
+    const GatherSync sync{flags_offset, rank, timeout_us};
+    return linear_gather_impl(ctx, weight, a_offset, c_offset, tmp_offset, bias, M, act_dtype, out_dtype, n_total, col_begin,
+                              peer_bases, n_peers, &sync);
 }
 
 int wb_arena_ipc_export(wb_context *ctx, int arena, void *handle_out)
@@ -691,7 +762,7 @@ int wb_plan_query(wb_context *ctx, wb_handle weight, int64_t M, int act_dtype, i
 int wb_plan_override(wb_context *ctx, int kernel, int split_k)
 {
     WB_CTX(ctx);
-    if (kernel < 0 || kernel > WB_KERNEL_DENSE_GEMV || split_k < 0)
+    if (kernel < 0 || kernel > WB_KERNEL_GEMV_STREAM || split_k < 0)
         return fail(WB_ERR_BAD_ARG, "wb_plan_override: bad kernel %d / split %d", kernel, split_k);
     ctx->force_kernel = kernel;
     ctx->force_split = split_k;

@@ -87,18 +87,6 @@ __device__ __forceinline__ bool mbar_wait_idle(uint64_t *bar, uint32_t parity, v
     return false;
 }
 
-#ifdef WB_TC_TRACE
-// Phase trace (compiled out by default): global-timer stamps of CTA 0, printed by thread 0 at the end of the kernel.
-__device__ __forceinline__ unsigned long long tc_now()
-{
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-#define TC_STAMP(i) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) tc_trace[i] = tc_now(); } while (0)
-#else
-#define TC_STAMP(i) do { } while (0)
-#endif
 
 __device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int x, int y, uint64_t *bar)
 {
@@ -342,10 +330,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     uint32_t *tmem_slot = (uint32_t *)(bars + 3 * STAGES + 1);
     volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
 
-#ifdef WB_TC_TRACE
-    __shared__ unsigned long long tc_trace[12];
-    if (threadIdx.x == 0) TC_STAMP(0);
-#endif
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m0 = blockIdx.x * MT, n0 = blockIdx.y * COLS;
     // split-K: slice blockIdx.z covers k-blocks [kb0, KB); the ring's stage and phase count from the slice start
@@ -372,11 +356,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    if (threadIdx.x == 0) TC_STAMP(1);
     // Everything above (barriers, TMEM) ran under the tail of the previous kernel when this one was launched with
     // programmatic stream serialization; nothing that the previous kernel writes or reads is touched before this point.
     pdl_sync();
-    if (threadIdx.x == 0) TC_STAMP(2);
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
@@ -389,8 +371,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 tma_load_2d(xs(s), &map_x, kb * BK, m0, &full[s]);
                 if constexpr (DENSE) tma_load_2d(wd(s), &map_w, kb * BK, n0, &full[s]);
                 else tma_load_2d(wp(s), &map_w, n0, kb * 8, &full[s]);
-                if (kb == kb0) TC_STAMP(3);
-                if (kb == kb0 + STAGES - 1) TC_STAMP(4);  // the last copy that did not have to wait for a free stage
                 if (++s == STAGES) s = 0, ph ^= 1;
             }
         }
@@ -405,7 +385,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 ok = mbar_wait(&full[s], ph, abort_flag, p.status, 2);
                 if (ok && !DENSE) ok = mbar_wait(&deq[s], ph, abort_flag, p.status, 3);
                 if (!ok) break;
-                if (kb == kb0) TC_STAMP(5);
                 tc_fence_after();
                 const uint64_t a0 = smem_desc_sw128(smem_u32(wd(s)));
                 const uint64_t b0 = smem_desc_sw128(smem_u32(xs(s)));
@@ -419,7 +398,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 if (++s == STAGES) s = 0, ph ^= 1;
             }
             if (ok) umma_commit(acc_full);
-            TC_STAMP(6);
         }
         __syncwarp();
     } else {
@@ -474,15 +452,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                     request_group(group);
                     fresh = true;
                 }
-#ifdef WB_TC_TRACE
-                const bool tr = threadIdx.x == 64 && kb == kb0 + 2 * KG;  // set 0's third k-block
-                if (tr) TC_STAMP(10);
-#endif
                 ok = mbar_wait(&full[s], ph, abort_flag, p.status, 4);
                 if (!ok) break;
-#ifdef WB_TC_TRACE
-                if (tr) TC_STAMP(11);
-#endif
                 uint8_t *stage = smem + s * S::STAGE_BYTES;
                 const uint32_t *src = (const uint32_t *)(stage + src_off);
 #pragma unroll
@@ -509,16 +480,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 fence_async_smem();  // make the generic-proxy stores visible to the tensor core's reads
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&deq[s]);
-#ifdef WB_TC_TRACE
-                if (tr) TC_STAMP(7);
-#endif
                 s += KG;
                 if (s >= STAGES) s -= STAGES, ph ^= 1;
             }
         }
         // epilogue: warp w may touch TMEM lanes 32*(w%4) .. +31
         if (ok) ok = mbar_wait(acc_full, 0, abort_flag, p.status, 5);
-        if (threadIdx.x == 64) TC_STAMP(8);
         if (ok) {
             tc_fence_after();
             const int q = warp & 3;
@@ -560,19 +527,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             }
         }
     }
-    if (threadIdx.x == 64) TC_STAMP(9);
     tc_fence_before();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
-#ifdef WB_TC_TRACE
-    __syncthreads();
-    if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
-        const unsigned long long t10 = tc_now(), b = tc_trace[0];
-        printf("tc trace ns: setup %llu pdl %llu tma0 %llu tma_ring_filled %llu mma0 %llu mma_all %llu acc_full %llu stores %llu end %llu | set 0, third k-block: wait from %llu to %llu, unpacked and signalled %llu\n",
-               tc_trace[1] - b, tc_trace[2] - b, tc_trace[3] - b, tc_trace[4] - b, tc_trace[5] - b, tc_trace[6] - b,
-               tc_trace[8] - b, tc_trace[9] - b, t10 - b, tc_trace[10] - b, tc_trace[11] - b, tc_trace[7] - b);
-    }
-#endif
 }
 
 // ----------------------------------------------------------------------------------------------------

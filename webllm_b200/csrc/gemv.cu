@@ -3,6 +3,7 @@
 // WGSL kernels behind QwenGpt.gemm (src/model/qwen.ts:568-618): gemm_gemv_f16.wgsl,
 // gemm_gemv_split_f16.wgsl, gemm_gemv_split_reduce.wgsl and gemm_nt_f16_from_f32.wgsl.
 #include <algorithm>
+#include <atomic>
 
 #include "common.cuh"
 
@@ -49,28 +50,6 @@ namespace wb {
 
 namespace wb {
 
-
-
-// Build-time diagnostic (-DWB_GEMV_TRACE): one CTA of every launch records globaltimer stamps at the phase
-// boundaries into a ring of 64 launches, read back with wb_debug_gemv_trace. Compiled out otherwise.
-#ifdef WB_GEMV_TRACE
-__device__ unsigned long long g_gemv_trace[64 * 8];
-__device__ unsigned g_gemv_trace_n;
-#define GT_ON (blockIdx.x == gridDim.x / 2 && blockIdx.y == 0 && threadIdx.x == 0)
-#define GT_INIT() __shared__ unsigned gt_slot; if (GT_ON) gt_slot = atomicAdd(&g_gemv_trace_n, 1u) & 63u
-#define GT(i) do { if (GT_ON) { unsigned long long _t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(_t)); g_gemv_trace[gt_slot * 8 + (i)] = _t; } } while (0)
-extern "C" int wb_debug_gemv_trace(unsigned long long *out, unsigned *n)
-{
-    cudaDeviceSynchronize();
-    cudaMemcpyFromSymbol(out, g_gemv_trace, sizeof(unsigned long long) * 512);
-    cudaMemcpyFromSymbol(n, g_gemv_trace_n, 4);
-    return 0;
-}
-#else
-#define GT_INIT()
-#define GT(i)
-#endif
-
 // DIRECT (MB == 1 only): every warp holds at most one chunk of one tile and loads it straight into registers with
 // 128-bit streaming loads instead of going through the cp.async ring. Issuing six cp.async per thread costs ~0.4 us
 // more than plain loads; that is hidden when the kernel's prologue runs under its predecessor (programmatic dependent
@@ -80,8 +59,6 @@ template <int MB, bool EXACT, bool DIRECT>
 __global__ void __launch_bounds__(MB == 1 ? 256 : 512, MB == 1 ? (DIRECT ? 2 : 3) : 1) gptq_gemv_mma_kernel(const GemvParams p)
 {
     extern __shared__ uint4 smem_u4[];
-    GT_INIT();
-    GT(0);
     const uint64_t l2_policy = MB == 1 ? l2_evict_first_policy() : 0ull;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
@@ -141,10 +118,7 @@ __global__ void __launch_bounds__(MB == 1 ? 256 : 512, MB == 1 ? (DIRECT ? 2 : 3
             asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.pf_ptr + off), "r"(n) : "memory");
         }
     }
-    GT(1);
     pdl_sync();  // weights are constant: their first chunks are requested while the previous kernel still runs
-
-    GT(2);
     // ---- stage the activations (see the two branches) ----
     const int rows_pad = chunks_cta * 16;
     __shared__ float pro_red[16];
@@ -365,7 +339,6 @@ __global__ void __launch_bounds__(MB == 1 ? 256 : 512, MB == 1 ? (DIRECT ? 2 : 3
         }
         __syncthreads();
     }
-    GT(3);
     // ---- main loop over this CTA's column tiles ----
     float *red = reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(smem_u4) + p.red_off);  // [wk][wn][MB*8][32]
     __shared__ int is_last;
@@ -396,12 +369,10 @@ __global__ void __launch_bounds__(MB == 1 ? 256 : 512, MB == 1 ? (DIRECT ? 2 : 3
                 read_slot(ring + slot_use * stage_stride, c, ra);
                 slot_use = slot_use + 1 == p.stages ? 0 : slot_use + 1;
             }
-            if (tj == 0 && i == 0) GT(4);
             const int chunk = ch_begin + wk + i * p.wk;
             const int rl0 = chunk * 16 + t - row_begin;
             compute_chunk<MB, EXACT>(p, ra, rl0, g, t, xs_hi, xs_lo, xsum, chunk - ch_begin, chunks_cta, tot);
         }
-        if (tj == 0) GT(5);
         // reduce over the wk warps that share the column tile (fixed order), then write / split-K
 #pragma unroll
         for (int mb = 0; mb < MB; mb++)
@@ -475,7 +446,6 @@ __global__ void __launch_bounds__(MB == 1 ? 256 : 512, MB == 1 ? (DIRECT ? 2 : 3
         __syncthreads();  // red and is_last are reused by the next tile
     }
     cp_async_wait(0);
-    GT(6);
 }
 
 // =====================================================================================================
@@ -607,6 +577,17 @@ __global__ void __launch_bounds__(128) linear_generic_kernel(const uint32_t *__r
 
 int launch_gemm_tc(wb_context *ctx, const Weight &w, const void *A, void *C, const float *bias, int64_t M,
                    int act_dtype, int out_dtype, int exact, const wb_plan &plan);
+// gemv_stream.cu
+bool gemv_stream_supports(const Weight &w, int64_t M, int chunks, int S, bool has_lo);
+int gemv_stream_grid_x(int sm_count, int64_t N, int S);
+int launch_gemv_stream(wb_context *ctx, const Weight &w, const GemvParams &gp, bool has_lo);
+
+// WEBLLM_B200_NO_STREAM=1 keeps every decode-size call on the general GEMV kernel (for comparisons).
+static bool stream_enabled()
+{
+    static const bool on = [] { const char *e = getenv("WEBLLM_B200_NO_STREAM"); return !(e && e[0] == '1'); }();
+    return on;
+}
 int plan_gemm_tc(wb_context *ctx, const Weight &w, int64_t M, int act_dtype, int exact, wb_plan *plan);
 bool gemm_tc_supports(const Weight &w, int64_t M);
 
@@ -674,7 +655,9 @@ static int gemv_pick_stages(int64_t M, int cps, bool two_halves, int wn, int wk)
 // cluster is portable (<= 8 CTAs) and the merge buffer is small; otherwise through the workspace and arrival counters.
 static bool gemv_cluster_merge(int64_t M, int S) { return S > 1 && S <= 8 && M <= 8; }
 
-static void plan_gemv_mma(wb_context *ctx, const Weight &w, int64_t M, int two_halves, wb_plan *plan)
+// `stream`: 0 = the general kernel only, 1 = the streaming kernel where the shape suits it, 2 = the streaming kernel
+// or nothing (plan->kernel stays 0 when it does not take the shape or the forced split).
+static void plan_gemv_mma(wb_context *ctx, const Weight &w, int64_t M, int two_halves, wb_plan *plan, int stream)
 {
     const int chunks = (int)((w.pack_rows + 15) / 16);
     const int col_tiles = (int)((w.N + 31) / 32);
@@ -700,24 +683,39 @@ static void plan_gemv_mma(wb_context *ctx, const Weight &w, int64_t M, int two_h
     // Bandwidth-bound shapes (M <= 4, whole chunks and tiles) go to the streaming kernel, whose CTAs are persistent
     // over 32-column tiles, two per SM: the split is the one that makes the longest CTA shortest (tiles per CTA x
     // chunks per slice) while a slice keeps at least 20 chunks.
-    if (M <= 4 && w.K % 128 == 0 && w.N % 32 == 0 && w.group % 128 == 0 && chunks >= 20) {
+    int stream_s = 0;
+    if (stream != 0 && ctx->force_split > 0) {
+        const int fs = ctx->force_split < chunks ? ctx->force_split : chunks;
+        if (gemv_stream_supports(w, M, chunks, fs, two_halves != 0)) stream_s = fs;
+    } else if (stream != 0) {
         const int tiles = (int)(w.N / 32);
-        int best_s = 0;
         long best_cost = 0;
         for (int s = 1; s <= 8; s++) {
+            if (!gemv_stream_supports(w, M, chunks, s, two_halves != 0)) continue;
             const int c = (chunks + s - 1) / s;
-            if (c < 20) break;
-            const int s_eff = (chunks + c - 1) / c;
-            int cap = 2 * ctx->sm_count / s_eff;
+            int cap = 2 * ctx->sm_count / s;
             if (cap < 1) cap = 1;
             const int waves = (tiles + cap - 1) / cap;
             const long cost = (long)waves * c;
-            const int ctas = (tiles + waves - 1) / waves * s_eff;
-            if (ctas * 2 < ctx->sm_count) continue;  // too few CTAs to stream: the general kernel with clusters does better
-            if (best_s == 0 || cost < best_cost) best_s = s_eff, best_cost = cost;
+            const int ctas = (tiles + waves - 1) / waves * s;
+            // too few CTAs to stream: the general kernel with clusters does better (unless this kernel was asked for)
+            if (stream == 1 && ctas * 2 < ctx->sm_count) continue;
+            if (stream_s == 0 || cost < best_cost) stream_s = s, best_cost = cost;
         }
-        if (best_s > 0) S = best_s;
     }
+    if (stream_s > 0) {
+        plan->kernel = WB_KERNEL_GEMV_STREAM;
+        plan->split_k = stream_s;
+        plan->grid_x = gemv_stream_grid_x(ctx->sm_count, w.N, stream_s);
+        plan->grid_y = stream_s;
+        plan->grid_z = 1;
+        plan->block = 256;
+        plan->tile_m = 0, plan->tile_n = 32;
+        plan->launches = 1;
+        plan->scratch_bytes = stream_s > 1 ? (uint64_t)stream_s * M * w.N * 4 : 0;
+        return;
+    }
+    if (stream == 2) return;
     // shared memory: staged activations (16 bytes per row per packed row, twice in exact mode)
     auto smem_for = [&](int s) { return (uint64_t)gemv_smem_bytes(M, (chunks + s - 1) / s, two_halves, wn, wk, 1, nullptr); };
     while (smem_for(S) > (uint64_t)kGemvSmemLimit && S < chunks) S++;
@@ -738,7 +736,8 @@ static void plan_gemv_mma(wb_context *ctx, const Weight &w, int64_t M, int two_h
     plan->scratch_bytes = S > 1 ? (uint64_t)S * M * w.N * 4 : 0;
 }
 
-int plan_linear(wb_context *ctx, const Weight &w, int64_t M, int act_dtype, int exact, wb_plan *plan)
+// allow_stream = false: a decode-size call that fuses a prologue stays on the general GEMV kernel.
+static int plan_linear_ex(wb_context *ctx, const Weight &w, int64_t M, int act_dtype, int exact, bool allow_stream, wb_plan *plan)
 {
     memset(plan, 0, sizeof *plan);
     int kind = ctx->force_kernel;
@@ -750,13 +749,20 @@ int plan_linear(wb_context *ctx, const Weight &w, int64_t M, int act_dtype, int 
     }
     switch (kind) {
     case WB_KERNEL_GEMV_MMA:
+    case WB_KERNEL_GEMV_STREAM: {
         if (!gemv_mma_supports(w, M))
             return fail(WB_ERR_UNSUPPORTED, "GEMV_MMA needs a GPTQ weight, M <= 32, K %% 8 == 0, N %% 4 == 0, group %% 128 == 0");
-        plan_gemv_mma(ctx, w, M, act_dtype == WB_F32, plan);
-        if ((uint64_t)plan->grid_x > (uint64_t)kMaxCounters)
+        // the planner's own choice may be either GEMV kernel; a forced kind means that kernel and no other
+        const int stream = kind == WB_KERNEL_GEMV_STREAM ? 2 : (ctx->force_kernel == 0 && allow_stream && stream_enabled()) ? 1 : 0;
+        plan_gemv_mma(ctx, w, M, act_dtype == WB_F32, plan, stream);
+        if (plan->kernel == 0)
+            return fail(WB_ERR_UNSUPPORTED, "GEMV_STREAM needs M <= 4, K %% 128 == 0, N %% 32 == 0, group %% 128 == 0 and K slices "
+                                            "of >= 20 chunks of 128 (the last one >= 8)");
+        if (plan->kernel == WB_KERNEL_GEMV_MMA && (uint64_t)plan->grid_x > (uint64_t)kMaxCounters)
             return fail(WB_ERR_UNSUPPORTED, "N too large for the split-K counter table");
         if (plan->scratch_bytes > kWorkspaceBytes) return fail(WB_ERR_OOM, "split-K partials exceed the workspace");
         return WB_OK;
+    }
     case WB_KERNEL_DENSE_GEMV:
         if (!dense_gemv_supports(w, M)) return fail(WB_ERR_UNSUPPORTED, "DENSE_GEMV needs an fp16 weight, M <= 8, K %% 8 == 0");
         plan->kernel = kind;
@@ -781,23 +787,29 @@ int plan_linear(wb_context *ctx, const Weight &w, int64_t M, int act_dtype, int 
     return fail(WB_ERR_BAD_ARG, "unknown kernel kind %d", kind);
 }
 
+int plan_linear(wb_context *ctx, const Weight &w, int64_t M, int act_dtype, int exact, wb_plan *plan)
+{
+    return plan_linear_ex(ctx, w, M, act_dtype, exact, true, plan);
+}
+
 // Most of a later weight that one call asks the L2 to fetch (a fraction of the 126 MB L2).
 constexpr uint64_t kPrefetchLimit = 32ull << 20;
 
 template <int MB, bool EXACT, bool DIRECT>
-static cudaError_t launch_gemv_inst(const GemvParams &p, dim3 grid, int block, size_t smem, cudaStream_t st)
+static cudaError_t launch_gemv_inst(const GemvParams &p, dim3 grid, int block, size_t smem, cudaStream_t st, bool pdl)
 {
     cudaFuncSetAttribute(gptq_gemv_mma_kernel<MB, EXACT, DIRECT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemvSmemLimit);
-    return launch_pdl_cluster(gptq_gemv_mma_kernel<MB, EXACT, DIRECT>, grid, dim3(block), smem, st, p.cluster ? (unsigned)p.S : 1u, p);
+    return launch_cluster_ex(gptq_gemv_mma_kernel<MB, EXACT, DIRECT>, grid, dim3(block), smem, st, p.cluster ? (unsigned)p.S : 1u, pdl, p);
 }
 
 template <int MB>
-static cudaError_t launch_gemv_mb(const GemvParams &p, dim3 grid, int block, size_t smem, bool exact, cudaStream_t st)
+static cudaError_t launch_gemv_mb(const GemvParams &p, dim3 grid, int block, size_t smem, bool exact, cudaStream_t st, bool pdl = true)
 {
     if constexpr (MB == 1) {
-        if (p.direct) return exact ? launch_gemv_inst<1, true, true>(p, grid, block, smem, st) : launch_gemv_inst<1, false, true>(p, grid, block, smem, st);
+        if (p.direct)
+            return exact ? launch_gemv_inst<1, true, true>(p, grid, block, smem, st, pdl) : launch_gemv_inst<1, false, true>(p, grid, block, smem, st, pdl);
     }
-    return exact ? launch_gemv_inst<MB, true, false>(p, grid, block, smem, st) : launch_gemv_inst<MB, false, false>(p, grid, block, smem, st);
+    return exact ? launch_gemv_inst<MB, true, false>(p, grid, block, smem, st, pdl) : launch_gemv_inst<MB, false, false>(p, grid, block, smem, st, pdl);
 }
 
 bool linear_fusion_supported(wb_context *ctx, const Weight &w, int64_t M)
@@ -806,25 +818,23 @@ bool linear_fusion_supported(wb_context *ctx, const Weight &w, int64_t M)
     return gemv_mma_supports(w, M);  // what plan_linear picks first for M <= 16
 }
 
-// gemv_stream.cu
-bool gemv_stream_supports(const Weight &w, int64_t M, int chunks_per_split);
-int launch_gemv_stream(wb_context *ctx, const Weight &w, const GemvParams &gp, bool has_lo, bool *launched);
-
 int launch_linear(wb_context *ctx, const Weight &w, const void *A, void *C, const float *bias, int64_t M,
                   int act_dtype, int out_dtype, int exact, const LinearFusion *fusion)
 {
     wb_plan plan;
     // exact mode only changes anything for f32 activations
     const int ex = (exact && act_dtype == WB_F32) ? 1 : 0;
-    WB_CHECK(plan_linear(ctx, w, M, act_dtype, ex, &plan));
-    if (fusion && fusion->kind != 0 && (plan.kernel != WB_KERNEL_GEMV_MMA || M > 8 || act_dtype != WB_F32))
+    const bool fused = fusion && fusion->kind != 0;
+    WB_CHECK(plan_linear_ex(ctx, w, M, act_dtype, ex, !fused, &plan));
+    if (fused && (plan.kernel != WB_KERNEL_GEMV_MMA || M > 8 || act_dtype != WB_F32))
         return fail(WB_ERR_UNSUPPORTED, "a fused prologue needs the int4 GEMV kernel, M <= 8 and f32 activations");
     // The streaming kernel always keeps f32 activations at ~22 bits (hi + lo halves): the reference's
     // GEMV reads A as f32 (gemm_gemv_f16.wgsl:45-58) and the extra MMAs are free in an HBM-bound kernel.
     const int ex_gemv = act_dtype == WB_F32 ? 1 : 0;
     const char *base = ctx->arena[WB_ARENA_WEIGHTS].base;
     switch (plan.kernel) {
-    case WB_KERNEL_GEMV_MMA: {
+    case WB_KERNEL_GEMV_MMA:
+    case WB_KERNEL_GEMV_STREAM: {
         GemvParams p;
         p.qw = (const uint32_t *)(base + w.off_main);
         p.qz = w.has_zeros ? (const uint32_t *)(base + w.off_zeros) : nullptr;
@@ -841,15 +851,10 @@ int launch_linear(wb_context *ctx, const Weight &w, const void *A, void *C, cons
         p.wn = plan.tile_m, p.wk = plan.tile_n;
         p.x_f16 = act_dtype == WB_F16, p.out_f16 = out_dtype == WB_F16;
         p.xs_stride = p.chunks_per_split * 16 + 4;
-        static const bool stream_on = [] { const char *e = getenv("WEBLLM_B200_NO_STREAM"); return !(e && e[0] == '1'); }();
-        if (stream_on && !(fusion && fusion->kind != 0) && gemv_stream_supports(w, M, p.chunks_per_split)) {
-            // bandwidth-bound shape: the TMA-fed streaming kernel (whole chunks, M <= 4)
-            bool launched = false;
-            WB_CHECK(launch_gemv_stream(ctx, w, p, ex_gemv != 0, &launched));
-            if (launched) {
-                ctx->prefetch_weight = -1;
-                return WB_OK;
-            }
+        if (plan.kernel == WB_KERNEL_GEMV_STREAM) {
+            // bandwidth-bound shape: whole chunks, M <= 4, weights straight into registers
+            ctx->prefetch_weight = -1;
+            return launch_gemv_stream(ctx, w, p, ex_gemv != 0);
         }
         p.prologue = kPrologueNone, p.delta = nullptr, p.x_out = nullptr, p.norm_w = nullptr, p.eps = 0.f, p.up = nullptr;
         p.ld_x = (int)w.K;
@@ -940,7 +945,11 @@ constexpr size_t kStaticScratchBytes = kStaticCounterWords * sizeof(unsigned) + 
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
 constexpr int kMaxDevices = 64;
-void *g_static_scratch_addr[kMaxDevices] = {};  // device address of g_static_scratch, per device ordinal
+// Device address of g_static_scratch per device ordinal, filled by the first call on that device. Threads that race
+// on a first call all store the same value (the address is a property of the device), hence relaxed atomics.
+std::atomic<void *> g_static_scratch_addr[kMaxDevices];
+
+bool misaligned(const void *p, uintptr_t a) { return ((uintptr_t)p & (a - 1)) != 0; }
 
 }  // namespace
 
@@ -957,18 +966,25 @@ extern "C" int wb_gptq_gemv_static(const void *qweight, const void *qzeros, cons
     if (K <= 0 || N <= 0 || M <= 0) return fail(WB_ERR_BAD_ARG, "wb_gptq_gemv_static: sizes must be positive");
     if (M > 32 || K % 8 != 0 || N % 4 != 0 || group_size <= 0 || group_size % 128 != 0)
         return fail(WB_ERR_UNSUPPORTED, "wb_gptq_gemv_static needs M <= 32, K %% 8 == 0, N %% 4 == 0, group %% 128 == 0");
+    // The kernel copies qweight in 16-byte pieces, reads x as 16-byte vectors and scales as 8-byte pairs: a pointer into
+    // the middle of a larger buffer that breaks these would fault on the device, so it is refused here instead.
+    if (misaligned(qweight, 16) || misaligned(x, 16) || misaligned(y, 16))
+        return fail(WB_ERR_BAD_ARG, "wb_gptq_gemv_static: qweight, x and y must be 16-byte aligned");
+    if (misaligned(scales_f16, 8)) return fail(WB_ERR_BAD_ARG, "wb_gptq_gemv_static: scales_f16 must be 8-byte aligned");
+    if (misaligned(qzeros, 4) || misaligned(bias, 4))
+        return fail(WB_ERR_BAD_ARG, "wb_gptq_gemv_static: qzeros and bias must be 4-byte aligned");
     int device = 0;
     WB_CUDA(cudaGetDevice(&device));
     if (device < 0 || device >= kMaxDevices) return fail(WB_ERR_UNSUPPORTED, "device ordinal %d is beyond %d", device, kMaxDevices);
-    if (!g_static_scratch_addr[device]) {
+    void *scratch = g_static_scratch_addr[device].load(std::memory_order_relaxed);
+    if (!scratch) {
         // In host code the array's name is only a handle; its device address has to be asked for, once per
         // device, with that device current. This is the set-up the first call on a device performs.
-        void *p = nullptr;
-        WB_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
-        g_static_scratch_addr[device] = p;
+        WB_CUDA(cudaGetSymbolAddress(&scratch, g_static_scratch));
+        g_static_scratch_addr[device].store(scratch, std::memory_order_relaxed);
     }
-    unsigned *counters = (unsigned *)g_static_scratch_addr[device];
-    float *partial = (float *)((unsigned char *)g_static_scratch_addr[device] + kStaticCounterWords * sizeof(unsigned));
+    unsigned *counters = (unsigned *)scratch;
+    float *partial = (float *)((unsigned char *)scratch + kStaticCounterWords * sizeof(unsigned));
 
     // launch shape: the regular planner's layout for M, the caller's (or a simple automatic) split
     const int pack_rows = (int)(K / 8), chunks = (pack_rows + 15) / 16, col_tiles = (int)((N + 31) / 32);
@@ -1021,9 +1037,12 @@ extern "C" int wb_gptq_gemv_static(const void *qweight, const void *qzeros, cons
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
     dim3 grid(gemv_grid_x(sms, ctas_n, S, wn * wk * 32, smem), S);
     const int block = wn * wk * 32;
-    cudaError_t e = MB == 1   ? launch_gemv_mb<1>(p, grid, block, smem, two_halves, st)
-                    : MB == 2 ? launch_gemv_mb<2>(p, grid, block, smem, two_halves, st)
-                              : launch_gemv_mb<4>(p, grid, block, smem, two_halves, st);
+    // Launched WITHOUT programmatic stream serialization: the tensors are the caller's, and whatever the caller
+    // enqueued before this call on the stream (a kernel that still writes qweight or x) must have completed before
+    // the first weight is requested.
+    cudaError_t e = MB == 1   ? launch_gemv_mb<1>(p, grid, block, smem, two_halves, st, false)
+                    : MB == 2 ? launch_gemv_mb<2>(p, grid, block, smem, two_halves, st, false)
+                              : launch_gemv_mb<4>(p, grid, block, smem, two_halves, st, false);
     WB_CUDA(e);
     return WB_OK;
 }

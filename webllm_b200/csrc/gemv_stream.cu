@@ -80,7 +80,7 @@ __global__ void __launch_bounds__(256, 2) gptq_gemv_stream_kernel(const GemvPara
     // three are in flight while the activations are staged; in the loop two are in flight behind the one in use.
     const uint32_t *wrow = p.qw + (int64_t)t * p.N + 4 * g;
     const int64_t row_step = (int64_t)4 * p.N;
-    const int ch_first = ch_begin + warp;  // chunks_cta >= 20: every warp has chunks
+    const int ch_first = ch_begin + warp;  // every slice holds >= 8 chunks (checked on the host): every warp has one
     auto fetch_at = [&](int j, int ch, StreamRegs &r) {
         const int tile = (int)blockIdx.x + j * (int)gridDim.x;
         stream_fetch(p, wrow + tile * 32, row_step, ch, tile * 32 + 4 * g, r);
@@ -273,29 +273,46 @@ __global__ void __launch_bounds__(256, 2) gptq_gemv_stream_kernel(const GemvPara
 }
 
 // ---- host side -------------------------------------------------------------------------------------------------
-bool gemv_stream_supports(const Weight &w, int64_t M, int chunks_per_split)
+// Dynamic shared memory of one CTA: the staged operand rows (hi, lo for f32 activations, one row of zeros), the
+// per-chunk activation sums and the cross-warp reduction buffer.
+static size_t gemv_stream_smem(int64_t M, int cps, bool has_lo)
 {
-    // whole chunks and tiles only; enough chunks per slice that streaming (not latency) is what matters
-    return w.kind == WeightKind::Gptq && M >= 1 && M <= 4 && w.K % 128 == 0 && w.N % 32 == 0 && w.group % 128 == 0 &&
-           chunks_per_split >= 20 && w.N / 32 <= kMaxCounters;  // one arrival counter per column tile when K is split
+    const size_t rows = (size_t)(has_lo ? 2 * M : M) + 1;
+    return rows * (size_t)(cps * 16 + 4) * 16 + (size_t)((M * cps + 3) & ~3) * 4 + 8 * 32 * 4 * 4;
 }
 
-// Returns WB_OK and *launched = true when the streaming kernel took the call; *launched = false when it does not fit.
-int launch_gemv_stream(wb_context *ctx, const Weight &w, const GemvParams &gp, bool has_lo, bool *launched)
+// Whole chunks and tiles only; enough chunks per slice that streaming (not latency) is what matters; every one of
+// the 8 warps must own a chunk in EVERY slice, the shorter last one included (a warp without one would prefetch past
+// its slice); two CTAs per SM must fit the shared memory; one arrival counter per column tile when K is split.
+bool gemv_stream_supports(const Weight &w, int64_t M, int chunks, int S, bool has_lo)
 {
-    *launched = false;
-    GemvParams p = gp;
-    const int cps = p.chunks_per_split, M = p.M;
-    p.xs_stride = cps * 16 + 4;
-    const size_t rows = (size_t)(has_lo ? 2 * M : M) + 1;
-    const size_t smem = rows * p.xs_stride * 16 + (size_t)((M * cps + 3) & ~3) * 4 + 8 * 32 * 4 * 4;
-    if (smem > 100 * 1024) return WB_OK;  // two CTAs per SM
-    // grid: what is resident at once (two CTAs per SM), evened out so that every CTA walks the same number of tiles
-    const int col_tiles = (int)(w.N / 32);
-    int capacity = ctx->sm_count * 2 / p.S;
+    if (w.kind != WeightKind::Gptq || M < 1 || M > 4 || w.K % 128 != 0 || w.N % 32 != 0 || w.group % 128 != 0) return false;
+    if (S < 1 || S > chunks) return false;
+    const int cps = (chunks + S - 1) / S;
+    if ((chunks + cps - 1) / cps != S) return false;  // would leave an empty slice
+    const int last = chunks - (S - 1) * cps;
+    return cps >= 20 && last >= 8 && w.N / 32 <= kMaxCounters && gemv_stream_smem(M, cps, has_lo) <= 100 * 1024;
+}
+
+// Launch grid: what is resident at once (two CTAs per SM), evened out so that every CTA walks the same number of tiles.
+int gemv_stream_grid_x(int sm_count, int64_t N, int S)
+{
+    const int col_tiles = (int)(N / 32);
+    int capacity = sm_count * 2 / S;
     if (capacity < 1) capacity = 1;
     const int waves = (col_tiles + capacity - 1) / capacity;
-    dim3 grid((unsigned)((col_tiles + waves - 1) / waves), (unsigned)p.S);
+    return (col_tiles + waves - 1) / waves;
+}
+
+int launch_gemv_stream(wb_context *ctx, const Weight &w, const GemvParams &gp, bool has_lo)
+{
+    GemvParams p = gp;
+    if (!gemv_stream_supports(w, p.M, p.chunks, p.S, has_lo))
+        return fail(WB_ERR_UNSUPPORTED, "the streaming GEMV does not take this shape or split");
+    const int cps = p.chunks_per_split;
+    p.xs_stride = cps * 16 + 4;
+    const size_t smem = gemv_stream_smem(p.M, cps, has_lo);
+    dim3 grid((unsigned)gemv_stream_grid_x(ctx->sm_count, w.N, p.S), (unsigned)p.S);
     cudaError_t e;
     if (has_lo) {
         cudaFuncSetAttribute(gptq_gemv_stream_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -306,7 +323,6 @@ int launch_gemv_stream(wb_context *ctx, const Weight &w, const GemvParams &gp, b
     }
     ctx->launches++;
     WB_CUDA(e);
-    *launched = true;
     return WB_OK;
 }
 

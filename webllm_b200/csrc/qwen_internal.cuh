@@ -1,4 +1,4 @@
-// Internal layout of the Qwen2 model object (shared by qwen_model.cu and qwen_mega.cu).
+// Internal layout of the Qwen2 model object (qwen_model.cu).
 #pragma once
 #include "qwen_ops.cuh"
 
@@ -17,8 +17,6 @@ struct Bufs {
     float *x, *xa, *n, *q, *k, *v, *att, *proj, *gu, *act, *logits;
     int ldq, ldk, ldv, ld_gu;
 };
-
-struct Mega;  // state of the single-kernel decode step (qwen_mega.cu)
 
 }  // namespace wbq
 
@@ -43,13 +41,5 @@ struct wb_qwen {
     cudaStream_t graph_stream = nullptr;
     int graph_exact = -1;
     uint64_t graph_launches = 0;    // kernels in one captured decode step
-    int decode_mode = 0;            // 0 = automatic, 1 = one kernel per operation (CUDA graph), 2 = single persistent kernel
-    wbq::Mega *mega = nullptr;
+    uint64_t carve_mark = 0, carve_top = 0;  // weight-arena `used` before and after the model's own allocations
 };
-
-namespace wbq {
-// qwen_mega.cu
-bool mega_supported(const wb_qwen *m);
-int mega_decode(wb_qwen *m, int64_t n_steps);  // runs n_steps decode steps on the device-resident state
-void mega_destroy(wb_qwen *m);
-}  // namespace wbq

@@ -209,6 +209,7 @@ int wb_qwen_create(wb_context *ctx, const wb_qwen_config *cfg, wb_qwen **out)
 {
     if (!ctx || !cfg || !out) return fail(WB_ERR_BAD_ARG, "wb_qwen_create: NULL argument");
     WB_CUDA(cudaSetDevice(ctx->device));
+    WB_NOT_RECORDING(ctx, "wb_qwen_create");
     if (cfg->n_head <= 0 || cfg->n_embd % cfg->n_head != 0)
         return fail(WB_ERR_BAD_ARG, "nEmbd(%d) 必须能被 nHead(%d) 整除", cfg->n_embd, cfg->n_head);
     if (cfg->n_kv_head <= 0 || cfg->n_head % cfg->n_kv_head != 0)
@@ -254,35 +255,46 @@ int wb_qwen_create(wb_context *ctx, const wb_qwen_config *cfg, wb_qwen **out)
         if ((L.qkv >= 0) != (m->layers[0].qkv >= 0) || (L.gate_up >= 0) != (m->layers[0].gate_up >= 0))
             return fail(WB_ERR_BAD_ARG, "layers must all use fused projections or none");
     }
-    // residency owned by the model: KV cache, rope table, decode state (taken from the weight slab)
-    const uint64_t cache_bytes = (uint64_t)cfg->n_layer * cfg->max_t * KV * kv_elem(m.get());
-    WB_CHECK(carve(ctx, WB_ARENA_WEIGHTS, cache_bytes, (void **)&m->k_cache));
-    WB_CHECK(carve(ctx, WB_ARENA_WEIGHTS, cache_bytes, (void **)&m->v_cache));
-    WB_CUDA(cudaMemsetAsync(m->k_cache, 0, cache_bytes, ctx->stream));
-    WB_CUDA(cudaMemsetAsync(m->v_cache, 0, cache_bytes, ctx->stream));
-    const int half = m->D / 2;
-    std::vector<float> cs((size_t)cfg->max_t * half * 2);
-    for (int pos = 0; pos < cfg->max_t; pos++)
-        for (int i = 0; i < half; i++) {
-            // ropeHalfRef: angle = pos * base^(-(2i)/D), evaluated in double (src/reference/qwen-ref.ts:49-53)
-            const double angle = (double)pos * pow((double)cfg->rope_theta, -((double)(2 * i) / (double)m->D));
-            cs[((size_t)pos * half + i) * 2] = (float)cos(angle);
-            cs[((size_t)pos * half + i) * 2 + 1] = (float)sin(angle);
-        }
-    WB_CHECK(carve_t(ctx, WB_ARENA_WEIGHTS, cs.size(), &m->cs_table));
-    WB_CUDA(cudaMemcpyAsync(m->cs_table, cs.data(), cs.size() * 4, cudaMemcpyHostToDevice, ctx->stream));
-    WB_CHECK(alloc_bufs(m.get(), WB_ARENA_WEIGHTS, 1, 1, &m->dec));
-    m->history_cap = cfg->max_t;
-    WB_CHECK(carve_t(ctx, WB_ARENA_WEIGHTS, (uint64_t)m->history_cap, &m->d_history));
-    WB_CHECK(carve_t(ctx, WB_ARENA_WEIGHTS, 64, &m->d_cache_len));
-    m->d_step = m->d_cache_len + 1;
-    WB_CHECK(carve_t(ctx, WB_ARENA_WEIGHTS, 128, &m->d_bval));
-    WB_CHECK(carve_t(ctx, WB_ARENA_WEIGHTS, 128, &m->d_bidx));
-    WB_CUDA(cudaMemsetAsync(m->d_cache_len, 0, 64 * sizeof(int), ctx->stream));
-    WB_CHECK(carve_t(ctx, WB_ARENA_WEIGHTS, (uint64_t)op_attention_decode_scratch_floats(m->H, m->D), &m->att_scratch));
-    WB_CHECK(carve_t(ctx, WB_ARENA_WEIGHTS, (uint64_t)m->H, &m->att_counters));
-    WB_CUDA(cudaMemsetAsync(m->att_counters, 0, (size_t)m->H * sizeof(unsigned), ctx->stream));
-    WB_CUDA(cudaStreamSynchronize(ctx->stream));
+    // residency owned by the model: KV cache, rope table, decode state (taken from the weight slab, handed back by
+    // wb_qwen_destroy when nothing was allocated after it)
+    m->carve_mark = ctx->arena[WB_ARENA_WEIGHTS].used;
+    const int rc = [&]() -> int {
+        const uint64_t cache_bytes = (uint64_t)cfg->n_layer * cfg->max_t * KV * kv_elem(m.get());
+        WB_CHECK(carve(ctx, WB_ARENA_WEIGHTS, cache_bytes, (void **)&m->k_cache));
+        WB_CHECK(carve(ctx, WB_ARENA_WEIGHTS, cache_bytes, (void **)&m->v_cache));
+        WB_CUDA(cudaMemsetAsync(m->k_cache, 0, cache_bytes, ctx->stream));
+        WB_CUDA(cudaMemsetAsync(m->v_cache, 0, cache_bytes, ctx->stream));
+        const int half = m->D / 2;
+        std::vector<float> cs((size_t)cfg->max_t * half * 2);
+        for (int pos = 0; pos < cfg->max_t; pos++)
+            for (int i = 0; i < half; i++) {
+                // ropeHalfRef: angle = pos * base^(-(2i)/D), evaluated in double (src/reference/qwen-ref.ts:49-53)
+                const double angle = (double)pos * pow((double)cfg->rope_theta, -((double)(2 * i) / (double)m->D));
+                cs[((size_t)pos * half + i) * 2] = (float)cos(angle);
+                cs[((size_t)pos * half + i) * 2 + 1] = (float)sin(angle);
+            }
+        WB_CHECK(carve_t(ctx, WB_ARENA_WEIGHTS, cs.size(), &m->cs_table));
+        WB_CUDA(cudaMemcpyAsync(m->cs_table, cs.data(), cs.size() * 4, cudaMemcpyHostToDevice, ctx->stream));
+        WB_CHECK(alloc_bufs(m.get(), WB_ARENA_WEIGHTS, 1, 1, &m->dec));
+        m->history_cap = cfg->max_t;
+        WB_CHECK(carve_t(ctx, WB_ARENA_WEIGHTS, (uint64_t)m->history_cap, &m->d_history));
+        WB_CHECK(carve_t(ctx, WB_ARENA_WEIGHTS, 64, &m->d_cache_len));
+        m->d_step = m->d_cache_len + 1;
+        WB_CHECK(carve_t(ctx, WB_ARENA_WEIGHTS, 128, &m->d_bval));
+        WB_CHECK(carve_t(ctx, WB_ARENA_WEIGHTS, 128, &m->d_bidx));
+        WB_CUDA(cudaMemsetAsync(m->d_cache_len, 0, 64 * sizeof(int), ctx->stream));
+        WB_CHECK(carve_t(ctx, WB_ARENA_WEIGHTS, (uint64_t)op_attention_decode_scratch_floats(m->H, m->D), &m->att_scratch));
+        WB_CHECK(carve_t(ctx, WB_ARENA_WEIGHTS, (uint64_t)m->H, &m->att_counters));
+        WB_CUDA(cudaMemsetAsync(m->att_counters, 0, (size_t)m->H * sizeof(unsigned), ctx->stream));
+        WB_CUDA(cudaStreamSynchronize(ctx->stream));  // `cs` is read by the copy until here
+        return WB_OK;
+    }();
+    if (rc != WB_OK) {
+        cudaStreamSynchronize(ctx->stream);
+        ctx->arena[WB_ARENA_WEIGHTS].used = m->carve_mark;
+        return rc;
+    }
+    m->carve_top = ctx->arena[WB_ARENA_WEIGHTS].used;
     *out = m.release();
     return WB_OK;
 }
@@ -293,7 +305,9 @@ int wb_qwen_destroy(wb_qwen *m)
     cudaSetDevice(m->ctx->device);
     cudaStreamSynchronize(m->ctx->stream);
     drop_graph(m);
-    wbq::mega_destroy(m);
+    // the model's carve is handed back when it still is the top of the weight arena
+    ArenaState &wa = m->ctx->arena[WB_ARENA_WEIGHTS];
+    if (wa.used == m->carve_top) wa.used = m->carve_mark;
     delete m;
     return WB_OK;
 }
@@ -345,6 +359,7 @@ static int run_eager(wb_qwen *m, const uint32_t *tokens, int64_t M, int64_t B, i
 int wb_qwen_forward(wb_qwen *m, const uint32_t *tokens, int64_t B, int64_t T, uint64_t *logits_offset)
 {
     WB_MODEL(m);
+    WB_NOT_RECORDING(m->ctx, "wb_qwen_forward");
     if (B <= 0 || T <= 0) return fail(WB_ERR_BAD_ARG, "forward: B and T must be positive");
     if (T > m->cfg.max_t) return fail(WB_ERR_BAD_ARG, "T=%lld 超过 blockSize=%d", (long long)T, m->cfg.max_t);
     return run_eager(m, tokens, B * T, B, T, 0, false, false, logits_offset);
@@ -353,6 +368,7 @@ int wb_qwen_forward(wb_qwen *m, const uint32_t *tokens, int64_t B, int64_t T, ui
 int wb_qwen_prefill(wb_qwen *m, const uint32_t *tokens, int64_t n, int last_only, uint64_t *logits_offset)
 {
     WB_MODEL(m);
+    WB_NOT_RECORDING(m->ctx, "wb_qwen_prefill");
     if (m->cache_len != 0) return fail(WB_ERR_BAD_ARG, "prefill 前请先 resetCache()（当前 cacheLen=%lld）", (long long)m->cache_len);
     if (n <= 0) return fail(WB_ERR_BAD_ARG, "prefill: tokens 不能为空");
     if (n > m->cfg.max_t) return fail(WB_ERR_BAD_ARG, "上下文长度 %lld 超过 blockSize=%d", (long long)n, m->cfg.max_t);
@@ -362,6 +378,7 @@ int wb_qwen_prefill(wb_qwen *m, const uint32_t *tokens, int64_t n, int last_only
 int wb_qwen_decode_step(wb_qwen *m, uint32_t token, uint64_t *logits_offset)
 {
     WB_MODEL(m);
+    WB_NOT_RECORDING(m->ctx, "wb_qwen_decode_step");
     if (m->cache_len == 0) return fail(WB_ERR_BAD_ARG, "decodeStep 前请先调用 prefill()");
     if (m->cache_len + 1 > m->cfg.max_t)
         return fail(WB_ERR_BAD_ARG, "上下文长度 %lld 超过 blockSize=%d", (long long)(m->cache_len + 1), m->cfg.max_t);
@@ -379,6 +396,7 @@ static int enqueue_graph_step(wb_qwen *m)
 int wb_qwen_decode_greedy(wb_qwen *m, uint32_t first_token, int64_t n_steps, uint32_t *out_tokens)
 {
     WB_MODEL(m);
+    WB_NOT_RECORDING(m->ctx, "wb_qwen_decode_greedy");
     wb_context *ctx = m->ctx;
     if (m->cache_len == 0) return fail(WB_ERR_BAD_ARG, "decodeStep 前请先调用 prefill()");
     if (n_steps <= 0 || !out_tokens) return fail(WB_ERR_BAD_ARG, "decode_greedy: n_steps must be positive");
@@ -388,16 +406,6 @@ int wb_qwen_decode_greedy(wb_qwen *m, uint32_t first_token, int64_t n_steps, uin
     const int state[2] = {(int)m->cache_len, 0};
     WB_CUDA(cudaMemcpyAsync(m->d_cache_len, state, sizeof state, cudaMemcpyHostToDevice, ctx->stream));
     WB_CUDA(cudaMemcpyAsync(m->dec.tokens, &first_token, 4, cudaMemcpyHostToDevice, ctx->stream));
-    // One kernel per operation replayed as a CUDA graph (the automatic choice: it measured faster), or, when
-    // asked for and the model qualifies (fused GPTQ projections), a single persistent kernel per step.
-    if (m->decode_mode == 2 && wbq::mega_supported(m)) {
-        WB_CHECK(wbq::mega_decode(m, n_steps));
-        WB_CUDA(cudaMemcpyAsync(out_tokens, m->d_history, (size_t)n_steps * 4, cudaMemcpyDeviceToHost, ctx->stream));
-        WB_CHECK(wb_synchronize(ctx));
-        m->cache_len += n_steps;
-        return WB_OK;
-    }
-    if (m->decode_mode == 2) return fail(WB_ERR_UNSUPPORTED, "the single-kernel decode step needs fused GPTQ projections (qkvW, gateUpW) with group % 128 == 0");
     if (m->graph && (m->graph_stream != ctx->stream || m->graph_exact != m->exact)) drop_graph(m);
     if (!m->graph) {
         // Warm-up step outside capture (sets kernel attributes, counts the step's kernels), then restore the
@@ -434,17 +442,10 @@ int wb_qwen_decode_greedy(wb_qwen *m, uint32_t first_token, int64_t n_steps, uin
     return WB_OK;
 }
 
-int wb_qwen_set_decode_mode(wb_qwen *m, int mode)
-{
-    WB_MODEL(m);
-    if (mode < 0 || mode > 2) return fail(WB_ERR_BAD_ARG, "decode mode must be 0 (automatic), 1 (graph of kernels) or 2 (single kernel)");
-    m->decode_mode = mode;
-    return WB_OK;
-}
-
 int wb_qwen_last_logits(wb_qwen *m, float *out)
 {
     WB_MODEL(m);
+    WB_NOT_RECORDING(m->ctx, "wb_qwen_last_logits");
     if (!out) return fail(WB_ERR_BAD_ARG, "out is NULL");
     WB_CUDA(cudaMemcpyAsync(out, m->dec.logits, (size_t)m->V * 4, cudaMemcpyDeviceToHost, m->ctx->stream));
     return wb_synchronize(m->ctx);

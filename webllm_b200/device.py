@@ -173,6 +173,48 @@ class Gpu:
                                            L.WB_F32 if C_full.dtype == "f32" else L.WB_F16, n_total, col_begin, arr,
                                            len(peer_bases)))
 
+    def linear_gather_barrier(self, weight: int, A: Tensor, C_full: Tensor, tmp: Tensor, bias: int | None, M: int,
+                              n_total: int, col_begin: int, peer_bases: list[int], flags: Tensor, rank: int,
+                              timeout_us: int = 0) -> None:
+        """``linear_gather`` followed by the library's own peer barrier (``wb_linear_gather_barrier``): when the
+        stream reaches the end of this call, every rank's columns are in this GPU's ``C_full``."""
+        arr = (C.c_void_p * max(1, len(peer_bases)))(*peer_bases)
+        L.check(self._lib.wb_linear_gather_barrier(self._ctx, weight, A.offset, C_full.offset, tmp.offset,
+                                                   -1 if bias is None else bias, M,
+                                                   L.WB_F32 if A.dtype == "f32" else L.WB_F16,
+                                                   L.WB_F32 if C_full.dtype == "f32" else L.WB_F16, n_total, col_begin,
+                                                   arr, len(peer_bases), flags.offset, rank, timeout_us))
+
+    def peer_barrier_init(self, flags: Tensor) -> None:
+        """Zeroes the barrier's flag words (``WB_PEER_FLAG_BYTES`` of the activation slab) and the epoch counter."""
+        L.check(self._lib.wb_peer_barrier_init(self._ctx, flags.offset))
+
+    def peer_barrier(self, flags: Tensor, rank: int, peer_bases: list[int], timeout_us: int = 0) -> None:
+        """Stream-ordered barrier across the ranks by the library's own kernel (``wb_peer_barrier``); a wait that
+        runs out surfaces as WB_ERR_TIMEOUT from the next ``synchronize``."""
+        arr = (C.c_void_p * max(1, len(peer_bases)))(*peer_bases)
+        L.check(self._lib.wb_peer_barrier(self._ctx, flags.offset, rank, arr, len(peer_bases), timeout_us))
+
+    # -- NCCL communicator behind the C ABI (loaded with dlopen on first use)
+    def comm_unique_id(self) -> bytes:
+        buf = C.create_string_buffer(L.WB_COMM_ID_BYTES)
+        L.check(self._lib.wb_comm_unique_id(buf))
+        return buf.raw
+
+    def comm_init(self, rank: int, nranks: int, unique_id: bytes, timeout_ms: int = 0) -> None:
+        L.check(self._lib.wb_comm_init(self._ctx, rank, nranks, C.c_char_p(unique_id), timeout_ms))
+
+    def comm_destroy(self) -> None:
+        L.check(self._lib.wb_comm_destroy(self._ctx))
+
+    def linear_colshard(self, weight: int, A: Tensor, C_full: Tensor, scratch: Tensor, bias: int | None, M: int,
+                        row_major: bool = True) -> None:
+        """Local product of this rank's columns + NCCL all-gather of the pieces (``wb_linear_colshard``)."""
+        L.check(self._lib.wb_linear_colshard(self._ctx, weight, A.offset, C_full.offset, scratch.offset,
+                                             -1 if bias is None else bias, M,
+                                             L.WB_F32 if A.dtype == "f32" else L.WB_F16,
+                                             L.WB_F32 if C_full.dtype == "f32" else L.WB_F16, 1 if row_major else 0))
+
     def ipc_export(self, arena: int = L.WB_ARENA_ACT) -> bytes:
         """Handle of a slab of this context for another process on the same node (``wb_arena_ipc_export``)."""
         buf = C.create_string_buffer(L.WB_IPC_HANDLE_BYTES)

@@ -7,8 +7,10 @@ the CPU tests). The reference has a single device (src/gpu/device.ts:40-98); bot
   ``qweight[:, cols]``, ``scales[:, cols]``, ``qzeros[:, cols/8]``), the activation is replicated, and one
   all-gather reassembles ``y``. Shard width must be a multiple of 8 so that no qzeros word is split.
 
-torch is plumbing here: it owns the activation slab that the context adopts (``wb_arena_adopt``), so that NCCL
-can run on arena tensors in place, and it provides the process group.
+The exchange itself sits behind the C ABI: ``wb_comm_init`` + ``wb_linear_colshard`` (an NCCL all-gather that the
+library enqueues on its own stream) or ``wb_linear_gather_barrier`` (the product's own stores into the peers' slabs
+plus the library's barrier kernel). torch is plumbing here: it provides the process group over which the ranks
+exchange the communicator id and the IPC handles, and the CPU (gloo) tests of the reassembly.
 """
 from __future__ import annotations
 
@@ -65,60 +67,52 @@ def gather_columns(y_local, M: int, group=None):
     return out.permute(1, 0, 2).reshape(M, -1).contiguous()
 
 
-class TorchSlabGpu:
-    """A ``Gpu`` whose activation slab is a torch tensor, so that collectives can run on arena tensors
-    without a copy, and whose kernels are enqueued on torch's current stream."""
+class ShardGroup:
+    """One rank of a column-sharded group: a ``Gpu`` whose activation slab every other rank has mapped (CUDA IPC, one
+    node) and, on request, an NCCL communicator owned by the library (``wb_comm_init``).
 
-    def __init__(self, device: int, weight_bytes: int, act_bytes: int):
-        import torch
+    Tensors are ``(slab, byte offset)`` on every rank: the ranks must make the same sequence of arena allocations, so
+    that one offset names the same tensor everywhere. The slab is made ``WB_PEER_FLAG_BYTES`` larger than asked: those
+    last bytes are the flag words of the library's peer barrier (keep arena allocations within ``act_bytes``). Kernels go to torch's current stream so that CUDA events recorded there time them."""
 
-        from .device import Gpu
-        self.torch = torch
-        self.device = torch.device(f"cuda:{device}")
-        torch.cuda.set_device(self.device)
-        self.slab = torch.empty(act_bytes, dtype=torch.uint8, device=self.device)
-        self.gpu = Gpu(device, weight_bytes=weight_bytes, act_slab=(self.slab.data_ptr(), act_bytes))
-        self.gpu.set_stream(torch.cuda.current_stream(self.device).cuda_stream)
-
-    def view(self, t, dtype=None):
-        """torch view of an arena tensor."""
-        torch = self.torch
-        dtype = dtype or (torch.float32 if t.dtype == "f32" else torch.float16)
-        return self.slab[t.offset:t.offset + t.nbytes].view(dtype)
-
-    def close(self):
-        self.gpu.close()
-
-
-class PeerSlabGpu:
-    """A ``Gpu`` whose activation slab the library allocated itself and that has every other rank's activation slab
-    mapped (CUDA IPC, one node), so that ``ColumnShardedLinear.forward_fused`` can store results straight into the
-    peers. Tensors are ``(slab, byte offset)`` on every rank: the ranks must make the same sequence of arena
-    allocations, so that one offset names the same tensor everywhere. Kernels go to torch's current stream, which
-    is also where the barrier's collective is enqueued."""
-
-    def __init__(self, device: int, weight_bytes: int, act_bytes: int, group=None):
+    def __init__(self, device: int, weight_bytes: int, act_bytes: int, group=None, nccl: bool = True, peers: bool = True,
+                 comm_timeout_ms: int = 0):
         import torch
         import torch.distributed as dist
 
+        from . import _lib as L
+        from .buffer import Tensor
         from .device import Gpu
         self.torch, self.group = torch, group
         self.device = torch.device(f"cuda:{device}")
         torch.cuda.set_device(self.device)
-        self.gpu = Gpu(device, weight_bytes=weight_bytes, act_bytes=act_bytes)
+        act_bytes = (act_bytes + 255) // 256 * 256
+        self.gpu = Gpu(device, weight_bytes=weight_bytes, act_bytes=act_bytes + L.WB_PEER_FLAG_BYTES)
         self.gpu.set_stream(torch.cuda.current_stream(self.device).cuda_stream)
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
-        handles = [None] * self.world
-        dist.all_gather_object(handles, self.gpu.ipc_export(), group=group)
-        self.peer_bases = [self.gpu.peer_open(h) for r, h in enumerate(handles) if r != self.rank]
-        self._flag = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.peer_bases: list[int] = []
+        self.flags = Tensor(act_bytes, L.WB_PEER_FLAG_BYTES // 4, [L.WB_PEER_FLAG_BYTES // 4], "f32")
+        self.has_comm = False
+        if peers:
+            handles = [None] * self.world
+            dist.all_gather_object(handles, self.gpu.ipc_export(), group=group)
+            self.peer_bases = [self.gpu.peer_open(h) for r, h in enumerate(handles) if r != self.rank]
+            self.gpu.peer_barrier_init(self.flags)
+            dist.barrier(group=group)  # every rank's flags are zero before any peer stores into them
+        if nccl:
+            box = [self.gpu.comm_unique_id() if self.rank == 0 else None]
+            dist.broadcast_object_list(box, src=0, group=group)
+            self.gpu.comm_init(self.rank, self.world, box[0], comm_timeout_ms)
+            self.has_comm = True
 
-    def barrier(self) -> None:
-        """Stream-ordered barrier across the ranks: a one-element all-reduce behind the kernels already enqueued."""
-        import torch.distributed as dist
-        dist.all_reduce(self._flag, group=self.group)
+    def barrier(self, timeout_us: int = 0) -> None:
+        """Stream-ordered barrier across the ranks by the library's own kernel (bounded wait, see ``wb_peer_barrier``)."""
+        self.gpu.peer_barrier(self.flags, self.rank, self.peer_bases, timeout_us)
 
     def close(self) -> None:
+        if self.has_comm:
+            self.gpu.comm_destroy()
+            self.has_comm = False
         for b in self.peer_bases:
             self.gpu.peer_close(b)
         self.peer_bases = []
@@ -126,16 +120,12 @@ class PeerSlabGpu:
 
 
 class ColumnShardedLinear:
-    """One GPTQ linear split by output columns over the ranks of a process group.
+    """One GPTQ linear split by output columns over the ranks of a ``ShardGroup``: rank r registers columns
+    ``[r*N/G, (r+1)*N/G)`` and runs the library's kernels on its slice (GEMV for small M, tcgen05 GEMM for large M)."""
 
-    ``forward(x_tensor, M)`` runs the local ``[M, N/G]`` product with the library's kernels (GEMV for small M,
-    tcgen05 GEMM for large M) and all-gathers the pieces over NCCL/NVLink.
-    """
-
-    def __init__(self, host: TorchSlabGpu, name: str, t: GptqTensors, bias: np.ndarray | None = None, group=None):
-        import torch.distributed as dist
-        self.host, self.group = host, group
-        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+    def __init__(self, host: ShardGroup, name: str, t: GptqTensors, bias: np.ndarray | None = None):
+        self.host = host
+        self.rank, self.world = host.rank, host.world
         self.N, self.K = t.out_features, t.in_features
         self.shard = column_shard(self.N, self.rank, self.world)
         gpu = host.gpu
@@ -145,19 +135,25 @@ class ColumnShardedLinear:
         if bias is not None:
             self.bias = gpu.f32_upload(name + ".bias", bias[self.shard.begin:self.shard.begin + self.shard.count])
 
+    def scratch_elems(self, M: int, row_major: bool = True) -> int:
+        """Elements of the scratch tensor ``forward`` needs (the local piece, plus the gathered pieces when they have
+        to be rearranged to row-major)."""
+        piece = M * self.shard.count
+        return (piece + 127) // 128 * 128 + (self.world * piece if row_major and M > 1 and self.world > 1 else 0)
+
     def local(self, A, C_local, M: int, exact: bool = False) -> None:
         self.host.gpu.linear(self.weight, A, C_local, self.bias, M, exact=exact)
 
-    def forward_fused(self, A, C_full, tmp, M: int) -> None:
-        """A: arena tensor [M, K] (replicated); C_full: arena tensor [M, N] at the same offset on every rank; tmp:
-        arena tensor [M, N/G] (used by decode-size calls only). ``host`` must be a ``PeerSlabGpu``. The kernel of
-        every rank stores its columns into all ranks' C_full; after the barrier every rank holds the full, row-major
-        [M, N]. The caller must not let any rank reuse C_full for another result before all ranks have read it."""
-        self.host.gpu.linear_gather(self.weight, A, C_full, tmp, self.bias, M, self.N, self.shard.begin,
-                                    self.host.peer_bases)
-        self.host.barrier()
+    def forward(self, A, C_full, scratch, M: int, row_major: bool = True) -> None:
+        """Local product + NCCL all-gather behind the C ABI (``wb_linear_colshard``). A: arena tensor [M, K]
+        (replicated); C_full: arena tensor that receives [M, N] row-major (or the rank-major pieces [G, M, N/G] with
+        ``row_major=False``); scratch: ``scratch_elems(M, row_major)`` elements of C_full's dtype."""
+        self.host.gpu.linear_colshard(self.weight, A, C_full, scratch, self.bias, M, row_major)
 
-    def forward(self, A, C_local, M: int, exact: bool = False):
-        """A: arena tensor [M, K] (replicated), C_local: arena tensor [M, N/G]. Returns a torch tensor [M, N]."""
-        self.local(A, C_local, M, exact)
-        return gather_columns(self.host.view(C_local), M, self.group)
+    def forward_fused(self, A, C_full, tmp, M: int, timeout_us: int = 0) -> None:
+        """The all-gather as the kernels' own stores: every rank's kernel stores its columns into all ranks' C_full
+        (same offset everywhere) and the library's barrier kernel follows, so that at this point of the stream every
+        rank holds the full, row-major [M, N]. tmp: arena tensor [M, N/G] (decode-size calls only). The caller must not
+        let any rank reuse C_full for another result before all ranks have read it (``host.barrier()``)."""
+        self.host.gpu.linear_gather_barrier(self.weight, A, C_full, tmp, self.bias, M, self.N, self.shard.begin,
+                                            self.host.peer_bases, self.host.flags, self.rank, timeout_us)

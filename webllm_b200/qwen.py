@@ -180,11 +180,6 @@ class QwenGpt:
         L.check(self._lib.wb_qwen_decode_greedy(self._ensure(), int(first_token), n_steps, out.ctypes.data_as(C.c_void_p)))
         return out
 
-    def set_decode_mode(self, mode: str) -> None:
-        """How ``decode_greedy`` runs a step: "auto", "graph" (one kernel per operation, replayed as a CUDA
-        graph) or "single" (one persistent kernel per step)."""
-        L.check(self._lib.wb_qwen_set_decode_mode(self._ensure(), {"auto": 0, "graph": 1, "single": 2}[mode]))
-
     def last_logits(self) -> np.ndarray:
         out = np.empty(self.config.vocab_size, np.float32)
         L.check(self._lib.wb_qwen_last_logits(self._ensure(), out.ctypes.data_as(C.c_void_p)))
