@@ -537,13 +537,27 @@ def column_shards(torch, dist, clock, rank: int, world: int, local: int, m_prefi
                     gpu.synchronize()
                     dist.barrier()
 
-                    reps = 5 if M > 1 else 3
-                    us_full = sclock.timed_ms(lambda: [gpu.linear(h, A, Cref, None, M) for h in fulls], reps, ranks=True) * 1e3 / full_copies
-                    us_local = sclock.timed_ms(lambda: [lin.local(A, Cl, M) for lin in lins], reps, ranks=True) * 1e3 / copies
-                    us_rank = sclock.timed_ms(lambda: [lin.forward(A, Cf, scratch, M, row_major=False) for lin in lins], reps, ranks=True) * 1e3 / copies
-                    us_row = (sclock.timed_ms(lambda: [lin.forward(A, Cf, scratch, M, row_major=True) for lin in lins], reps, ranks=True) * 1e3 / copies
+                    # kernels of this library are timed as replayed command batches (the host's launch rate is not what
+                    # is measured); the NCCL variant is enqueued call by call
+                    def batched(calls):
+                        with gpu.batch() as b:
+                            for c in calls:
+                                c()
+                        return b
+
+                    reps = 5 if M > 1 else 10
+                    b_full = batched([lambda h=h: gpu.linear(h, A, Cref, None, M) for h in fulls])
+                    b_local = batched([lambda lin=lin: lin.local(A, Cl, M) for lin in lins])
+                    b_st = batched([lambda lin=lin: lin.forward_fused(A, Cf, Cl, M) for lin in lins])
+                    us_full = sclock.timed_ms(b_full.submit, reps, ranks=True) * 1e3 / full_copies
+                    us_local = sclock.timed_ms(b_local.submit, reps, ranks=True) * 1e3 / copies
+                    us_st = sclock.timed_ms(b_st.submit, reps, ranks=True) * 1e3 / copies
+                    for b in (b_full, b_local, b_st):
+                        b.destroy()
+                    nreps = 5 if M > 1 else 3
+                    us_rank = sclock.timed_ms(lambda: [lin.forward(A, Cf, scratch, M, row_major=False) for lin in lins], nreps, ranks=True) * 1e3 / copies
+                    us_row = (sclock.timed_ms(lambda: [lin.forward(A, Cf, scratch, M, row_major=True) for lin in lins], nreps, ranks=True) * 1e3 / copies
                               if M > 1 else us_rank)
-                    us_st = sclock.timed_ms(lambda: [lin.forward_fused(A, Cf, Cl, M) for lin in lins], reps, ranks=True) * 1e3 / copies
                     gpu.synchronize()
                     dist.barrier()
                     for _ in range(full_copies + copies):
@@ -562,6 +576,9 @@ def column_shards(torch, dist, clock, rank: int, world: int, local: int, m_prefi
 # ---------------------------------------------------------------------------------------------------- our arm
 def run_ours(args) -> None:
     rank, world, local = dist_env()
+    # libraries (NCCL's version banner) may write to stdout: everything but the JSON line goes to stderr
+    json_out = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
     import torch
     import torch.distributed as dist
     torch.cuda.set_device(local)
@@ -668,7 +685,8 @@ def run_ours(args) -> None:
             line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
             line["cpu_baseline"]["decode_tokens_per_s_1_thread"] = one["value"]
             line["cpu_baseline"]["per_op"] = cpu_per_op(oracle.max_threads())
-        print(json.dumps(line), flush=True)
+        json_out.write(json.dumps(line) + "\n")
+        json_out.flush()
 
 
 # ---------------------------------------------------------------------------------------------------- profiler cases

@@ -168,7 +168,7 @@ WB_API int wb_linear(wb_context *ctx, wb_handle weight, uint64_t a_offset, uint6
  *      [M, N], and one small launch spreads it). The call is stream-ordered like wb_linear and does NOT wait for
  *      the peers: before any rank reads its full tensor, every rank's call must have completed (a barrier across
  *      the ranks after the call: wb_peer_barrier below, or any collective on the same streams), and no rank may still
- *      be reading the tensor when the next call writes it. Cannot be recorded into a command batch.
+ *      be reading the tensor when the next call writes it.
  *      wb_arena_ipc_export writes WB_IPC_HANDLE_BYTES bytes that another process on the same node passes to
  *      wb_peer_open to map this context's slab (only a slab made by wb_arena_create); wb_peer_close unmaps it. */
 #define WB_IPC_HANDLE_BYTES 64
@@ -180,13 +180,14 @@ WB_API int wb_peer_open(wb_context *ctx, const void *handle, void **base_out);
 WB_API int wb_peer_close(wb_context *ctx, void *base);
 /* The barrier that wb_linear_gather needs, done by a kernel of this library instead of a collective (no counterpart in
  * the reference). `flags_offset` names WB_PEER_FLAG_BYTES bytes of the activation slab, the same offset on every rank;
- * `rank` is this process's index among the n_peers + 1 ranks. wb_peer_barrier_init zeroes the flags and the context's
- * epoch counter: every rank calls it once, and the ranks must meet on the host (any host-side barrier) between the
- * last init and the first wb_peer_barrier. wb_peer_barrier is stream-ordered: the kernel stores an increasing epoch word
+ * `rank` is this process's index among the n_peers + 1 ranks. wb_peer_barrier_init zeroes the flags and the epoch
+ * counter kept beside them on the device: every rank calls it once, and the ranks must meet on the host (any host-side
+ * barrier) between the last init and the first wb_peer_barrier. wb_peer_barrier is stream-ordered: the kernel stores an increasing epoch word
  * into slot `rank` of every peer's flags (behind a system-scope fence, so everything this stream stored into the peers
  * before it is visible first) and waits until every other slot of its own flags has reached the epoch. The wait is
  * bounded: after timeout_us (0 = 2 s) the kernel records a code and returns, and the next wb_synchronize / wb_download
  * returns WB_ERR_TIMEOUT; nothing hangs when a peer never arrives. Every rank must issue the same sequence of barriers.
+ * Both calls may be recorded into a command batch (the epoch advances on the device with every replay).
  * wb_linear_gather_barrier is wb_linear_gather followed by that barrier; for decode-size calls the copy into the peers
  * and the barrier are one launch. */
 #define WB_PEER_FLAG_BYTES 256

@@ -12,9 +12,10 @@
 //     this file's barrier kernel replaces a collective as the "everyone has stored" signal. Each rank writes
 //     an increasing epoch word into slot `rank` of every peer's flag array (after a system-scope fence, so
 //     the data stores are visible first) and then polls its own array until every other slot has reached the
-//     epoch. The poll is bounded by wall time on the device: when it runs out the kernel writes a code to the
-//     context's status word and returns, and wb_synchronize reports WB_ERR_TIMEOUT. Plain peer stores and
-//     loads of this GPU's own memory only: no multimem, no multicast, no kernel reads a peer's memory.
+//     epoch. The epoch counter lives on the device, so the barrier can be recorded into a command batch. The
+//     poll is bounded by wall time on the device: when it runs out the kernel writes a code to the context's
+//     status word and returns, and wb_synchronize reports WB_ERR_TIMEOUT. Plain peer stores and loads of this
+//     GPU's own memory only: no multimem, no multicast, no kernel reads a peer's memory.
 #include <dlfcn.h>
 #include <nccl.h>
 
@@ -78,9 +79,11 @@ int nccl_settle(ncclComm_t comm, ncclResult_t r, int timeout_ms, const char *wha
 {
     const auto t0 = std::chrono::steady_clock::now();
     while (r == ncclInProgress) {
-        if (std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t0).count() > timeout_ms)
+        const auto waited = std::chrono::duration_cast<std::chrono::microseconds>(std::chrono::steady_clock::now() - t0).count();
+        if (waited > (long long)timeout_ms * 1000)
             return fail(WB_ERR_TIMEOUT, "%s did not complete within %d ms (a rank that never joined?)", what, timeout_ms);
-        std::this_thread::sleep_for(std::chrono::microseconds(200));
+        // an enqueue settles within microseconds: poll closely at first, back off for the long waits (creation)
+        if (waited > 200) std::this_thread::sleep_for(std::chrono::microseconds(waited > 20000 ? 500 : 20));
         ncclResult_t q = g_nccl.CommGetAsyncError(comm, &r);
         if (q != ncclSuccess) return nccl_fail(what, q);
     }
@@ -90,11 +93,15 @@ int nccl_settle(ncclComm_t comm, ncclResult_t r, int timeout_ms, const char *wha
 
 // ---- kernels ---------------------------------------------------------------------------------------------------
 
+// Layout of the WB_PEER_FLAG_BYTES flag area of a slab: word r (r < 8) is written by rank r's barrier kernel with
+// that rank's epoch; word 8 is this GPU's own epoch counter. The counter lives on the device and the kernel advances
+// it, so a recorded barrier (command batch, CUDA graph) takes a new epoch on every replay.
+constexpr int kEpochWord = 8;
+
 struct PeerSync {
-    unsigned *own_flags;                    // this GPU's flag array, one word per rank
-    unsigned *peer_flags[kMaxGatherDst];    // the same array in every peer slab
+    unsigned *own_flags;                    // this GPU's flag area
+    unsigned *peer_flags[kMaxGatherDst];    // the same area in every peer slab
     int n_peers, rank, nranks;
-    unsigned epoch;
     unsigned long long limit_ns;
     int *status;
 };
@@ -106,34 +113,45 @@ __device__ __forceinline__ unsigned long long global_ns()
     return t;
 }
 
-// Signal and wait; called by every thread of ONE CTA after a __syncthreads() that follows its stores and a
-// __threadfence_system(). Threads 0 .. n_peers - 1 publish the epoch, threads 0 .. nranks - 1 (but `rank`) wait.
+// Signal and wait; called by the first warp of ONE CTA after a __syncthreads() that follows the CTA's stores. Thread 0
+// alone issues the system-scope fence (the barrier before it orders the other threads' stores in front of the fence,
+// and one fence is far cheaper than one per thread) and then publishes the epoch; threads 0 .. nranks - 1 (but
+// `rank`) wait. What the peers stored into this GPU's memory before their flag is seen by the kernels that follow
+// in the stream (kernel boundary), so the waiting side needs no fence of its own.
 __device__ __forceinline__ void peer_signal_and_wait(const PeerSync &ps)
 {
     const int t = threadIdx.x;
-    if (t < ps.n_peers) {
+    // every rank issues the same sequence of barriers, so the local counters agree on the epoch
+    const unsigned epoch = ps.own_flags[kEpochWord] + 1u;
+    __syncwarp();
+    if (t == 0) {
+        ps.own_flags[kEpochWord] = epoch;
         __threadfence_system();
-        *(volatile unsigned *)(ps.peer_flags[t] + ps.rank) = ps.epoch;
+#pragma unroll
+        for (int g = 0; g < kMaxGatherDst - 1; g++)
+            if (g < ps.n_peers) *(volatile unsigned *)(ps.peer_flags[g] + ps.rank) = epoch;
     }
     if (t < ps.nranks && t != ps.rank) {
         const unsigned long long t0 = global_ns();
         const volatile unsigned *flag = ps.own_flags + t;
         bool ok = false;
         for (unsigned it = 0; it < (1u << 28); it++) {
-            if ((int)(*flag - ps.epoch) >= 0) {
+            if ((int)(*flag - epoch) >= 0) {
                 ok = true;
                 break;
             }
-            __nanosleep(64);
+            __nanosleep(32);
             if ((it & 15u) == 15u && global_ns() - t0 > ps.limit_ns) break;
         }
         if (!ok) *(volatile int *)ps.status = 7;  // the peer barrier gave up
-        __threadfence_system();  // acquire side: what the peers stored before their flag is visible to later kernels
     }
 }
 
+// Both kernels are launched with programmatic stream serialization: their CTA becomes resident under the tail of the
+// kernel before them and waits there (pdl_sync) until that kernel has completed and its stores are visible.
 __global__ void __launch_bounds__(32) peer_barrier_kernel(const PeerSync ps)
 {
+    pdl_sync();
     peer_signal_and_wait(ps);
 }
 
@@ -142,6 +160,7 @@ __global__ void __launch_bounds__(32) peer_barrier_kernel(const PeerSync ps)
 __global__ void __launch_bounds__(1024) scatter_barrier_kernel(const void *__restrict__ src, const OutPlace pl, int64_t M, int N,
                                                                 int esz, const PeerSync ps)
 {
+    pdl_sync();
     const int row_bytes = N * esz;
     const bool vec = (row_bytes & 15) == 0 && ((pl.ld * esz) & 15) == 0 && ((pl.col0 * esz) & 15) == 0;
     if (vec) {
@@ -167,9 +186,8 @@ __global__ void __launch_bounds__(1024) scatter_barrier_kernel(const void *__res
             }
         }
     }
-    __threadfence_system();
     __syncthreads();
-    peer_signal_and_wait(ps);
+    if (threadIdx.x < 32) peer_signal_and_wait(ps);
 }
 
 // [G][M][Nl] (what an all-gather delivers) -> row-major [M][G * Nl], 16-byte pieces (Nl * esz % 16 == 0)
@@ -208,7 +226,6 @@ static int fill_sync(wb_context *ctx, uint64_t flags_offset, int rank, void *con
         ps->peer_flags[g] = (unsigned *)((char *)peer_bases[g] + flags_offset);
     }
     ps->n_peers = n_peers, ps->rank = rank, ps->nranks = n_peers + 1;
-    ps->epoch = ++ctx->peer_epoch;
     ps->limit_ns = (unsigned long long)(timeout_us ? timeout_us : 2000000u) * 1000ull;
     ps->status = ctx->status_word;
     return WB_OK;
@@ -220,9 +237,10 @@ int launch_scatter_barrier(wb_context *ctx, const void *src, int64_t M, int64_t 
 {
     PeerSync ps;
     WB_CHECK(fill_sync(ctx, flags_offset, rank, peer_bases, n_peers, timeout_us, &ps));
-    scatter_barrier_kernel<<<1, 1024, 0, ctx->stream>>>(src, ctx->place, M, (int)N, f16 ? 2 : 4, ps);
+    const cudaError_t e = launch_pdl(scatter_barrier_kernel, dim3(1), dim3(1024), 0, ctx->stream, src, ctx->place, M, (int)N,
+                                     f16 ? 2 : 4, ps);
     ctx->launches++;
-    WB_CUDA(cudaGetLastError());
+    WB_CUDA(e);
     return WB_OK;
 }
 
@@ -340,7 +358,6 @@ int wb_peer_barrier_init(wb_context *ctx, uint64_t flags_offset)
     WB_CHECK(check_range(ctx, WB_ARENA_ACT, flags_offset, WB_PEER_FLAG_BYTES, "peer barrier flags"));
     WB_CUDA(cudaMemsetAsync(arena_ptr(ctx, WB_ARENA_ACT, flags_offset), 0, WB_PEER_FLAG_BYTES, ctx->stream));
     WB_CUDA(cudaStreamSynchronize(ctx->stream));
-    ctx->peer_epoch = 0;
     return WB_OK;
 }
 
@@ -348,12 +365,11 @@ int wb_peer_barrier(wb_context *ctx, uint64_t flags_offset, int rank, void *cons
 {
     if (!ctx) return fail(WB_ERR_BAD_ARG, "context is NULL");
     WB_CUDA(cudaSetDevice(ctx->device));
-    if (ctx->capturing) return fail(WB_ERR_BAD_ARG, "wb_peer_barrier cannot be recorded into a command batch");
     PeerSync ps;
     WB_CHECK(fill_sync(ctx, flags_offset, rank, peer_bases, n_peers, timeout_us, &ps));
-    peer_barrier_kernel<<<1, 32, 0, ctx->stream>>>(ps);
+    const cudaError_t e = launch_pdl(peer_barrier_kernel, dim3(1), dim3(32), 0, ctx->stream, ps);
     ctx->launches++;
-    WB_CUDA(cudaGetLastError());
+    WB_CUDA(e);
     return WB_OK;
 }
 

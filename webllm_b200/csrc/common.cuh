@@ -109,7 +109,6 @@ struct wb_context {
     uint64_t launches_at_capture = 0;
     void *nccl_comm = nullptr;       // ncclComm_t of the column-sharded group (comm.cu); nullptr until wb_comm_init
     int comm_rank = 0, comm_size = 1;
-    unsigned peer_epoch = 0;         // barriers issued by wb_peer_barrier since wb_peer_barrier_init
 };
 
 namespace wb {

@@ -624,7 +624,6 @@ static int linear_gather_impl(wb_context *ctx, wb_handle weight, uint64_t a_offs
     WB_CTX(ctx);
     Weight *w;
     WB_CHECK(linear_args(ctx, weight, M, act_dtype, out_dtype, &w));
-    if (ctx->capturing) return fail(WB_ERR_BAD_ARG, "wb_linear_gather cannot be recorded into a command batch");
     if (n_peers < 0 || n_peers > kMaxGatherDst - 1 || (n_peers > 0 && !peer_bases))
         return fail(WB_ERR_BAD_ARG, "wb_linear_gather: at most %d peers", kMaxGatherDst - 1);
     if (col_begin < 0 || n_total <= 0 || col_begin + w->N > n_total)

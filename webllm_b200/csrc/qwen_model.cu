@@ -154,9 +154,13 @@ int forward_impl(wb_qwen *m, const Bufs &b, int64_t M, int64_t B, int64_t T, int
             if (M == 1 && D % 8 == 0 && D <= 128 && op_attention_decode_smem(D, max_keys, kv16) <= 160 * 1024) {
                 WB_CHECK(op_attention_decode(ctx, b.q, kc, vc, kv16, b.att, m->att_scratch, m->att_counters, H, KVH, D, past_ptr,
                                              (int)past, max_keys, KV));
-            } else
-            WB_CHECK(op_attention(ctx, b.q, kc, vc, kv16, b.att, (int)M, H, KVH, D, (int)T, past_ptr, (int)past, 1, max_keys,
-                                  b.ldq, KV));
+            } else if (!m->exact && op_attention_prefill_supported((int)M, H, KVH, D, b.ldq, KV)) {
+                // prefill in the default mode: causal attention on the tensor cores (fp16 operands, like the linears)
+                WB_CHECK(op_attention_prefill(ctx, b.q, kc, vc, kv16, b.att, (int)M, H, KVH, D, past_ptr, (int)past, b.ldq, KV));
+            } else {
+                WB_CHECK(op_attention(ctx, b.q, kc, vc, kv16, b.att, (int)M, H, KVH, D, (int)T, past_ptr, (int)past, 1, max_keys,
+                                      b.ldq, KV));
+            }
         } else {
             WB_CHECK(op_attention(ctx, b.q, b.k, b.v, 0, b.att, (int)M, H, KVH, D, (int)T, nullptr, 0, 0, (int)T, b.ldq, b.ldk));
         }

@@ -16,6 +16,11 @@ int op_rope_kv(wb_context *ctx, float *q, float *k, const float *v, void *k_cach
                int ldk, int ldv);
 int op_attention(wb_context *ctx, const float *q, const void *kmem, const void *vmem, int kv_f16, float *out, int M, int H,
                  int KVH, int D, int T, const int *past_ptr, int past_imm, int use_cache, int max_keys, int ldq, int kv_ld);
+// The same for M >= 16 rows against the KV cache on the tensor cores (attention_prefill.cu): fp16 operands, f32 softmax
+// and accumulation; head size 64 or 128. Used by the default mode; the fp32-activation mode keeps op_attention.
+bool op_attention_prefill_supported(int M, int H, int KVH, int D, int ldq, int kv_ld);
+int op_attention_prefill(wb_context *ctx, const float *q, const void *kmem, const void *vmem, int kv_f16, float *out, int M, int H,
+                         int KVH, int D, const int *past_ptr, int past_imm, int ldq, int kv_ld);
 // One query row against the cache, keys split over several CTAs per head; scratch holds the per-slice
 // softmax state (op_attention_decode_scratch_floats floats), counters one zeroed word per head.
 // With k_raw / v_raw / cs_table set, q, k_raw and v_raw are the un-rotated projection outputs: the kernel applies the
