@@ -217,9 +217,9 @@ def test_full_size_decode_token_identical(built_lib, oracle):
 def test_tensor_core_prefill_attention_every_row(built_lib, oracle, kv, n_prompt):
     """Prefill in the default mode runs the causal attention on the tensor cores (head size 64): the logits of EVERY
     row against qwenForwardRef, so that a wrong mask or a key block skipped too early shows up on the row it hits;
-    token counts that end inside a 64-row block and cross several 64-key blocks; both cache types. The bar is the
-    reference's own for its fp16-operand paths (atol 2e-3 of the logits' rms, rtol 2e-2); the fp32-activation mode
-    on the same prompt keeps the scalar kernel and its tighter bar."""
+    token counts that end inside a 64-row block and cross several 64-key blocks; both cache types. The bar is that of
+    the default mode (fp16 operands in every linear and in the attention: 1e-2 of the logits' rms, rtol 2e-2, and no
+    row's rms error above 1e-2); the fp32-activation mode on the same prompt keeps the scalar kernel and its tighter bar."""
     G = synthetic.random_qwen_gptq(SMALL, seed=7, std=0.05)
     Wd = _dense_from_gptq(oracle, G)
     prompt = np.random.default_rng(n_prompt).integers(0, SMALL.vocab_size, n_prompt).astype(np.uint32)
@@ -229,10 +229,10 @@ def test_tensor_core_prefill_attention_every_row(built_lib, oracle, kv, n_prompt
         model = QwenGpt(gpu, SMALL, max_t=n_prompt, kv_dtype=kv)
         model.upload_gptq_model(G, fuse=True)
         got = model.read_tensor(model.prefill(prompt)).reshape(n_prompt, -1)
-        r = oracle.check_tolerance(got, ref, 2e-3 * rms, 2e-2)
-        assert r.ok, (kv, n_prompt, r)
-        worst_row = float(np.max(np.sqrt(np.mean((got - ref).astype(np.float64) ** 2, axis=1)))) / rms
-        assert worst_row < 5e-3, worst_row  # no single row stands out: the mask is per row
+        row_err = np.sqrt(np.mean((got - ref).astype(np.float64) ** 2, axis=1)) / rms
+        r = oracle.check_tolerance(got, ref, 1e-2 * rms, 2e-2)
+        assert r.ok, (kv, n_prompt, r, rms, float(row_err.max()), int(row_err.argmax()))
+        assert row_err.max() < 1e-2, (float(row_err.max()), int(row_err.argmax()))  # no single row stands out: the mask is per row
         if kv == "f32":  # (an fp16 cache rounds k and v, which the uncached reference forward does not)
             model.set_exact(True)
             model.reset_cache()
