@@ -30,6 +30,7 @@ serialise kernels); these are the commands the summaries under profiles/ were ca
                   separately registered copies of a synthetic weight, so consecutive launches read different memory
     --case gemm   --K 896 --N 9728 --M 2048 [--copies 2] [--reps 2]                     the same with fp16 activations
     --case decode [--layers 24] [--steps 3] [--prompt 64]                                the decode step of this bench
+    --case prefill [--layers 4] [--prompt 2048]                                          one prefill of that many tokens
     --case read   [--mb 35.27]                                                           a kernel that only reads (yardstick)
 """
 from __future__ import annotations
@@ -730,6 +731,22 @@ def run_case(args) -> None:
         print(f"{args.steps} steps, {dt * 1e3:.3f} ms per step by wall clock, tokens {toks[:4].tolist()}")
         model.close()
         gpu.close()
+    elif args.case == "prefill":
+        cfg = dataclasses.replace(synthetic.QWEN25_05B, n_layer=args.layers)
+        weights = synthetic.random_qwen_gptq(cfg, seed=0)
+        gpu = Gpu(0, weight_bytes=(1 << 30) + (512 << 20), act_bytes=1 << 30)
+        model = QwenGpt(gpu, cfg, max_t=args.prompt, kv_dtype="f16")
+        model.upload_gptq_model(weights, fuse=True)
+        prompt = np.random.default_rng(100).integers(0, cfg.vocab_size, args.prompt).astype(np.uint32)
+        for _ in range(2):
+            model.reset_cache()
+            gpu.synchronize()
+            t0 = time.perf_counter()
+            row = model.read_tensor(model.prefill(prompt, last_only=True))
+            dt = time.perf_counter() - t0
+        print(f"prefill of {args.prompt} tokens through {cfg.n_layer} layers: {dt * 1e3:.3f} ms by wall clock, argmax {int(row.argmax())}")
+        model.close()
+        gpu.close()
     elif args.case == "read":
         import torch
         nbytes = int(args.mb * 1e6) // 256 * 256
@@ -756,7 +773,7 @@ def main() -> None:
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg of the default arm")
     ap.add_argument("--no-extras", action="store_true", help="headline and roofline only")
-    ap.add_argument("--case", choices=("gemv", "gemm", "decode", "read"), help="run one small profiler workload instead")
+    ap.add_argument("--case", choices=("gemv", "gemm", "decode", "prefill", "read"), help="run one small profiler workload instead")
     ap.add_argument("--K", type=int, default=3584), ap.add_argument("--N", type=int, default=18944)
     ap.add_argument("--M", type=int, default=0), ap.add_argument("--copies", type=int, default=8)
     ap.add_argument("--act", choices=("f32", "f16"), default="f32"), ap.add_argument("--reps", type=int, default=2)
@@ -766,6 +783,10 @@ def main() -> None:
     if args.case:
         if args.case == "decode" and args.steps == 128:
             args.steps = 3
+        if args.case == "prefill" and args.layers == 24:
+            args.layers = 4
+        if args.case == "prefill" and args.prompt == 64:
+            args.prompt = 2048
         run_case(args)
     elif args.impl == "reference":
         run_reference(args)

@@ -63,9 +63,10 @@ __device__ __forceinline__ void stage_block(__half *dst, const KV *src, int key0
 
 template <typename KV, int D>
 __global__ void __launch_bounds__(128) attention_prefill_mma_kernel(const float *__restrict__ q, const KV *__restrict__ kmem,
-                                                                    const KV *__restrict__ vmem, float *__restrict__ out, int M,
-                                                                    int H, int KVH, const int *__restrict__ past_ptr,
-                                                                    int past_imm, int ldq, int kv_ld, float scale)
+                                                                    const KV *__restrict__ vmem, float *__restrict__ out,
+                                                                    __half *__restrict__ out16, int M, int H, int KVH,
+                                                                    const int *__restrict__ past_ptr, int past_imm, int ldq,
+                                                                    int kv_ld, float scale)
 {
     pdl_sync();
     constexpr int LD = D + 8;     // padded row of a staged block, in halves: rows 16 bytes apart modulo 128
@@ -200,24 +201,29 @@ __global__ void __launch_bounds__(128) attention_prefill_mma_kernel(const float 
         l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
     }
     const float inv_a = l_run[0] > 0.f ? 1.f / l_run[0] : 0.f, inv_b = l_run[1] > 0.f ? 1.f / l_run[1] : 0.f;
-    float *oa = out + (int64_t)row_a * (H * D) + h * D + 2 * t, *ob = out + (int64_t)row_b * (H * D) + h * D + 2 * t;
+    const int64_t ia = (int64_t)row_a * (H * D) + h * D + 2 * t, ib = (int64_t)row_b * (H * D) + h * D + 2 * t;
 #pragma unroll
     for (int j = 0; j < DT; j++) {
-        if (row_a < M) *reinterpret_cast<float2 *>(oa + j * 8) = make_float2(o[j][0] * inv_a, o[j][1] * inv_a);
-        if (row_b < M) *reinterpret_cast<float2 *>(ob + j * 8) = make_float2(o[j][2] * inv_b, o[j][3] * inv_b);
+        if (out16) {  // the o projection is a tensor-core GEMM: it takes the fp16 value it would round to itself
+            if (row_a < M) *reinterpret_cast<uint32_t *>(out16 + ia + j * 8) = pack_h2(o[j][0] * inv_a, o[j][1] * inv_a);
+            if (row_b < M) *reinterpret_cast<uint32_t *>(out16 + ib + j * 8) = pack_h2(o[j][2] * inv_b, o[j][3] * inv_b);
+        } else {
+            if (row_a < M) *reinterpret_cast<float2 *>(out + ia + j * 8) = make_float2(o[j][0] * inv_a, o[j][1] * inv_a);
+            if (row_b < M) *reinterpret_cast<float2 *>(out + ib + j * 8) = make_float2(o[j][2] * inv_b, o[j][3] * inv_b);
+        }
     }
 }
 
 template <typename KV, int D>
-cudaError_t launch_prefill(cudaStream_t st, const float *q, const void *kmem, const void *vmem, float *out, int M, int H, int KVH,
-                           const int *past_ptr, int past_imm, int ldq, int kv_ld)
+cudaError_t launch_prefill(cudaStream_t st, const float *q, const void *kmem, const void *vmem, float *out, __half *out16, int M, int H,
+                           int KVH, const int *past_ptr, int past_imm, int ldq, int kv_ld)
 {
     const size_t smem = (size_t)4 * kKeys * (D + 8) * sizeof(__half);
     auto kern = attention_prefill_mma_kernel<KV, D>;
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     const dim3 grid((unsigned)((M + kQRows - 1) / kQRows), (unsigned)H);
-    return launch_pdl(kern, grid, dim3(128), smem, st, q, (const KV *)kmem, (const KV *)vmem, out, M, H, KVH, past_ptr, past_imm, ldq,
-                      kv_ld, 1.0f / sqrtf((float)D));
+    return launch_pdl(kern, grid, dim3(128), smem, st, q, (const KV *)kmem, (const KV *)vmem, out, out16, M, H, KVH, past_ptr, past_imm,
+                      ldq, kv_ld, 1.0f / sqrtf((float)D));
 }
 
 }  // namespace
@@ -228,17 +234,17 @@ bool op_attention_prefill_supported(int M, int H, int KVH, int D, int ldq, int k
 }
 
 int op_attention_prefill(wb_context *ctx, const float *q, const void *kmem, const void *vmem, int kv_f16, float *out, int M, int H,
-                         int KVH, int D, const int *past_ptr, int past_imm, int ldq, int kv_ld)
+                         int KVH, int D, const int *past_ptr, int past_imm, int ldq, int kv_ld, __half *out16)
 {
     if (!op_attention_prefill_supported(M, H, KVH, D, ldq, kv_ld))
         return fail(WB_ERR_UNSUPPORTED, "tensor-core prefill attention needs M >= 16 and a head size of 64 or 128");
     cudaError_t e;
     if (D == 64)
-        e = kv_f16 ? launch_prefill<__half, 64>(ctx->stream, q, kmem, vmem, out, M, H, KVH, past_ptr, past_imm, ldq, kv_ld)
-                   : launch_prefill<float, 64>(ctx->stream, q, kmem, vmem, out, M, H, KVH, past_ptr, past_imm, ldq, kv_ld);
+        e = kv_f16 ? launch_prefill<__half, 64>(ctx->stream, q, kmem, vmem, out, out16, M, H, KVH, past_ptr, past_imm, ldq, kv_ld)
+                   : launch_prefill<float, 64>(ctx->stream, q, kmem, vmem, out, out16, M, H, KVH, past_ptr, past_imm, ldq, kv_ld);
     else
-        e = kv_f16 ? launch_prefill<__half, 128>(ctx->stream, q, kmem, vmem, out, M, H, KVH, past_ptr, past_imm, ldq, kv_ld)
-                   : launch_prefill<float, 128>(ctx->stream, q, kmem, vmem, out, M, H, KVH, past_ptr, past_imm, ldq, kv_ld);
+        e = kv_f16 ? launch_prefill<__half, 128>(ctx->stream, q, kmem, vmem, out, out16, M, H, KVH, past_ptr, past_imm, ldq, kv_ld)
+                   : launch_prefill<float, 128>(ctx->stream, q, kmem, vmem, out, out16, M, H, KVH, past_ptr, past_imm, ldq, kv_ld);
     ctx->launches++;
     WB_CUDA(e);
     return WB_OK;

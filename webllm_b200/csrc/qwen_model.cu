@@ -3,6 +3,7 @@
 // them and q/k/v (gate/up) may run as one fused projection.
 #include <math.h>
 
+#include <algorithm>
 #include <memory>
 
 #include "qwen_internal.cuh"
@@ -74,6 +75,8 @@ int alloc_bufs(wb_qwen *m, int arena, int64_t M, int64_t logit_rows, Bufs *b)
     WB_CHECK(carve_t(ctx, arena, M * 2 * I, &b->gu));
     b->ld_gu = fused_gu ? 2 * I : I;
     WB_CHECK(carve_t(ctx, arena, M * I, &b->act));
+    b->h16 = nullptr;
+    if (M > 16) WB_CHECK(carve_t(ctx, arena, M * (int64_t)std::max(C, I), &b->h16));
     WB_CHECK(carve_t(ctx, arena, logit_rows * m->V, &b->logits));
     return WB_OK;
 }
@@ -88,6 +91,16 @@ int linear(wb_qwen *m, int wh, const float *A, float *Cout, int bias, int64_t M,
     const Weight &w = ctx->weights[wh];
     const float *bp = bias >= 0 ? (const float *)(ctx->arena[WB_ARENA_WEIGHTS].base + ctx->weights[bias].off_main) : nullptr;
     return launch_linear(ctx, w, A, Cout, bp, M, WB_F32, WB_F32, m->exact, fusion);
+}
+
+// The same with the activation already in fp16 (written so by the step before it: see `half_in` in forward_impl).
+int linear_h16(wb_qwen *m, int wh, const __half *A, float *Cout, int bias, int64_t M)
+{
+    wb_context *ctx = m->ctx;
+    ctx->prefetch_weight = -1;
+    const Weight &w = ctx->weights[wh];
+    const float *bp = bias >= 0 ? (const float *)(ctx->arena[WB_ARENA_WEIGHTS].base + ctx->weights[bias].off_main) : nullptr;
+    return launch_linear(ctx, w, A, Cout, bp, M, WB_F16, WB_F32, 0, nullptr);
 }
 
 // One forward pass over rows [0, M). past_ptr != nullptr: positions come from device memory (graph replay).
@@ -137,11 +150,16 @@ int forward_impl(wb_qwen *m, const Bufs &b, int64_t M, int64_t B, int64_t T, int
             continue;
         }
         // --- attention sub-layer
+        // Default mode at prefill sizes: every projection runs on the tensor cores and would round its f32 input to
+        // fp16 first; the step that produces that input writes the fp16 value itself (same numbers, one pass over
+        // the activations fewer per projection). Only where the fused projections exist (one consumer per producer).
+        const bool half_in = !m->exact && b.h16 != nullptr && L.qkv >= 0 && L.gate_up >= 0;
         float *x_in = (delta ? (x == b.x ? b.xa : b.x) : x);
-        WB_CHECK(op_rmsnorm(ctx, x, delta, x_in, f32w(L.in_norm), b.n, (int)M, C, m->cfg.rms_eps));
+        WB_CHECK(op_rmsnorm(ctx, x, delta, x_in, f32w(L.in_norm), b.n, (int)M, C, m->cfg.rms_eps, half_in ? b.h16 : nullptr));
         x = x_in;
         if (L.qkv >= 0) {
-            WB_CHECK(linear(m, L.qkv, b.n, b.q, L.qkvb, M, L.o));
+            if (half_in) WB_CHECK(linear_h16(m, L.qkv, b.h16, b.q, L.qkvb, M));
+            else WB_CHECK(linear(m, L.qkv, b.n, b.q, L.qkvb, M, L.o));
         } else {
             WB_CHECK(linear(m, L.q, b.n, b.q, L.qb, M));
             WB_CHECK(linear(m, L.k, b.n, b.k, L.kb, M));
@@ -149,6 +167,7 @@ int forward_impl(wb_qwen *m, const Bufs &b, int64_t M, int64_t B, int64_t T, int
         }
         WB_CHECK(op_rope_kv(ctx, b.q, b.k, b.v, kc, vc, kv16, m->cs_table, (int)M, H, KVH, D, (int)T, past_ptr, (int)past,
                             b.ldq, b.ldk, b.ldv));
+        bool att_half = false;
         if (use_cache) {
             const int max_keys = past_ptr ? m->cfg.max_t : (int)(past + M);
             if (M == 1 && D % 8 == 0 && D <= 128 && op_attention_decode_smem(D, max_keys, kv16) <= 160 * 1024) {
@@ -156,7 +175,9 @@ int forward_impl(wb_qwen *m, const Bufs &b, int64_t M, int64_t B, int64_t T, int
                                              (int)past, max_keys, KV));
             } else if (!m->exact && op_attention_prefill_supported((int)M, H, KVH, D, b.ldq, KV)) {
                 // prefill in the default mode: causal attention on the tensor cores (fp16 operands, like the linears)
-                WB_CHECK(op_attention_prefill(ctx, b.q, kc, vc, kv16, b.att, (int)M, H, KVH, D, past_ptr, (int)past, b.ldq, KV));
+                att_half = half_in;
+                WB_CHECK(op_attention_prefill(ctx, b.q, kc, vc, kv16, b.att, (int)M, H, KVH, D, past_ptr, (int)past, b.ldq, KV,
+                                              att_half ? b.h16 : nullptr));
             } else {
                 WB_CHECK(op_attention(ctx, b.q, kc, vc, kv16, b.att, (int)M, H, KVH, D, (int)T, past_ptr, (int)past, 1, max_keys,
                                       b.ldq, KV));
@@ -164,20 +185,23 @@ int forward_impl(wb_qwen *m, const Bufs &b, int64_t M, int64_t B, int64_t T, int
         } else {
             WB_CHECK(op_attention(ctx, b.q, b.k, b.v, 0, b.att, (int)M, H, KVH, D, (int)T, nullptr, 0, 0, (int)T, b.ldq, b.ldk));
         }
-        WB_CHECK(linear(m, L.o, b.att, b.proj, -1, M, L.gate_up));
+        if (att_half) WB_CHECK(linear_h16(m, L.o, b.h16, b.proj, -1, M));
+        else WB_CHECK(linear(m, L.o, b.att, b.proj, -1, M, L.gate_up));
         // --- MLP sub-layer: xa = x + proj; n = rmsnorm(xa)
         float *xa = (x == b.x ? b.xa : b.x);
-        WB_CHECK(op_rmsnorm(ctx, x, b.proj, xa, f32w(L.post_norm), b.n, (int)M, C, m->cfg.rms_eps));
+        WB_CHECK(op_rmsnorm(ctx, x, b.proj, xa, f32w(L.post_norm), b.n, (int)M, C, m->cfg.rms_eps, half_in ? b.h16 : nullptr));
         x = xa;
         if (L.gate_up >= 0) {
-            WB_CHECK(linear(m, L.gate_up, b.n, b.gu, -1, M, L.down));
-            WB_CHECK(op_silu_mul(ctx, b.gu, b.gu + I, b.act, (int)M, I, 2 * I));
+            if (half_in) WB_CHECK(linear_h16(m, L.gate_up, b.h16, b.gu, -1, M));
+            else WB_CHECK(linear(m, L.gate_up, b.n, b.gu, -1, M, L.down));
+            WB_CHECK(op_silu_mul(ctx, b.gu, b.gu + I, b.act, (int)M, I, 2 * I, half_in ? b.h16 : nullptr));
         } else {
             WB_CHECK(linear(m, L.gate, b.n, b.gu, -1, M));
             WB_CHECK(linear(m, L.up, b.n, b.gu + M * I, -1, M));
             WB_CHECK(op_silu_mul(ctx, b.gu, b.gu + M * I, b.act, (int)M, I, I));
         }
-        WB_CHECK(linear(m, L.down, b.act, b.proj, -1, M, i + 1 < m->cfg.n_layer ? m->layers[i + 1].qkv : -1));
+        if (half_in) WB_CHECK(linear_h16(m, L.down, b.h16, b.proj, -1, M));
+        else WB_CHECK(linear(m, L.down, b.act, b.proj, -1, M, i + 1 < m->cfg.n_layer ? m->layers[i + 1].qkv : -1));
         delta = b.proj;
     }
     // final norm (+ the last residual add), then the tied lm_head

@@ -34,9 +34,11 @@ __device__ __forceinline__ float block_sum(float v, float *red)
 
 // rmsnorm.wgsl / rmsNormRef (src/reference/qwen-ref.ts:12-29): y = x / sqrt(mean(x^2) + eps) * w,
 // optionally fused with the residual add that precedes it: x_out = x + delta (vec_add.wgsl).
+// y16 != nullptr: the result is stored as fp16 instead (the next step is a tensor-core GEMM, which would round its
+// f32 input to fp16 anyway: same values, one pass over the activations fewer).
 __global__ void __launch_bounds__(256) rmsnorm_kernel(const float *__restrict__ x, const float *__restrict__ delta,
                                                       float *__restrict__ x_out, const float *__restrict__ w,
-                                                      float *__restrict__ y, int D, float eps)
+                                                      float *__restrict__ y, __half *__restrict__ y16, int D, float eps)
 {
     pdl_sync();
     __shared__ float red[8];
@@ -53,7 +55,9 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const float *__restrict__ 
     const float rstd = rsqrtf(block_sum(ss, red) / (float)D + eps);
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
         const float v = delta ? x_out[base + d] : x[base + d];
-        y[base + d] = v * rstd * w[d];
+        const float r = v * rstd * w[d];
+        if (y16) y16[base + d] = __float2half_rn(r);
+        else y[base + d] = r;
     }
 }
 
@@ -76,6 +80,31 @@ __global__ void silu_mul_kernel(const float *__restrict__ gate, const float *__r
     const int m = (int)(idx / I), i = (int)(idx - (int64_t)m * I);
     const float g = gate[(int64_t)m * ld + i], u = up[(int64_t)m * ld + i];
     out[idx] = g / (1.f + expf(-g)) * u;
+}
+
+// The same, four values per thread (I and ld multiples of 4), result in f32 or, with out16, in fp16 for the tensor-core
+// GEMM that follows (which would round the f32 value to fp16 itself: same values).
+__global__ void __launch_bounds__(256) silu_mul_vec4_kernel(const float *__restrict__ gate, const float *__restrict__ up,
+                                                            float *__restrict__ out, __half *__restrict__ out16, int M, int I, int ld)
+{
+    pdl_sync();
+    const int q = I >> 2;
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (int64_t)M * q) return;
+    const int m = (int)(idx / q), i = (int)(idx - (int64_t)m * q) * 4;
+    const float4 g = *reinterpret_cast<const float4 *>(gate + (int64_t)m * ld + i);
+    const float4 u = *reinterpret_cast<const float4 *>(up + (int64_t)m * ld + i);
+    float4 r;
+    r.x = g.x / (1.f + expf(-g.x)) * u.x, r.y = g.y / (1.f + expf(-g.y)) * u.y;
+    r.z = g.z / (1.f + expf(-g.z)) * u.z, r.w = g.w / (1.f + expf(-g.w)) * u.w;
+    if (out16) {
+        const __half2 a = __floats2half2_rn(r.x, r.y), b = __floats2half2_rn(r.z, r.w);
+        uint2 o;
+        o.x = *reinterpret_cast<const uint32_t *>(&a), o.y = *reinterpret_cast<const uint32_t *>(&b);
+        *reinterpret_cast<uint2 *>(out16 + (int64_t)m * I + i) = o;
+    } else {
+        *reinterpret_cast<float4 *>(out + (int64_t)m * I + i) = r;
+    }
 }
 
 // rope_half.wgsl + kv_store.wgsl (ropeHalfRef, src/reference/qwen-ref.ts:35-64): HF rotate-half with
@@ -498,9 +527,10 @@ int op_embed(wb_context *ctx, const __half *table, const uint32_t *tokens, float
     LAUNCH_OK(ctx);
 }
 
-int op_rmsnorm(wb_context *ctx, const float *x, const float *delta, float *x_out, const float *w, float *y, int M, int D, float eps)
+int op_rmsnorm(wb_context *ctx, const float *x, const float *delta, float *x_out, const float *w, float *y, int M, int D, float eps,
+               __half *y16)
 {
-    WB_CUDA(launch_pdl(rmsnorm_kernel, dim3(M), dim3(256), 0, ctx->stream, x, delta, x_out, w, y, D, eps));
+    WB_CUDA(launch_pdl(rmsnorm_kernel, dim3(M), dim3(256), 0, ctx->stream, x, delta, x_out, w, y, y16, D, eps));
     LAUNCH_OK(ctx);
 }
 
@@ -510,10 +540,15 @@ int op_add(wb_context *ctx, const float *a, const float *b, float *out, int64_t 
     LAUNCH_OK(ctx);
 }
 
-int op_silu_mul(wb_context *ctx, const float *gate, const float *up, float *out, int M, int I, int ld)
+int op_silu_mul(wb_context *ctx, const float *gate, const float *up, float *out, int M, int I, int ld, __half *out16)
 {
     const int64_t n = (int64_t)M * I;
-    WB_CUDA(launch_pdl(silu_mul_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, ctx->stream, gate, up, out, M, I, ld));
+    if (I % 4 == 0 && ld % 4 == 0 && ((uintptr_t)gate % 16) == 0 && ((uintptr_t)up % 16) == 0) {
+        WB_CUDA(launch_pdl(silu_mul_vec4_kernel, dim3((unsigned)((n / 4 + 255) / 256)), dim3(256), 0, ctx->stream, gate, up, out, out16, M, I, ld));
+    } else {
+        if (out16) return fail(WB_ERR_UNSUPPORTED, "fp16 silu output needs I %% 4 == 0");
+        WB_CUDA(launch_pdl(silu_mul_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, ctx->stream, gate, up, out, M, I, ld));
+    }
     LAUNCH_OK(ctx);
 }
 
