@@ -112,7 +112,7 @@ def test_f16_upload_matches_reference_conversion(gpu, oracle, golden):
 
 
 def test_read_sweep_diagnostic_runs_and_checks_its_range(gpu):
-    """wb_read_sweep (the bandwidth yardstick of `probe read`) launches one kernel over a slab range and refuses
+    """wb_read_sweep (the bandwidth yardstick of `bench.py --case read`) launches one kernel over a slab range and refuses
     ranges outside the slab or not in 16-byte units; it never writes, so the slab is unchanged afterwards."""
     from webllm_b200 import _lib
     data = np.arange(1 << 16, dtype=np.float32)
