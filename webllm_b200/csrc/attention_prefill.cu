@@ -33,24 +33,41 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void *
                  : "r"((uint32_t)__cvta_generic_to_shared(smem_row)));
 }
 
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void *smem_row)
+{
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"((uint32_t)__cvta_generic_to_shared(smem_row)));
+}
+
 __device__ __forceinline__ uint32_t pack_h2(float a, float b) { return h2_as_u32(__floats2half2_rn(a, b)); }
 
-// Stages keys [key0, key0 + 64) of one KV head into `dst` ([64][D + 8] halves); rows at or past n_keys become zeros.
-template <typename KV, int D>
-__device__ __forceinline__ void stage_block(__half *dst, const KV *src, int key0, int n_keys, int kv_ld, int tid)
+// 2^x by the special-function unit (the softmax only needs a few ulp: its weights are rounded to fp16 next)
+__device__ __forceinline__ float ex2(float x)
 {
-    constexpr int LD = D + 8;
-    constexpr int PER_ROW = D / 8;  // 16-byte pieces of fp16 per row
-    for (int i = tid; i < kKeys * PER_ROW; i += 128) {
-        const int r = i / PER_ROW, c = (i - r * PER_ROW) * 8;
-        __half *d = dst + r * LD + c;
-        const int key = key0 + r;
-        if (key < n_keys) {
-            const KV *s = src + (int64_t)key * kv_ld + c;
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// Stages keys [key0, key0 + 64) of one KV head into `dst` ([64][D + 8] halves); rows at or past n_keys become zeros.
+// A thread copies the same pieces of every block (piece u: row (tid + 128 u) / (D / 8), 16 bytes), so the offsets are
+// computed once by the caller: dst_off[u] in halves, src_off[u] in elements of the cache row.
+template <typename KV, int D>
+__device__ __forceinline__ void stage_block(__half *dst, const KV *src, int key0, int n_keys, int kv_ld, const int (&dst_off)[D / 16],
+                                            const int (&src_off)[D / 16], const int (&row)[D / 16])
+{
+    const KV *base = src + (int64_t)key0 * kv_ld;
+    const bool whole = key0 + kKeys <= n_keys;
+#pragma unroll
+    for (int u = 0; u < D / 16; u++) {
+        __half *d = dst + dst_off[u];
+        if (whole || key0 + row[u] < n_keys) {
+            const KV *sp = base + src_off[u];
             if constexpr (sizeof(KV) == 2) {
-                cp16(d, s);
+                cp16(d, sp);
             } else {
-                const float4 a = *reinterpret_cast<const float4 *>(s), b = *reinterpret_cast<const float4 *>(s + 4);
+                const float4 a = *reinterpret_cast<const float4 *>(sp), b = *reinterpret_cast<const float4 *>(sp + 4);
                 uint4 o;
                 o.x = pack_h2(a.x, a.y), o.y = pack_h2(a.z, a.w), o.z = pack_h2(b.x, b.y), o.w = pack_h2(b.z, b.w);
                 *reinterpret_cast<uint4 *>(d) = o;
@@ -62,7 +79,7 @@ __device__ __forceinline__ void stage_block(__half *dst, const KV *src, int key0
 }
 
 template <typename KV, int D>
-__global__ void __launch_bounds__(128) attention_prefill_mma_kernel(const float *__restrict__ q, const KV *__restrict__ kmem,
+__global__ void __launch_bounds__(128, D == 64 ? 4 : 2) attention_prefill_mma_kernel(const float *__restrict__ q, const KV *__restrict__ kmem,
                                                                     const KV *__restrict__ vmem, float *__restrict__ out,
                                                                     __half *__restrict__ out16, int M, int H, int KVH,
                                                                     const int *__restrict__ past_ptr, int past_imm, int ldq,
@@ -85,9 +102,16 @@ __global__ void __launch_bounds__(128) attention_prefill_mma_kernel(const float 
     const int n_blocks = (past + last_row) / kKeys + 1;
     const KV *kbase = kmem + kvh * D, *vbase = vmem + kvh * D;
 
+    // this thread's pieces of a staged block: 64 rows x D / 8 pieces of 16 bytes over 128 threads
+    int st_dst[D / 16], st_src[D / 16], st_row[D / 16];
+#pragma unroll
+    for (int u = 0; u < D / 16; u++) {
+        const int i = tid + 128 * u, r = i / (D / 8), c = (i - r * (D / 8)) * 8;
+        st_row[u] = r, st_dst[u] = r * LD + c, st_src[u] = r * kv_ld + c;
+    }
     // first block on its way while the Q fragments are loaded
-    stage_block<KV, D>(Ks, kbase, 0, n_keys, kv_ld, tid);
-    stage_block<KV, D>(Vs, vbase, 0, n_keys, kv_ld, tid);
+    stage_block<KV, D>(Ks, kbase, 0, n_keys, kv_ld, st_dst, st_src, st_row);
+    stage_block<KV, D>(Vs, vbase, 0, n_keys, kv_ld, st_dst, st_src, st_row);
     cp_async_commit();
 
     // Q fragments of this warp's 16 rows (rows g and g + 8 of the tile), fp16, kept for the whole kernel
@@ -115,8 +139,8 @@ __global__ void __launch_bounds__(128) attention_prefill_mma_kernel(const float 
     for (int kb = 0; kb < n_blocks; kb++) {
         const int buf = kb & 1;
         if (kb + 1 < n_blocks) {  // next block into the other buffer (its last readers passed the barrier below)
-            stage_block<KV, D>(Ks + (buf ^ 1) * kKeys * LD, kbase, (kb + 1) * kKeys, n_keys, kv_ld, tid);
-            stage_block<KV, D>(Vs + (buf ^ 1) * kKeys * LD, vbase, (kb + 1) * kKeys, n_keys, kv_ld, tid);
+            stage_block<KV, D>(Ks + (buf ^ 1) * kKeys * LD, kbase, (kb + 1) * kKeys, n_keys, kv_ld, st_dst, st_src, st_row);
+            stage_block<KV, D>(Vs + (buf ^ 1) * kKeys * LD, vbase, (kb + 1) * kKeys, n_keys, kv_ld, st_dst, st_src, st_row);
         }
         cp_async_commit();
         cp_async_wait(1);  // everything but the newest group: block kb has landed
@@ -124,55 +148,61 @@ __global__ void __launch_bounds__(128) attention_prefill_mma_kernel(const float 
         const int key0 = kb * kKeys;
         if (key0 <= warp_last_key && r0 + warp * 16 < M) {
             const __half *Kb = Ks + buf * kKeys * LD, *Vb = Vs + buf * kKeys * LD;
-            // ---- S = Q K^T for 16 rows x 64 keys: 8 key tiles x KS k-steps
+            // ---- S = Q K^T for 16 rows x 64 keys: 8 key tiles x KS k-steps; one ldmatrix.x4 brings the K fragments of
+            // two k-steps of a key tile (lanes 0-7 / 8-15 address d 0..7 / 8..15 of k-step ks, lanes 16-31 of ks + 1)
             float s[8][4];
+            const __half *klane = Kb + (lane & 7) * LD + (lane >> 3) * 8;
 #pragma unroll
             for (int j = 0; j < 8; j++) {
                 s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
-                const __half *kr = Kb + (j * 8 + g) * LD + 2 * t;
 #pragma unroll
-                for (int ks = 0; ks < KS; ks++) {
-                    const uint32_t b0 = *reinterpret_cast<const uint32_t *>(kr + ks * 16);
-                    const uint32_t b1 = *reinterpret_cast<const uint32_t *>(kr + ks * 16 + 8);
-                    mma_16816(s[j], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b0, b1);
+                for (int ks = 0; ks < KS; ks += 2) {
+                    uint32_t kf[4];
+                    ldmatrix_x4(kf, klane + j * 8 * LD + ks * 16);
+                    mma_16816(s[j], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], kf[0], kf[1]);
+                    mma_16816(s[j], qa[ks + 1][0], qa[ks + 1][1], qa[ks + 1][2], qa[ks + 1][3], kf[2], kf[3]);
                 }
             }
-            // ---- scale, mask (only blocks that reach past the first row's diagonal), running maximum
+            // ---- mask (only blocks that reach past the first row's diagonal), running maximum of the raw scores (the
+            // scale is positive, so it commutes with the maximum and is folded into the exponent's multiply-add)
             const bool need_mask = key0 + kKeys - 1 > past + r0 + warp * 16;
-            const int lim_a = past + row_a, lim_b = past + row_b;  // last visible key of rows g / g + 8
+            if (need_mask) {
+                const int lim_a = past + row_a, lim_b = past + row_b;  // last visible key of rows g / g + 8
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const int key = key0 + j * 8 + 2 * t + (i & 1);
+                        if (key > ((i & 2) ? lim_b : lim_a)) s[j][i] = -INFINITY;
+                    }
+                }
+            }
             float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
             for (int j = 0; j < 8; j++) {
-#pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    float v = s[j][i] * sl2;
-                    if (need_mask) {
-                        const int key = key0 + j * 8 + 2 * t + (i & 1);
-                        if (key > ((i & 2) ? lim_b : lim_a)) v = -INFINITY;
-                    }
-                    s[j][i] = v;
-                    mx[i >> 1] = fmaxf(mx[i >> 1], v);
-                }
+                mx[0] = fmaxf(mx[0], fmaxf(s[j][0], s[j][1]));
+                mx[1] = fmaxf(mx[1], fmaxf(s[j][2], s[j][3]));
             }
-            float alpha[2], m_use[2];
+            float alpha[2], neg_m[2];  // neg_m: minus the running maximum, in units of log2(e) / sqrt(D)
 #pragma unroll
             for (int r = 0; r < 2; r++) {
                 mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
                 mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
                 const float m_new = fmaxf(m_run[r], mx[r]);
-                m_use[r] = m_new == -INFINITY ? 0.f : m_new;  // a row with no visible key yet (rows past M): keep zeros, no NaN
-                alpha[r] = exp2f(m_run[r] - m_use[r]);
+                const float m_use = m_new == -INFINITY ? 0.f : m_new;  // a row with no visible key yet (rows past M): keep zeros, no NaN
+                alpha[r] = ex2((m_run[r] - m_use) * sl2);
+                neg_m[r] = -m_use * sl2;
                 m_run[r] = m_new;
                 l_run[r] *= alpha[r];
             }
 #pragma unroll
             for (int j = 0; j < DT; j++) o[j][0] *= alpha[0], o[j][1] *= alpha[0], o[j][2] *= alpha[1], o[j][3] *= alpha[1];
-            // ---- P = exp2(S - m), packed as the A fragments of P V; row sums stay per thread until the end
+            // ---- P = 2^(S sl2 - m), packed as the A fragments of P V; row sums stay per thread until the end
             uint32_t pa[4][4];
 #pragma unroll
             for (int j = 0; j < 8; j++) {
-                const float p0 = exp2f(s[j][0] - m_use[0]), p1 = exp2f(s[j][1] - m_use[0]);
-                const float p2 = exp2f(s[j][2] - m_use[1]), p3 = exp2f(s[j][3] - m_use[1]);
+                const float p0 = ex2(fmaf(s[j][0], sl2, neg_m[0])), p1 = ex2(fmaf(s[j][1], sl2, neg_m[0]));
+                const float p2 = ex2(fmaf(s[j][2], sl2, neg_m[1])), p3 = ex2(fmaf(s[j][3], sl2, neg_m[1]));
                 l_run[0] += p0 + p1, l_run[1] += p2 + p3;
                 pa[j >> 1][(j & 1) * 2] = pack_h2(p0, p1);       // a0 / a2: row g, keys 16 kk + 2t (+8)
                 pa[j >> 1][(j & 1) * 2 + 1] = pack_h2(p2, p3);   // a1 / a3: row g + 8

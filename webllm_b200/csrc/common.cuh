@@ -44,6 +44,12 @@ int fail(int code, const char *fmt, ...);
 // ---------------------------------------------------------------- weights
 enum class WeightKind : int { Gptq = 1, DenseF16 = 2, F32 = 3 };
 
+// A CUtensorMap (128 bytes, 64-byte aligned) encoded on first use and kept with the weight it describes.
+struct TmapSlot {
+    alignas(64) unsigned char bytes[128];
+    bool ok = false;
+};
+
 struct Weight {
     std::string name;
     WeightKind kind;
@@ -58,6 +64,8 @@ struct Weight {
     bool has_zeros = false;
     uint64_t bytes = 0;
     uint64_t arena_top = 0;   // `used` of the weight arena right after this registration (what wb_weight_pop checks)
+    // tensor maps of the weight operand of the tensor-core GEMM, for 128 and 256 output columns per CTA
+    mutable TmapSlot tmap_tc[2];
 };
 
 struct ArenaState {

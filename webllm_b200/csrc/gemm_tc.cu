@@ -960,30 +960,41 @@ template <int MT, bool DENSE, int NH>
 static cudaError_t launch_tc(const CUtensorMap &mx, const CUtensorMap &mw, const tc::Params &p, dim3 grid, cudaStream_t st, int sms)
 {
     constexpr int smem = tc::Smem<MT, DENSE, NH>::TOTAL;
-    auto go = [&](auto kernel) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    // the shared-memory attribute of a kernel instance is set once per device, not on every call (variant: 0 = one
+    // tile per CTA, 1 = split-K, 2 = gather, 3 = persistent, 4 = persistent gather)
+    static bool attr_set[5][16] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    auto ensure_attr = [&](auto kernel, int variant) -> cudaError_t {
+        if (dev >= 0 && dev < 16 && attr_set[variant][dev]) return cudaSuccess;
+        const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e == cudaSuccess && dev >= 0 && dev < 16) attr_set[variant][dev] = true;
+        return e;
+    };
+    auto go = [&](auto kernel, int variant) {
+        cudaError_t e = ensure_attr(kernel, variant);
         if (e != cudaSuccess) return e;
         return launch_pdl(kernel, grid, dim3(tc::THREADS), (size_t)smem, st, mx, mw, p);
     };
     // more tiles than SMs and no K split: one persistent CTA per SM walks the tiles
     const bool persist_on = persist_enabled();
     const int n_tiles = (int)(grid.x * grid.y);
-    auto go_persist = [&](auto kernel) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    auto go_persist = [&](auto kernel, int variant) {
+        cudaError_t e = ensure_attr(kernel, variant);
         if (e != cudaSuccess) return e;
         return launch_pdl(kernel, dim3((unsigned)sms), dim3(tc::THREADS_P), (size_t)smem, st, mx, mw, p, (int)grid.x, n_tiles);
     };
-    if (grid.z > 1) return go(tc::gemm_tc_kernel<MT, DENSE, true, NH, false>);  // slices write partial sums: no placement
+    if (grid.z > 1) return go(tc::gemm_tc_kernel<MT, DENSE, true, NH, false>, 1);  // slices write partial sums: no placement
     // only where TMEM holds two accumulator sets: with one set the MMAs would wait for four warps to drain it
     constexpr bool two_sets = 2 * (MT < 32 ? 32 : MT) * NH <= 512;
     const bool persist = persist_on && two_sets && n_tiles > sms;
     if constexpr (!DENSE) {
         if (p.n_dst > 0)
-            return persist ? go_persist(tc::gemm_tc_persist_kernel<MT, DENSE, NH, true>)
-                           : go(tc::gemm_tc_kernel<MT, DENSE, false, NH, true>);
+            return persist ? go_persist(tc::gemm_tc_persist_kernel<MT, DENSE, NH, true>, 4)
+                           : go(tc::gemm_tc_kernel<MT, DENSE, false, NH, true>, 2);
     }
-    return persist ? go_persist(tc::gemm_tc_persist_kernel<MT, DENSE, NH, false>)
-                   : go(tc::gemm_tc_kernel<MT, DENSE, false, NH, false>);
+    return persist ? go_persist(tc::gemm_tc_persist_kernel<MT, DENSE, NH, false>, 3)
+                   : go(tc::gemm_tc_kernel<MT, DENSE, false, NH, false>, 0);
 }
 
 // tile_n = 256 (two accumulators per CTA) exists for the 128-, 192- and 256-token tiles only
@@ -1019,7 +1030,11 @@ int launch_gemm_tc(wb_context *ctx, const Weight &w, const void *A, void *C, con
     }
     const int mt = plan.tile_m;
     const int nh = plan.tile_n == 2 * tc::BN ? 2 : 1;
-    CUtensorMap mx, mw;
+    // the activation map depends on the call (pointer, M, tile); the weight map only on the weight and the tile width:
+    // it is encoded once and kept with the weight
+    CUtensorMap mx;
+    TmapSlot &wslot = w.tmap_tc[nh - 1];
+    CUtensorMap &mw = *reinterpret_cast<CUtensorMap *>(wslot.bytes);
     WB_CHECK(make_map_2d(ctx, &mx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a16, (uint64_t)w.K, (uint64_t)M, tc::BK, (uint32_t)mt, true));
     tc::Params p;
     p.out = C, p.bias = bias, p.status = ctx->status_word;
@@ -1038,16 +1053,20 @@ int launch_gemm_tc(wb_context *ctx, const Weight &w, const void *A, void *C, con
     dim3 grid(plan.grid_x, plan.grid_y, S);
     cudaError_t e;
     if (w.kind == WeightKind::Gptq) {
-        WB_CHECK(make_map_2d(ctx, &mw, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, base + w.off_main, (uint64_t)w.N,
-                             (uint64_t)w.pack_rows, tc::BN * nh, 8, false));
+        if (!wslot.ok)
+            WB_CHECK(make_map_2d(ctx, &mw, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, base + w.off_main, (uint64_t)w.N,
+                                 (uint64_t)w.pack_rows, tc::BN * nh, 8, false));
+        wslot.ok = true;
         p.qz = w.has_zeros ? (const uint32_t *)(base + w.off_zeros) : nullptr;
         p.sc = (const __half *)(base + w.off_scales);
         p.zcols = (int)w.zcols;
         p.group_blocks = (int)(w.group / 64);
         e = launch_tc_mt<false>(mt, nh, mx, mw, p, grid, ctx->stream, ctx->sm_count);
     } else {
-        WB_CHECK(make_map_2d(ctx, &mw, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, base + w.off_main, (uint64_t)w.K, (uint64_t)w.N,
-                             tc::BK, tc::BN * nh, true));
+        if (!wslot.ok)
+            WB_CHECK(make_map_2d(ctx, &mw, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, base + w.off_main, (uint64_t)w.K, (uint64_t)w.N,
+                                 tc::BK, tc::BN * nh, true));
+        wslot.ok = true;
         p.qz = nullptr, p.sc = nullptr, p.zcols = 0, p.group_blocks = 1;
         e = launch_tc_mt<true>(mt, nh, mx, mw, p, grid, ctx->stream, ctx->sm_count);
     }
