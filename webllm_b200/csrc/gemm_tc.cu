@@ -822,6 +822,40 @@ __global__ void splitk_reduce_kernel(const float *__restrict__ partial, const fl
     }
 }
 
+// The same, four consecutive columns per thread (N, the pitch and the column offset multiples of 4; 16-byte stores for
+// f32, 8-byte for fp16).
+__global__ void __launch_bounds__(256) splitk_reduce_vec4_kernel(const float *__restrict__ partial, const float *__restrict__ bias,
+                                                                 const OutPlace pl, int64_t MN4, int N4, int S, int out_f16)
+{
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= MN4) return;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < S; s++) {
+        const float4 a = *reinterpret_cast<const float4 *>(partial + ((int64_t)s * MN4 + i) * 4);
+        v.x += a.x, v.y += a.y, v.z += a.z, v.w += a.w;
+    }
+    const int64_t m = i / N4;
+    const int n = (int)(i - m * N4) * 4;
+    if (bias) {
+        const float4 b = *reinterpret_cast<const float4 *>(bias + n);
+        v.x += b.x, v.y += b.y, v.z += b.z, v.w += b.w;
+    }
+    const int64_t o = m * pl.ld + pl.col0 + n;
+#pragma unroll
+    for (int g = 0; g < kMaxGatherDst; g++) {  // static indices into the parameter
+        if (g < pl.n_dst) {
+            if (out_f16) {
+                const __half2 a = __floats2half2_rn(v.x, v.y), b = __floats2half2_rn(v.z, v.w);
+                uint2 w;
+                w.x = *reinterpret_cast<const uint32_t *>(&a), w.y = *reinterpret_cast<const uint32_t *>(&b);
+                *reinterpret_cast<uint2 *>((__half *)pl.dst[g] + o) = w;
+            } else {
+                *reinterpret_cast<float4 *>((float *)pl.dst[g] + o) = v;
+            }
+        }
+    }
+}
+
 // Copies a dense local [M, N] result to its columns of every destination (the decode-size kernels write a dense
 // result; at those sizes the pieces are a few KB and a second small launch costs less than a collective).
 __global__ void scatter_cols_kernel(const void *__restrict__ src, const OutPlace pl, int64_t MN, int N, int f16)
@@ -1074,8 +1108,12 @@ int launch_gemm_tc(wb_context *ctx, const Weight &w, const void *A, void *C, con
     WB_CUDA(e);
     if (S > 1) {
         const int64_t MN = M * w.N;
-        tc::splitk_reduce_kernel<<<(unsigned)((MN + 255) / 256), 256, 0, ctx->stream>>>(p.partial, bias, place, MN, (int)w.N, S,
-                                                                                         out_dtype == WB_F16);
+        if (w.N % 4 == 0 && place.ld % 4 == 0 && place.col0 % 4 == 0)
+            tc::splitk_reduce_vec4_kernel<<<(unsigned)((MN / 4 + 255) / 256), 256, 0, ctx->stream>>>(p.partial, bias, place, MN / 4,
+                                                                                                       (int)(w.N / 4), S, out_dtype == WB_F16);
+        else
+            tc::splitk_reduce_kernel<<<(unsigned)((MN + 255) / 256), 256, 0, ctx->stream>>>(p.partial, bias, place, MN, (int)w.N, S,
+                                                                                             out_dtype == WB_F16);
         ctx->launches++;
         WB_CUDA(cudaGetLastError());
     }
