@@ -55,8 +55,10 @@ typedef enum {
     WB_KERNEL_GEMM_TC = 2,    /* tcgen05 / TMEM GEMM, TMA-fed, dequant in shared memory */
     WB_KERNEL_GENERIC = 3,    /* shape-agnostic CUDA kernel for ragged sizes (K%8, N%4, group%32 != 0) */
     WB_KERNEL_DENSE_GEMV = 4, /* fp16 [N,K] weight, M <= 8 */
-    WB_KERNEL_GEMV_STREAM = 5 /* M <= 4 on bandwidth-bound shapes (whole 128-k chunks, N % 32 == 0, >= 20 chunks per K
-                                 slice): same arithmetic as GEMV_MMA, weights straight into registers, persistent CTAs */
+    WB_KERNEL_GEMV_STREAM = 5, /* M <= 4 on bandwidth-bound shapes (whole 128-k chunks, N % 32 == 0, >= 20 chunks per K
+                                  slice): same arithmetic as GEMV_MMA, weights straight into registers, persistent CTAs */
+    WB_KERNEL_GEMM_TC_PAIR = 6 /* the tcgen05 GEMM on CTA pairs (cta_group::2): GPTQ weights, M >= 128, N >= 256; each CTA
+                                  of a pair unpacks 128 weight columns and loads half of the activation tile */
 } wb_kernel_kind;
 
 typedef struct {

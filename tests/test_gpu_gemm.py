@@ -62,7 +62,7 @@ def test_prefill_m2048(gpu, oracle, name, K, N):
     h, W16 = _weight(gpu, oracle, name, K, N)
     M = 2048
     x16 = np.random.default_rng(7).standard_normal((M, K)).astype(np.float16)
-    assert gpu.plan(h, M, "f16")["kernel_name"] == "gemm_tc"
+    assert gpu.plan(h, M, "f16")["kernel_name"] in ("gemm_tc", "gemm_tc_pair")
     got = run_linear(gpu, h, x16, M, N, None, act="f16")
     rows = sorted(set(np.random.default_rng(1).integers(0, M, 94).tolist()) | {0, M - 1})
     assert_close(oracle, got[rows], _ref_rows(oracle, x16, W16, rows), F16_RTOL, f"{name} M=2048")
@@ -73,6 +73,46 @@ def test_prefill_m2048(gpu, oracle, name, K, N):
     got32 = run_linear(gpu, h, x16.astype(np.float32) * np.float32(1.0002), M, N, None)
     x_r = (x16.astype(np.float32) * np.float32(1.0002)).astype(np.float16)
     assert_close(oracle, got32[rows], _ref_rows(oracle, x_r, W16, rows), F16_RTOL, f"{name} f32 activations")
+
+
+@pytest.mark.parametrize("name,K,N", [("q", 896, 896), ("qkv", 896, 1152), ("gate", 896, 4864), ("down", 4864, 896)])
+@pytest.mark.parametrize("M,split", [(128, 0), (300, 0), (1000, 0), (2048, 0), (520, 3)])
+def test_gemm_pair_kernel(gpu, oracle, name, K, N, M, split):
+    """The CTA-pair kernel (cta_group::2) forced: every token tile (128, 192, 256), token counts that leave the second
+    CTA's half of the activation tile partly or wholly empty, column counts that leave the second CTA's weight half empty
+    (896 = 3.5 x 256, 1152 = 4.5 x 256), work-item counts below and above the number of pairs, and K slices."""
+    h, W16 = _weight(gpu, oracle, name, K, N)
+    bias = np.random.default_rng(N).standard_normal(N).astype(np.float32)
+    try:
+        hb = gpu.weight(f"tcb_{name}")
+    except WebllmError:
+        hb = gpu.f32_upload(f"tcb_{name}", bias)
+    x16 = np.random.default_rng(M + K).standard_normal((M, K)).astype(np.float16)
+    gpu.plan_override(_lib.WB_KERNEL_GEMM_TC_PAIR, split)
+    try:
+        p = gpu.plan(h, M, "f16")
+        assert p["kernel_name"] == "gemm_tc_pair" and p["tile_n"] == 256 and (split == 0 or p["split_k"] == split)
+        got = run_linear(gpu, h, x16, M, N, hb, act="f16")
+        gpu.synchronize()  # surfaces a device-side wait that gave up
+        rows = sorted(set(np.random.default_rng(2).integers(0, M, 60).tolist()) | {0, M // 2 - 1, M // 2, M - 1})
+        assert_close(oracle, got[rows], _ref_rows(oracle, x16, W16, rows, bias), F16_RTOL, f"pair {name} M={M}")
+        got16 = run_linear(gpu, h, x16, M, N, hb, act="f16", out="f16")
+        assert np.array_equal(got16.astype(np.float16).view(np.uint16), got.astype(np.float16).view(np.uint16))
+    finally:
+        gpu.plan_override(0, 0)
+
+
+def test_gemm_pair_kernel_refuses_what_it_cannot_do(gpu, oracle):
+    h, _ = _weight(gpu, oracle, "k", 896, 128)
+    gpu.plan_override(_lib.WB_KERNEL_GEMM_TC_PAIR, 0)
+    try:
+        with pytest.raises(WebllmError, match="GEMM_TC_PAIR"):
+            gpu.plan(h, 512, "f16")  # N < 256
+        hq, _ = _weight(gpu, oracle, "q", 896, 896)
+        with pytest.raises(WebllmError, match="GEMM_TC_PAIR"):
+            gpu.plan(hq, 64, "f16")  # M < 128
+    finally:
+        gpu.plan_override(0, 0)
 
 
 def test_linearity_at_full_size(gpu, oracle):

@@ -91,7 +91,7 @@ def test_gather_from_the_persistent_tile_loop(gpu, oracle):
         sh = parallel.column_shard(N, r, G)
         h = gpu.gptq_register(f"pshard{r}", t.qweight, t.qzeros, t.scales, K, N, 128, 4, cols=(sh.begin, sh.count))
         p = gpu.plan(h, M, "f16")
-        assert p["kernel_name"] == "gemm_tc" and p["split_k"] == 1
+        assert p["kernel_name"] in ("gemm_tc", "gemm_tc_pair") and p["split_k"] == 1
         gpu.linear_gather(h, A, Cf, tmp, None, M, N, sh.begin, [])
     rows = sorted(set(np.random.default_rng(1).integers(0, M, 94).tolist()) | {0, M - 1})  # sampled: the host is slow
     got = gpu.read(Cf).reshape(M, N)[rows].astype(np.float32)

@@ -20,7 +20,8 @@ WB_IPC_HANDLE_BYTES = 64
 WB_PEER_FLAG_BYTES = 256
 WB_COMM_ID_BYTES = 128
 WB_KERNEL_GEMV_MMA, WB_KERNEL_GEMM_TC, WB_KERNEL_GENERIC, WB_KERNEL_DENSE_GEMV, WB_KERNEL_GEMV_STREAM = 1, 2, 3, 4, 5
-KERNEL_NAMES = {1: "gemv_mma", 2: "gemm_tc", 3: "generic", 4: "dense_gemv", 5: "gemv_stream"}
+WB_KERNEL_GEMM_TC_PAIR = 6
+KERNEL_NAMES = {1: "gemv_mma", 2: "gemm_tc", 3: "generic", 4: "dense_gemv", 5: "gemv_stream", 6: "gemm_tc_pair"}
 
 
 class WebllmError(RuntimeError):

@@ -761,7 +761,7 @@ int wb_plan_query(wb_context *ctx, wb_handle weight, int64_t M, int act_dtype, i
 int wb_plan_override(wb_context *ctx, int kernel, int split_k)
 {
     WB_CTX(ctx);
-    if (kernel < 0 || kernel > WB_KERNEL_GEMV_STREAM || split_k < 0)
+    if (kernel < 0 || kernel > WB_KERNEL_GEMM_TC_PAIR || split_k < 0)
         return fail(WB_ERR_BAD_ARG, "wb_plan_override: bad kernel %d / split %d", kernel, split_k);
     ctx->force_kernel = kernel;
     ctx->force_split = split_k;

@@ -588,7 +588,7 @@ static bool stream_enabled()
     static const bool on = [] { const char *e = getenv("WEBLLM_B200_NO_STREAM"); return !(e && e[0] == '1'); }();
     return on;
 }
-int plan_gemm_tc(wb_context *ctx, const Weight &w, int64_t M, int act_dtype, int exact, wb_plan *plan);
+int plan_gemm_tc(wb_context *ctx, const Weight &w, int64_t M, int act_dtype, int exact, int pair_mode, wb_plan *plan);
 bool gemm_tc_supports(const Weight &w, int64_t M);
 
 static bool gemv_mma_shape_ok(const Weight &w)
@@ -773,8 +773,15 @@ static int plan_linear_ex(wb_context *ctx, const Weight &w, int64_t M, int act_d
         plan->launches = 1;
         return WB_OK;
     case WB_KERNEL_GEMM_TC:
+    case WB_KERNEL_GEMM_TC_PAIR: {
         if (!gemm_tc_supports(w, M)) return fail(WB_ERR_UNSUPPORTED, "GEMM_TC does not support this shape");
-        return plan_gemm_tc(ctx, w, M, act_dtype, exact, plan);
+        // the planner's own choice may be either tensor-core kernel; a forced kind means that kernel and no other
+        const int pair_mode = kind == WB_KERNEL_GEMM_TC_PAIR ? 2 : ctx->force_kernel == 0 ? 1 : 0;
+        const int rc = plan_gemm_tc(ctx, w, M, act_dtype, exact, pair_mode, plan);
+        if (rc == WB_OK && plan->kernel == 0)
+            return fail(WB_ERR_UNSUPPORTED, "GEMM_TC_PAIR needs a GPTQ weight, M >= 128, N >= 256 and a dense local result");
+        return rc;
+    }
     case WB_KERNEL_GENERIC:
         plan->kernel = kind;
         plan->split_k = 1;
@@ -903,6 +910,7 @@ int launch_linear(wb_context *ctx, const Weight &w, const void *A, void *C, cons
         return WB_OK;
     }
     case WB_KERNEL_GEMM_TC:
+    case WB_KERNEL_GEMM_TC_PAIR:
         return launch_gemm_tc(ctx, w, A, C, bias, M, act_dtype, out_dtype, ex, plan);
     case WB_KERNEL_GENERIC: {
         const bool gptq = w.kind == WeightKind::Gptq;
