@@ -8,10 +8,10 @@
 // read both halves. Per SM and 64-k block that is half the activation bytes from L2, half the shared-memory fill and
 // half the operand reads of the one-CTA kernel, for the same arithmetic and the same unpack work.
 //
-// Roles per CTA, 22 warps: 0 = TMA producer (own packed-weight box, own half of the activation box), 1 = MMA issuer
-// (rank 0 of the pair only; both ranks allocate and free tensor memory), 2-17 = unpack (four sets of one thread per
-// column that take the k-blocks in turn), 18-21 = epilogue (drain one of the two accumulator sets while the MMAs of
-// the next item run). The pair walks the work items pair, pair + pairs, ...; an item is (K slice, column tile, token
+// Roles per CTA: a TMA producer warp (own packed-weight box, own half of the activation box), an MMA issuer warp
+// (rank 0 of the pair only; both ranks allocate and free tensor memory), sixteen unpack warps (four sets of one thread
+// per column that take the k-blocks in turn) and four epilogue warps (drain one of the two accumulator sets while the
+// MMAs of the next item run); which warp id has which role is listed at WARPS_PAIR. The pair walks the work items pair, pair + pairs, ...; an item is (K slice, column tile, token
 // tile); with more than one K slice the items write f32 partial sums that the split-K reduce launch adds.
 //
 // Barriers (mbarriers in shared memory, all waits bounded):
@@ -32,18 +32,27 @@ namespace tcp {
 using namespace tc;
 
 constexpr int EPI_WARPS = 4;
-constexpr int THREADS_PAIR = 64 + 32 * UNPACK_WARPS + 32 * EPI_WARPS;
+// Warp roles. The thread that issues the MMAs paces the kernel with its own instruction latency, so its warp scheduler
+// (warps with id % 4 == 1) carries no unpack warp: warp 1 = MMA issuer, 5 = TMA producer, 9 / 13 / 17 idle, 21 = epilogue;
+// the sixteen warps 0 .. 20 with id % 4 != 1 unpack; warps 22, 23, 24 are the other three epilogue warps (a warp reads
+// the tensor-memory lane quarter id % 4).
+constexpr int WARPS_PAIR = 25;
+constexpr int THREADS_PAIR = 32 * WARPS_PAIR;
 constexpr int KG = 4;  // unpack sets: 128 threads each, one thread per weight column
+constexpr int STG_ROWS = 64;                 // token rows of an epilogue staging tile
+constexpr int STG_BYTES = STG_ROWS * BN * 2;  // [64 tokens][128 columns] fp16
 
-template <int MT>
+// STG: two epilogue staging tiles are carved out of the shared memory (one pipeline stage fewer for the 256-token tile)
+template <int MT, bool STG>
 struct SmemPair {
     static constexpr int X_BYTES = (MT / 2) * BK * 2;   // this CTA's half of the activation tile
     static constexpr int WD_BYTES = BN * BK * 2;        // unpacked fp16 operand, 128 columns x 64 k
     static constexpr int WP_BYTES = 8 * BN * 4;         // packed box, 8 rows x 128 columns
     static constexpr int STAGE_BYTES = X_BYTES + WD_BYTES + WP_BYTES;  // every piece is a multiple of 1024
-    static constexpr int MAX_STAGES = (227 * 1024 - 1280) / STAGE_BYTES;
+    static constexpr int STG_TOTAL = STG ? 2 * STG_BYTES : 0;
+    static constexpr int MAX_STAGES = (227 * 1024 - 1280 - STG_TOTAL) / STAGE_BYTES;
     static constexpr int STAGES = MAX_STAGES > 6 ? 6 : MAX_STAGES;
-    static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    static constexpr int TOTAL = STAGES * STAGE_BYTES + STG_TOTAL + 1024 /*alignment slack*/ + 256 /*barriers*/;
     static_assert(STAGES >= KG, "every unpack set needs a stage of its own");
     static_assert(X_BYTES % 1024 == 0, "operand tiles start on a swizzle atom");
 };
@@ -91,20 +100,22 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr)
 {
     asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
 }
-template <int MT, bool SPLIT>
+template <int MT, bool SPLIT, bool STG>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS_PAIR, 1)
-gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, const Params p,
-                 const int tiles_m, const int tiles_n, const int n_items)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                 const __grid_constant__ CUtensorMap map_c, const Params p, const int tiles_m, const int tiles_n, const int n_items,
+                 const int use_tma_store)
 {
-    using S = SmemPair<MT>;
+    using S = SmemPair<MT, STG>;
     constexpr int STAGES = S::STAGES;
     constexpr uint32_t ACC_COLS = MT;                       // TMEM columns of one accumulator set
     constexpr uint32_t USED = 2 * ACC_COLS;
     constexpr uint32_t TMEM_COLS = USED <= 256 ? 256 : 512;
-    static_assert(USED <= 512 && MT % 32 == 0 && MT >= 128, "token tile");
+    static_assert(USED <= 512 && MT % STG_ROWS == 0 && MT >= 128, "token tile");
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint64_t *bars = (uint64_t *)(smem + STAGES * S::STAGE_BYTES);
+    uint8_t *stg = smem + STAGES * S::STAGE_BYTES;  // two epilogue staging tiles
+    uint64_t *bars = (uint64_t *)(stg + S::STG_TOTAL);
     uint64_t *full_w = bars, *ready = bars + STAGES, *empty = bars + 2 * STAGES;
     uint64_t *acc_full = bars + 3 * STAGES, *acc_empty = bars + 3 * STAGES + 2;
     uint32_t *tmem_slot = (uint32_t *)(bars + 3 * STAGES + 4);
@@ -153,7 +164,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     const uint32_t tmem_base = *tmem_slot;
     pdl_sync();
 
-    if (warp == 0) {
+    const bool sched1 = (warp & 3) == 1;
+    const int unpack_idx = (warp >> 2) * 3 + ((warp & 3) == 0 ? 0 : (warp & 3) - 1);  // 0 .. 15 for the unpack warps
+    if (warp == 5) {
         // ------------------------------------------------------------------ TMA producer (both CTAs)
         if (lane == 0) {
             int s = 0;
@@ -207,13 +220,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             }
         }
         __syncwarp();
-    } else if (warp < 2 + UNPACK_WARPS) {
+    } else if (!sched1 && warp <= 20) {
         // ------------------------------------------------------------------ unpack: the sets take the k-blocks of the
         // CTA's whole sequence (item after item) in turn
         constexpr int SET_THREADS = 32 * UNPACK_WARPS / KG;
         static_assert(SET_THREADS == BN, "one thread per weight column");
-        const int kg = (threadIdx.x - 64) / SET_THREADS;
-        const int tn = (threadIdx.x - 64) % SET_THREADS;
+        const int kg = (unpack_idx * 32 + lane) / SET_THREADS;
+        const int tn = (unpack_idx * 32 + lane) % SET_THREADS;
         const __half2 sixteenth = __float2half2_rn(0.0625f);
         const int src_off = S::X_BYTES + S::WD_BYTES + tn * 4;
         int dst_off[8];
@@ -300,14 +313,22 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             s += KG;
             if (s >= STAGES) s -= STAGES, ph ^= 1;
         }
-    } else {
+    } else if (warp >= 21) {
         // ------------------------------------------------------------------ epilogue: warp w drains TMEM lanes 32 * (w % 4) ..
         const int q = warp & 3;
         const uint32_t acc_empty0 = cluster_map_shared(&acc_empty[0], 0);
         bool ok = true;
+        int stg_sel = 0;
         for (int ti = 0; ti < items_cta && ok; ti++) {
             const int buf = ti & 1, use = ti >> 1;
             ok = mbar_wait_idle(&acc_full[buf], (uint32_t)use & 1u, abort_flag, p.status, 5);
+            // the four warps meet at barriers below: they go on together or not at all
+            {
+                uint32_t all;
+                asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 p, %1, 0;\n\tbar.red.and.pred q, 1, 128, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+                             : "=r"(all) : "r"((uint32_t)ok) : "memory");
+                ok = all != 0;
+            }
             if (!ok) break;
             tc_fence_after();
             const int m0 = item_m0(ti), n0 = item_n0(ti);
@@ -321,18 +342,52 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             const int n_warp = n0 + q * 32;
             const int n = n_warp + lane;
             const float bias = (!SPLIT && p.bias && n < p.N) ? p.bias[n] : 0.f;
+            if (!STG || !use_tma_store) {
 #pragma unroll 1
-            for (int c = 0; c < MT; c += 16) {
-                uint32_t r[16];
-                tmem_ld_32x32b_x16(acc + (uint32_t)c, r);
-                tmem_ld_wait();
-                store_block16<false>(d, out16, vec, r, bias, m0 + c, p.M, n_warp, p.N, lane);
+                for (int c = 0; c < MT; c += 16) {
+                    uint32_t r[16];
+                    tmem_ld_32x32b_x16(acc + (uint32_t)c, r);
+                    tmem_ld_wait();
+                    store_block16<false>(d, out16, vec, r, bias, m0 + c, p.M, n_warp, p.N, lane);
+                }
+            } else {
+                // fp16 result through shared memory: a lane holds one output column of 16 token rows, so it writes 16
+                // two-byte words into a [64 tokens][128 columns] staging tile (no exchange between lanes, no dependent
+                // chain), and one thread hands each finished tile to a TMA store, which also clips the ragged edges.
+                // Two staging tiles alternate; a tile is rewritten once the store that read it has finished reading.
+                const int epi_tid = (warp == 21 ? 0 : warp - 21) * 32 + lane;  // 0 .. 127, thread 0 issues the stores
+#pragma unroll 1
+                for (int c = 0; c < MT; c += STG_ROWS) {
+                    if (epi_tid == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    __half *tile = (__half *)(stg + stg_sel * STG_BYTES) + q * 32 + lane;
+#pragma unroll 1
+                    for (int cc = 0; cc < STG_ROWS; cc += 16) {
+                        uint32_t r[16];
+                        tmem_ld_32x32b_x16(acc + (uint32_t)(c + cc), r);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 16; j++) tile[(cc + j) * BN] = __float2half_rn(__uint_as_float(r[j]) + bias);
+                    }
+                    fence_async_smem();
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    if (epi_tid == 0) {
+                        if (m0 + c < p.M && n0 < p.N)
+                            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+                                         ::"l"(&map_c), "r"(n0), "r"(m0 + c), "r"(smem_u32(stg + stg_sel * STG_BYTES))
+                                         : "memory");
+                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");  // also when empty: the waits count groups
+                    }
+                    stg_sel ^= 1;
+                }
             }
             // the accumulator set may be overwritten once the four warps of both CTAs have read it
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(acc_empty0 + (uint32_t)buf * 8u);
         }
+        // the staging tiles must outlive the stores that read them
+        if (warp == 21 && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     }
     tc_fence_before();
     __syncthreads();
@@ -355,34 +410,38 @@ bool gemm_pair_supports(const Weight &w, int64_t M)
 }
 
 template <int MT>
-static cudaError_t launch_pair_mt(const CUtensorMap &mx, const CUtensorMap &mw, const tc::Params &p, int tiles_m, int tiles_n, int S,
-                                  cudaStream_t st, int sms)
+static cudaError_t launch_pair_mt(const CUtensorMap &mx, const CUtensorMap &mw, const CUtensorMap *mc, const tc::Params &p, int tiles_m,
+                                  int tiles_n, int S, cudaStream_t st, int sms)
 {
-    constexpr int smem = tcp::SmemPair<MT>::TOTAL;
-    static bool attr_set[2][16] = {};
+    static bool attr_set[3][16] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     const int n_items = tiles_m * tiles_n * S;
     int pairs = sms / 2;
     if (pairs > n_items) pairs = n_items;
-    auto go = [&](auto kernel, int variant) -> cudaError_t {
+    auto go = [&](auto kernel, int variant, int smem) -> cudaError_t {
         if (!(dev >= 0 && dev < 16 && attr_set[variant][dev])) {
             cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
             if (e != cudaSuccess) return e;
             if (dev >= 0 && dev < 16) attr_set[variant][dev] = true;
         }
-        return launch_pdl(kernel, dim3((unsigned)(2 * pairs)), dim3(tcp::THREADS_PAIR), (size_t)smem, st, mx, mw, p, tiles_m, tiles_n, n_items);
+        return launch_pdl(kernel, dim3((unsigned)(2 * pairs)), dim3(tcp::THREADS_PAIR), (size_t)smem, st, mx, mw, mc ? *mc : mx, p, tiles_m,
+                          tiles_n, n_items, mc ? 1 : 0);
     };
-    return S > 1 ? go(tcp::gemm_pair_kernel<MT, true>, 1) : go(tcp::gemm_pair_kernel<MT, false>, 0);
+    if (S > 1) return go(tcp::gemm_pair_kernel<MT, true, false>, 1, tcp::SmemPair<MT, false>::TOTAL);
+    if (mc) return go(tcp::gemm_pair_kernel<MT, false, true>, 2, tcp::SmemPair<MT, true>::TOTAL);
+    return go(tcp::gemm_pair_kernel<MT, false, false>, 0, tcp::SmemPair<MT, false>::TOTAL);
 }
 
-cudaError_t launch_gemm_pair(int mt, const CUtensorMap &mx, const CUtensorMap &mw, const tc::Params &p, int tiles_m, int tiles_n, int S,
-                             cudaStream_t st, int sms)
+// mc: tensor map of the fp16 result ([M, N], boxes of 128 columns x 64 rows) for the epilogue's TMA stores, or nullptr
+// (f32 result, K slices, or a row pitch that is not a multiple of 16 bytes): then the epilogue stores from registers.
+cudaError_t launch_gemm_pair(int mt, const CUtensorMap &mx, const CUtensorMap &mw, const CUtensorMap *mc, const tc::Params &p, int tiles_m,
+                             int tiles_n, int S, cudaStream_t st, int sms)
 {
     switch (mt) {
-    case 128: return launch_pair_mt<128>(mx, mw, p, tiles_m, tiles_n, S, st, sms);
-    case 192: return launch_pair_mt<192>(mx, mw, p, tiles_m, tiles_n, S, st, sms);
-    default: return launch_pair_mt<256>(mx, mw, p, tiles_m, tiles_n, S, st, sms);
+    case 128: return launch_pair_mt<128>(mx, mw, mc, p, tiles_m, tiles_n, S, st, sms);
+    case 192: return launch_pair_mt<192>(mx, mw, mc, p, tiles_m, tiles_n, S, st, sms);
+    default: return launch_pair_mt<256>(mx, mw, mc, p, tiles_m, tiles_n, S, st, sms);
     }
 }
 

@@ -635,8 +635,8 @@ static int make_map_2d(wb_context *ctx, CUtensorMap *map, CUtensorMapDataType dt
 
 // gemm_pair.cu
 bool gemm_pair_supports(const Weight &w, int64_t M);
-cudaError_t launch_gemm_pair(int mt, const CUtensorMap &mx, const CUtensorMap &mw, const tc::Params &p, int tiles_m, int tiles_n, int S,
-                             cudaStream_t st, int sms);
+cudaError_t launch_gemm_pair(int mt, const CUtensorMap &mx, const CUtensorMap &mw, const CUtensorMap *mc, const tc::Params &p, int tiles_m,
+                             int tiles_n, int S, cudaStream_t st, int sms);
 
 bool gemm_tc_supports(const Weight &w, int64_t M)
 {
@@ -647,6 +647,7 @@ bool gemm_tc_supports(const Weight &w, int64_t M)
 
 // microseconds per 64-k block of a pair's work item (measured)
 constexpr double kPairKb256 = 0.40, kPairKb192 = 0.37, kPairKb128 = 0.34;
+constexpr int kPairStageKb = 32;  // up to this many k-blocks per work item the 256-token tile stages its fp16 result
 
 static int env_int(const char *name)
 {
@@ -759,7 +760,7 @@ int plan_gemm_tc(wb_context *ctx, const Weight &w, int64_t M, int act_dtype, int
             plan->grid_x = (int)((M + pmt - 1) / pmt);
             plan->grid_y = (int)((w.N + 255) / 256);
             plan->split_k = plan->grid_z = pS;
-            plan->block = 704;
+            plan->block = 800;
             plan->tile_m = pmt;
             plan->tile_n = 256;
             mt = pmt, nh = 2, S = pS;
@@ -893,8 +894,19 @@ int launch_gemm_tc(wb_context *ctx, const Weight &w, const void *A, void *C, con
         p.sc = (const __half *)(base + w.off_scales);
         p.zcols = (int)w.zcols;
         p.group_blocks = (int)(w.group / 64);
-        e = pair ? launch_gemm_pair(mt, mx, mw, p, plan.grid_x, plan.grid_y, S, ctx->stream, ctx->sm_count)
-                 : launch_tc_mt<false>(mt, nh, mx, mw, p, grid, ctx->stream, ctx->sm_count);
+        if (pair) {
+            // an fp16 result leaves the epilogue through shared memory and TMA stores
+            CUtensorMap mc;
+            // (where a work item has few k-blocks: with many, the drain hides under the next item's MMAs anyway and the
+            // shared memory serves better as a sixth pipeline stage)
+            const bool tma_store = S == 1 && out_dtype == WB_F16 && w.N % 8 == 0 && ((uintptr_t)C & 15) == 0 &&
+                                   (mt < 256 || kblocks <= kPairStageKb);
+            if (tma_store)
+                WB_CHECK(make_map_2d(ctx, &mc, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, C, (uint64_t)w.N, (uint64_t)M, tc::BN, 64, false));
+            e = launch_gemm_pair(mt, mx, mw, tma_store ? &mc : nullptr, p, plan.grid_x, plan.grid_y, S, ctx->stream, ctx->sm_count);
+        } else {
+            e = launch_tc_mt<false>(mt, nh, mx, mw, p, grid, ctx->stream, ctx->sm_count);
+        }
     } else {
         if (!wslot.ok)
             WB_CHECK(make_map_2d(ctx, &mw, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, base + w.off_main, (uint64_t)w.K, (uint64_t)w.N,
