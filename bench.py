@@ -504,6 +504,7 @@ def column_shards(torch, dist, clock, rank: int, world: int, local: int, m_prefi
                 K, N = synthetic.QWEN7B_SHAPES[name]
                 t = synthetic.random_gptq(K, N, 128, seed=1)
                 for M in (1, m_prefill):
+                    progress(f"column shards: {name} M={M} (rank {rank})")
                     copies = 1 if M > 1 else max(2, min(16, int(300e6 // (t.nbytes // world))))
                     full_copies = 1 if M > 1 else max(2, min(8, int(300e6 // t.nbytes)))
                     lins = [parallel.ColumnShardedLinear(host, f"{name}7b_{M}_{i}", t) for i in range(copies)]
@@ -658,17 +659,23 @@ def run_ours(args) -> None:
         line["roofline"] = kernel_sections(gpu, clock, cfg, peaks)
     if not args.no_extras:
         if rank == 0:
+            progress("extras: gemv")
             extras.update(gemv_extras(gpu, clock, peaks))
+            progress("extras: gemm")
             extras.update(gemm_extras(gpu, clock, cfg, peaks))
+            progress("extras: batch sweep")
             extras["batch_sweep_05b"] = batch_sweep(gpu, clock)
+            progress("extras: prefill end to end")
             extras["prefill_e2e_2048"] = prefill_e2e(gpu, cfg)
         barrier()
+        progress(f"extras: replicated prefill (rank {rank})")
         rp = replicated_prefill(gpu, clock, cfg, peaks, rank, world)  # every rank takes part
         if rank == 0:
             extras["replicated_prefill_256x2048"] = rp
     model.close()
     gpu.close()
     if world > 1 and not args.no_extras:
+        progress(f"extras: column shards (rank {rank})")
         cs = column_shards(torch, dist, clock, rank, world, local)
         if rank == 0:
             extras["column_shards_7b"] = cs
@@ -691,6 +698,11 @@ def run_ours(args) -> None:
 
 
 # ---------------------------------------------------------------------------------------------------- profiler cases
+def progress(msg: str) -> None:
+    """One line on stderr per section: a run that dies half-way says where."""
+    print(f"[bench] {msg}", file=sys.stderr, flush=True)
+
+
 def run_case(args) -> None:
     from webllm_b200 import Gpu, QwenGpt, synthetic
     if args.case in ("gemv", "gemm"):

@@ -656,7 +656,7 @@ static int linear_gather_impl(wb_context *ctx, wb_handle weight, uint64_t a_offs
     WB_CHECK(rc);
     const void *A = arena_ptr(ctx, WB_ARENA_ACT, a_offset);
     bool barrier_done = false;
-    if (plan.kernel == WB_KERNEL_GEMM_TC) {
+    if (plan.kernel == WB_KERNEL_GEMM_TC || plan.kernel == WB_KERNEL_GEMM_TC_PAIR) {
         // the tensor-core kernel (and its split-K reduce) stores every output tile straight to all destinations
         ctx->place = pl;
         rc = launch_linear(ctx, *w, A, pl.dst[0], bias_ptr, M, act_dtype, out_dtype, 0);

@@ -32,15 +32,13 @@ namespace tcp {
 using namespace tc;
 
 constexpr int EPI_WARPS = 4;
-// Warp roles. The thread that issues the MMAs paces the kernel with its own instruction latency, so its warp scheduler
-// (warps with id % 4 == 1) carries no unpack warp: warp 1 = MMA issuer, 5 = TMA producer, 9 / 13 / 17 idle, 21 = epilogue;
-// the sixteen warps 0 .. 20 with id % 4 != 1 unpack; warps 22, 23, 24 are the other three epilogue warps (a warp reads
-// the tensor-memory lane quarter id % 4).
-constexpr int WARPS_PAIR = 25;
+// Warp roles as listed at MMA_WARP (gemm_tc.cuh), plus the four epilogue warps 21 .. 24 (a warp reads the tensor-memory
+// lane quarter id % 4).
+constexpr int WARPS_PAIR = WARPS + EPI_WARPS;
 constexpr int THREADS_PAIR = 32 * WARPS_PAIR;
 constexpr int KG = 4;  // unpack sets: 128 threads each, one thread per weight column
-constexpr int STG_ROWS = 64;                 // token rows of an epilogue staging tile
-constexpr int STG_BYTES = STG_ROWS * BN * 2;  // [64 tokens][128 columns] fp16
+constexpr int STG_ROWS = 64;                 // token rows of an fp16 epilogue staging tile (half as many of f32)
+constexpr int STG_BYTES = STG_ROWS * BN * 2;  // [64 tokens][128 columns] fp16 or [32][128] f32
 
 // STG: two epilogue staging tiles are carved out of the shared memory (one pipeline stage fewer for the 256-token tile)
 template <int MT, bool STG>
@@ -100,7 +98,8 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr)
 {
     asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
 }
-template <int MT, bool SPLIT, bool STG>
+// GATHER: the result goes to the placement in Params (this GPU's slab and its peers', row pitch ld_out) from registers.
+template <int MT, bool SPLIT, bool STG, bool GATHER = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS_PAIR, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                  const __grid_constant__ CUtensorMap map_c, const Params p, const int tiles_m, const int tiles_n, const int n_items,
@@ -156,7 +155,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) tmem_alloc_pair(tmem_slot, TMEM_COLS);
+    if (warp == MMA_WARP) tmem_alloc_pair(tmem_slot, TMEM_COLS);
     tc_fence_before();
     __syncthreads();
     cluster_sync_all();  // the other CTA's barriers are initialised before anything arrives on them
@@ -164,9 +163,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     const uint32_t tmem_base = *tmem_slot;
     pdl_sync();
 
-    const bool sched1 = (warp & 3) == 1;
-    const int unpack_idx = (warp >> 2) * 3 + ((warp & 3) == 0 ? 0 : (warp & 3) - 1);  // 0 .. 15 for the unpack warps
-    if (warp == 5) {
+    const int unpack_idx = unpack_index(warp);
+    if (warp == TMA_WARP) {
         // ------------------------------------------------------------------ TMA producer (both CTAs)
         if (lane == 0) {
             int s = 0;
@@ -191,7 +189,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                 if (++s == STAGES) s = 0, ph ^= 1;
             }
         }
-    } else if (warp == 1) {
+    } else if (warp == MMA_WARP) {
         // ------------------------------------------------------------------ MMA issuer (rank 0 for both SMs)
         if (lane == 0 && rank == 0) {
             constexpr uint32_t idesc = idesc_f16(2 * BN, MT);
@@ -220,7 +218,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             }
         }
         __syncwarp();
-    } else if (!sched1 && warp <= 20) {
+    } else if (is_unpack_warp(warp)) {
         // ------------------------------------------------------------------ unpack: the sets take the k-blocks of the
         // CTA's whole sequence (item after item) in turn
         constexpr int SET_THREADS = 32 * UNPACK_WARPS / KG;
@@ -313,7 +311,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             s += KG;
             if (s >= STAGES) s -= STAGES, ph ^= 1;
         }
-    } else if (warp >= 21) {
+    } else if (warp >= WARPS) {
         // ------------------------------------------------------------------ epilogue: warp w drains TMEM lanes 32 * (w % 4) ..
         const int q = warp & 3;
         const uint32_t acc_empty0 = cluster_map_shared(&acc_empty[0], 0);
@@ -336,9 +334,16 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             StoreDst d;
             d.n_dst = 1, d.ld = p.N, d.col0 = 0;
             bool out16;
-            if (SPLIT) d.dst[0] = p.partial + (int64_t)item_slice(ti) * p.M * p.N, out16 = false;
-            else d.dst[0] = p.out, out16 = p.out_f16 != 0;
-            const bool vec = (p.N & 7) == 0;
+            if (SPLIT) {
+                d.dst[0] = p.partial + (int64_t)item_slice(ti) * p.M * p.N, out16 = false;
+            } else if constexpr (GATHER) {
+#pragma unroll
+                for (int g = 0; g < kMaxGatherDst; g++) d.dst[g] = p.dst[g];
+                d.n_dst = p.n_dst, d.ld = p.ld_out, d.col0 = p.col0, out16 = p.out_f16 != 0;
+            } else {
+                d.dst[0] = p.out, out16 = p.out_f16 != 0;
+            }
+            const bool vec = (p.N & 7) == 0 && (d.ld & 7) == 0 && (d.col0 & 7) == 0;
             const int n_warp = n0 + q * 32;
             const int n = n_warp + lane;
             const float bias = (!SPLIT && p.bias && n < p.N) ? p.bias[n] : 0.f;
@@ -348,33 +353,44 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                     uint32_t r[16];
                     tmem_ld_32x32b_x16(acc + (uint32_t)c, r);
                     tmem_ld_wait();
-                    store_block16<false>(d, out16, vec, r, bias, m0 + c, p.M, n_warp, p.N, lane);
+                    store_block16<GATHER>(d, out16, vec, r, bias, m0 + c, p.M, n_warp, p.N, lane);
                 }
             } else {
-                // fp16 result through shared memory: a lane holds one output column of 16 token rows, so it writes 16
-                // two-byte words into a [64 tokens][128 columns] staging tile (no exchange between lanes, no dependent
-                // chain), and one thread hands each finished tile to a TMA store, which also clips the ragged edges.
-                // Two staging tiles alternate; a tile is rewritten once the store that read it has finished reading.
-                const int epi_tid = (warp == 21 ? 0 : warp - 21) * 32 + lane;  // 0 .. 127, thread 0 issues the stores
+                // The result leaves through shared memory: a lane holds one output column of 16 token rows, so it writes
+                // 16 words into a [tokens][128 columns] staging tile (no exchange between lanes, no dependent chain), and
+                // one thread hands each finished tile to a TMA store, which also clips the ragged edges. A tile is 16 KB:
+                // 64 token rows of fp16 or 32 of f32 (also the partial sums of a K slice, third map coordinate). Two tiles
+                // alternate; a tile is rewritten once the store that read it has finished reading.
+                const int epi_tid = (warp - WARPS) * 32 + lane;  // 0 .. 127, thread 0 issues the stores
+                const bool o16 = !SPLIT && out16;
+                const int rows = o16 ? STG_ROWS : STG_ROWS / 2;
+                const int slice = SPLIT ? item_slice(ti) : 0;
 #pragma unroll 1
-                for (int c = 0; c < MT; c += STG_ROWS) {
+                for (int c = 0; c < MT; c += rows) {
                     if (epi_tid == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
                     asm volatile("bar.sync 1, 128;" ::: "memory");
-                    __half *tile = (__half *)(stg + stg_sel * STG_BYTES) + q * 32 + lane;
+                    uint8_t *tile_base = stg + stg_sel * STG_BYTES;
 #pragma unroll 1
-                    for (int cc = 0; cc < STG_ROWS; cc += 16) {
+                    for (int cc = 0; cc < rows; cc += 16) {
                         uint32_t r[16];
                         tmem_ld_32x32b_x16(acc + (uint32_t)(c + cc), r);
                         tmem_ld_wait();
+                        if (o16) {
+                            __half *tile = (__half *)tile_base + q * 32 + lane;
 #pragma unroll
-                        for (int j = 0; j < 16; j++) tile[(cc + j) * BN] = __float2half_rn(__uint_as_float(r[j]) + bias);
+                            for (int j = 0; j < 16; j++) tile[(cc + j) * BN] = __float2half_rn(__uint_as_float(r[j]) + bias);
+                        } else {
+                            float *tile = (float *)tile_base + q * 32 + lane;
+#pragma unroll
+                            for (int j = 0; j < 16; j++) tile[(cc + j) * BN] = __uint_as_float(r[j]) + bias;
+                        }
                     }
                     fence_async_smem();
                     asm volatile("bar.sync 1, 128;" ::: "memory");
                     if (epi_tid == 0) {
                         if (m0 + c < p.M && n0 < p.N)
-                            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
-                                         ::"l"(&map_c), "r"(n0), "r"(m0 + c), "r"(smem_u32(stg + stg_sel * STG_BYTES))
+                            asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%1, %2, %3}], [%4];"
+                                         ::"l"(&map_c), "r"(n0), "r"(m0 + c), "r"(slice), "r"(smem_u32(tile_base))
                                          : "memory");
                         asm volatile("cp.async.bulk.commit_group;" ::: "memory");  // also when empty: the waits count groups
                     }
@@ -387,12 +403,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             if (lane == 0) mbar_arrive_cluster(acc_empty0 + (uint32_t)buf * 8u);
         }
         // the staging tiles must outlive the stores that read them
-        if (warp == 21 && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+        if (warp == WARPS && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     }
     tc_fence_before();
     __syncthreads();
     cluster_sync_all();  // neither CTA leaves (or frees tensor memory) while the other may still reach into it
-    if (warp == 1) tmem_dealloc_pair(tmem_base, TMEM_COLS);
+    if (warp == MMA_WARP) tmem_dealloc_pair(tmem_base, TMEM_COLS);
 }
 
 }  // namespace tcp
@@ -413,7 +429,7 @@ template <int MT>
 static cudaError_t launch_pair_mt(const CUtensorMap &mx, const CUtensorMap &mw, const CUtensorMap *mc, const tc::Params &p, int tiles_m,
                                   int tiles_n, int S, cudaStream_t st, int sms)
 {
-    static bool attr_set[3][16] = {};
+    static bool attr_set[5][16] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     const int n_items = tiles_m * tiles_n * S;
@@ -428,13 +444,17 @@ static cudaError_t launch_pair_mt(const CUtensorMap &mx, const CUtensorMap &mw, 
         return launch_pdl(kernel, dim3((unsigned)(2 * pairs)), dim3(tcp::THREADS_PAIR), (size_t)smem, st, mx, mw, mc ? *mc : mx, p, tiles_m,
                           tiles_n, n_items, mc ? 1 : 0);
     };
-    if (S > 1) return go(tcp::gemm_pair_kernel<MT, true, false>, 1, tcp::SmemPair<MT, false>::TOTAL);
+    if (S > 1)
+        return mc ? go(tcp::gemm_pair_kernel<MT, true, true>, 3, tcp::SmemPair<MT, true>::TOTAL)
+                  : go(tcp::gemm_pair_kernel<MT, true, false>, 1, tcp::SmemPair<MT, false>::TOTAL);
+    if (p.n_dst > 0) return go(tcp::gemm_pair_kernel<MT, false, false, true>, 4, tcp::SmemPair<MT, false>::TOTAL);
     if (mc) return go(tcp::gemm_pair_kernel<MT, false, true>, 2, tcp::SmemPair<MT, true>::TOTAL);
     return go(tcp::gemm_pair_kernel<MT, false, false>, 0, tcp::SmemPair<MT, false>::TOTAL);
 }
 
-// mc: tensor map of the fp16 result ([M, N], boxes of 128 columns x 64 rows) for the epilogue's TMA stores, or nullptr
-// (f32 result, K slices, or a row pitch that is not a multiple of 16 bytes): then the epilogue stores from registers.
+// mc: tensor map of the result or of the K slices' partial sums ([slices, M, N], boxes of 128 columns x 64 fp16 or 32 f32
+// rows) for the epilogue's TMA stores, or nullptr (a row pitch that is not a multiple of 16 bytes; a long-K launch that
+// would rather have the shared memory as a pipeline stage): then the epilogue stores from registers.
 cudaError_t launch_gemm_pair(int mt, const CUtensorMap &mx, const CUtensorMap &mw, const CUtensorMap *mc, const tc::Params &p, int tiles_m,
                              int tiles_n, int S, cudaStream_t st, int sms)
 {

@@ -86,7 +86,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+    if (warp == MMA_WARP) tmem_alloc(tmem_slot, TMEM_COLS);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -95,7 +95,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     // programmatic stream serialization; nothing that the previous kernel writes or reads is touched before this point.
     pdl_sync();
 
-    if (warp == 0) {
+    bool ok = true;
+    if (warp == TMA_WARP) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
             int s = 0;
@@ -109,11 +110,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 if (++s == STAGES) s = 0, ph ^= 1;
             }
         }
-    } else if (warp == 1) {
+        __syncwarp();
+    } else if (warp == MMA_WARP) {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             constexpr uint32_t idesc = idesc_f16(BN, MT);
-            bool ok = true;
             int s = 0;
             uint32_t ph = 0;
             for (int kb = kb0; kb < KB && ok; kb++) {
@@ -135,14 +136,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             if (ok) umma_commit(acc_full);
         }
         __syncwarp();
-    } else {
-        // ------------------------------------------------------------------ unpack, then epilogue
+    } else if (is_unpack_warp(warp)) {
+        // ------------------------------------------------------------------ unpack
         constexpr int SET_THREADS = 32 * UNPACK_WARPS / KG;
         constexpr int RPT = 8 * COLS / SET_THREADS;    // packed rows of a k-block per thread: 8 rows x COLS words in all
-        const int kg = (threadIdx.x - 64) / SET_THREADS;          // which set
-        const int tn = (threadIdx.x - 64) % SET_THREADS % COLS;   // column of the tile
-        const int rhalf = (threadIdx.x - 64) % SET_THREADS / COLS;  // which RPT of the 8 packed rows
-        bool ok = true;
+        const int ut = unpack_index(warp) * 32 + lane;
+        const int kg = ut / SET_THREADS;          // which set
+        const int tn = ut % SET_THREADS % COLS;   // column of the tile
+        const int rhalf = ut % SET_THREADS / COLS;  // which RPT of the 8 packed rows
         if constexpr (!DENSE) {
             const int n = n0 + tn;
             const bool n_ok = n < p.N;
@@ -219,7 +220,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 if (s >= STAGES) s -= STAGES, ph ^= 1;
             }
         }
-        // epilogue: warp w may touch TMEM lanes 32*(w%4) .. +31
+    }
+    // ---------------------------------------------------------------------- epilogue, all 21 warps: warp w may touch
+    // TMEM lanes 32 * (w % 4) .. + 31; the warps of a lane quarter (six for quarter 0, five for the others) take the
+    // 16-token blocks of the accumulator in turn
+    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;  // the single-thread roles report for their warp
+    {
         if (ok) ok = mbar_wait(acc_full, 0, abort_flag, p.status, 5);
         if (ok) {
             tc_fence_after();
@@ -227,12 +233,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             // split-K: slices write f32 partial sums, splitk_reduce_kernel adds them and the bias
             constexpr bool split = SPLIT;
             float *part = SPLIT ? p.partial + (int64_t)blockIdx.z * p.M * p.N : nullptr;
-            // the warps that share a TMEM lane quarter split the columns
-            constexpr int SHARE = UNPACK_WARPS / 4;                      // warps per lane quarter
-            constexpr int NSPLIT = MT / 16 < SHARE ? MT / 16 : SHARE;    // how many of them get columns (16 at a time)
-            constexpr int CSPAN = MT / NSPLIT;
-            const int c_begin = ((warp - 2) >> 2) * CSPAN;
-            const int c_end = ((warp - 2) >> 2) < NSPLIT ? c_begin + CSPAN : c_begin;
+            const int share = q == 0 ? 6 : 5;  // warps of this lane quarter
+            const int c_begin = (warp >> 2) * 16, c_step = share * 16;
             // where the block goes: this slice's f32 partial sums, the dense local result, or the placement of a
             // column-sharded call
             StoreDst d;
@@ -253,7 +255,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 const int n = n_warp + lane;
                 const float bias = (!split && p.bias && n < p.N) ? p.bias[n] : 0.f;
 #pragma unroll 1
-                for (int c = c_begin; c < c_end; c += 16) {
+                for (int c = c_begin; c < MT; c += c_step) {
                     uint32_t r[16];
                     tmem_ld_32x32b_x16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(h * ACC_COLS + c), r);
                     tmem_ld_wait();
@@ -264,7 +266,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+    if (warp == MMA_WARP) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
 // ----------------------------------------------------------------------------------------------------
@@ -275,8 +277,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 // their own drain a finished accumulator while the MMAs of the next tile are issued: pipeline fill, TMEM drain and
 // the stores (to peers too, in a column-sharded call) leave the critical path of every tile but the last.
 // Roles, 22 warps: 0 = TMA, 1 = MMA, 2-17 = unpack (as above), 18-21 = epilogue (TMEM lane quarter warp % 4).
-constexpr int EPI_WARPS = 4;
-constexpr int THREADS_P = THREADS + 32 * EPI_WARPS;
+constexpr int EPI_WARPS = 4;         // warps 21 .. 24, after the roles listed at MMA_WARP
+constexpr int THREADS_P = 32 * (WARPS + EPI_WARPS);
 
 template <int MT, bool DENSE, int NH, bool GATHER>
 __global__ void __launch_bounds__(THREADS_P, 1)
@@ -326,7 +328,7 @@ gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+    if (warp == MMA_WARP) tmem_alloc(tmem_slot, TMEM_COLS);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -335,7 +337,7 @@ gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
     // programmatic stream serialization; nothing that the previous kernel writes or reads is touched before this point.
     pdl_sync();
 
-    if (warp == 0) {
+    if (warp == TMA_WARP) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
             int s = 0;
@@ -354,7 +356,7 @@ gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
                 }
             }
         }
-    } else if (warp == 1) {
+    } else if (warp == MMA_WARP) {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             constexpr uint32_t idesc = idesc_f16(BN, MT);
@@ -387,15 +389,16 @@ gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
             }
         }
         __syncwarp();
-    } else if (warp < 2 + UNPACK_WARPS) {
+    } else if (is_unpack_warp(warp)) {
         // ------------------------------------------------------------------ unpack: the sets take the k-blocks of the
         // CTA's whole sequence (tile after tile) in turn
         if constexpr (!DENSE) {
             constexpr int SET_THREADS = 32 * UNPACK_WARPS / KG;
             constexpr int RPT = 8 * COLS / SET_THREADS;
-            const int kg = (threadIdx.x - 64) / SET_THREADS;
-            const int tn = (threadIdx.x - 64) % SET_THREADS % COLS;
-            const int rhalf = (threadIdx.x - 64) % SET_THREADS / COLS;
+            const int ut = unpack_index(warp) * 32 + lane;
+            const int kg = ut / SET_THREADS;
+            const int tn = ut % SET_THREADS % COLS;
+            const int rhalf = ut % SET_THREADS / COLS;
             const __half2 sixteenth = __float2half2_rn(0.0625f);
             const int src_off = S::X_BYTES + S::WD_BYTES + (tn + rhalf * RPT * COLS) * 4;
             int dst_off[RPT];
@@ -477,7 +480,7 @@ gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
                 if (s >= STAGES) s -= STAGES, ph ^= 1;
             }
         }
-    } else {
+    } else if (warp >= WARPS) {
         // ------------------------------------------------------------------ epilogue: warp w drains TMEM lanes 32 * (w % 4) ..
         const int q = warp & 3;
         bool ok = true;
@@ -519,7 +522,7 @@ gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+    if (warp == MMA_WARP) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
 __global__ void cast_f32_to_f16_kernel(const float *__restrict__ in, __half *__restrict__ out, int64_t n)
@@ -563,6 +566,7 @@ __global__ void __launch_bounds__(256) splitk_reduce_vec4_kernel(const float *__
                                                                  const OutPlace pl, int64_t MN4, int N4, int S, int out_f16)
 {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    pdl_sync();  // launched under the tail of the GEMM whose partial sums it reads
     if (i >= MN4) return;
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int s = 0; s < S; s++) {
@@ -646,7 +650,7 @@ bool gemm_tc_supports(const Weight &w, int64_t M)
 }
 
 // microseconds per 64-k block of a pair's work item (measured)
-constexpr double kPairKb256 = 0.40, kPairKb192 = 0.37, kPairKb128 = 0.34;
+constexpr double kPairKb256 = 0.37, kPairKb192 = 0.35, kPairKb128 = 0.34, kPairItem = 0.4;
 constexpr int kPairStageKb = 32;  // up to this many k-blocks per work item the 256-token tile stages its fp16 result
 
 static int env_int(const char *name)
@@ -683,7 +687,7 @@ static double pick_plan(int64_t M, int64_t N, int kblocks, int sms, int force_sp
         for (int nh = 1; nh <= 2; nh++) {
             if (force_nh && nh != force_nh && mt >= 128 && N >= 256) continue;  // pinned wherever it exists
             if (nh == 2 && (mt < 128 || N < 256)) continue;
-            const double t_kb = nh == 2 ? (mt == 256 ? 0.91 : mt == 192 ? 0.855 : 0.80) : (mt == 256 ? 0.62 : mt == 192 ? 0.585 : 0.55);
+            const double t_kb = nh == 2 ? (mt == 256 ? 0.89 : mt == 192 ? 0.84 : 0.80) : (mt == 256 ? 0.56 : mt == 192 ? 0.52 : 0.45);
             const double t_tile = 1.5 + 2.7 * nh * mt / 256.;
             const int64_t tiles = ((M + mt - 1) / mt) * ((N + 128 * nh - 1) / (128 * nh));
             for (int S = 1; S <= 16; S++) {
@@ -732,7 +736,7 @@ static double pick_plan_pair(int64_t M, int64_t N, int kblocks, int sms, int for
             if ((kblocks + per - 1) / per != S) continue;
             if (S > 1 && (double)S * M * N * 4. > 64e6) continue;
             const int64_t rounds = (tiles * S + pairs - 1) / pairs;
-            double t = 2.5 + t_tile + rounds * per * t_kb;
+            double t = 3.3 + t_tile + rounds * (per * t_kb + kPairItem);
             if (S > 1) t += 2.5 + (S + 1) * (double)M * N * 4. / 4e6;
             if (best < 0. || t < best) best = t, *mt_out = mt, *s_out = S;
         }
@@ -750,11 +754,14 @@ int plan_gemm_tc(wb_context *ctx, const Weight &w, int64_t M, int act_dtype, int
     // microseconds that the stores to the peers of a column-sharded call take at ~700 GB/s per direction
     const double t_remote = ctx->place.n_dst > 1 ? (double)(ctx->place.n_dst - 1) * M * w.N * ctx->place.elem_bytes / 700e3 : 0.;
     const double t_one = pick_plan(M, w.N, kblocks, ctx->sm_count, ctx->force_split, t_remote, &mt, &nh, &S);
-    const bool pair_ok = pair_mode > 0 && ctx->place.n_dst == 0 && gemm_pair_supports(w, M) && ctx->sm_count >= 2;
+    // Stores into peers' slabs stay with the one-CTA kernels: a two-GPU run of the pair kernel with peer destinations
+    // (7B-class shards at M = 4096) ended in a launch failure whose cause reading has not shown, so it is not launched so.
+    const bool pair_ok = pair_mode > 0 && ctx->place.n_dst <= 1 && gemm_pair_supports(w, M) && ctx->sm_count >= 2;
     if (pair_mode == 2 && !pair_ok) return WB_OK;
     if (pair_ok) {
         int pmt, pS;
-        const double t_pair = pick_plan_pair(M, w.N, kblocks, ctx->sm_count, ctx->force_split, &pmt, &pS);
+        double t_pair = pick_plan_pair(M, w.N, kblocks, ctx->sm_count, ctx->force_split, &pmt, &pS);
+        if (t_remote > 0. && pS == 1 && t_pair < t_remote) t_pair = t_remote;  // the stores to the peers run under the MMAs
         if (pair_mode == 2 || (t_pair > 0. && t_pair < t_one)) {
             plan->kernel = WB_KERNEL_GEMM_TC_PAIR;
             plan->grid_x = (int)((M + pmt - 1) / pmt);
@@ -878,8 +885,7 @@ int launch_gemm_tc(wb_context *ctx, const Weight &w, const void *A, void *C, con
     OutPlace place = ctx->place;  // n_dst > 0: a column-sharded call (wb_linear_gather)
     if (place.n_dst > 0 && w.kind != WeightKind::Gptq)
         return fail(WB_ERR_UNSUPPORTED, "wb_linear_gather takes GPTQ weights only");
-    if (pair && (place.n_dst > 0 || w.kind != WeightKind::Gptq))
-        return fail(WB_ERR_UNSUPPORTED, "the CTA-pair GEMM takes GPTQ weights and a dense local result");
+    if (pair && w.kind != WeightKind::Gptq) return fail(WB_ERR_UNSUPPORTED, "the CTA-pair GEMM takes GPTQ weights");
     p.ld_out = place.ld, p.col0 = place.col0, p.n_dst = place.n_dst;
     for (int g = 0; g < kMaxGatherDst; g++) p.dst[g] = place.dst[g];
     if (place.n_dst == 0) place.ld = w.N, place.col0 = 0, place.n_dst = 1, place.dst[0] = C;  // for the split-K reduce
@@ -895,14 +901,24 @@ int launch_gemm_tc(wb_context *ctx, const Weight &w, const void *A, void *C, con
         p.zcols = (int)w.zcols;
         p.group_blocks = (int)(w.group / 64);
         if (pair) {
-            // an fp16 result leaves the epilogue through shared memory and TMA stores
+            // the result (or the K slices' f32 partial sums) leaves the epilogue through shared memory and TMA stores
+            // where a work item has few k-blocks: with many, the drain hides under the next item's MMAs anyway and the
+            // shared memory serves the 256-token tile better as a sixth pipeline stage
             CUtensorMap mc;
-            // (where a work item has few k-blocks: with many, the drain hides under the next item's MMAs anyway and the
-            // shared memory serves better as a sixth pipeline stage)
-            const bool tma_store = S == 1 && out_dtype == WB_F16 && w.N % 8 == 0 && ((uintptr_t)C & 15) == 0 &&
-                                   (mt < 256 || kblocks <= kPairStageKb);
-            if (tma_store)
-                WB_CHECK(make_map_2d(ctx, &mc, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, C, (uint64_t)w.N, (uint64_t)M, tc::BN, 64, false));
+            const bool c16 = S == 1 && out_dtype == WB_F16;
+            void *cbase = S > 1 ? (void *)p.partial : C;
+            const bool tma_store = (S > 1 || p.n_dst == 0) && w.N % (c16 ? 8 : 4) == 0 && ((uintptr_t)cbase & 15) == 0 && (mt < 256 || p.kb_per_slice <= kPairStageKb);
+            if (tma_store) {
+                cuuint64_t dims[3] = {(cuuint64_t)w.N, (cuuint64_t)M, (cuuint64_t)S};
+                cuuint64_t strides[2] = {(cuuint64_t)w.N * (c16 ? 2 : 4), (cuuint64_t)w.N * M * (c16 ? 2 : 4)};
+                cuuint32_t box[3] = {(cuuint32_t)tc::BN, c16 ? 64u : 32u, 1u};
+                cuuint32_t estr[3] = {1, 1, 1};
+                CUresult r = ((EncodeTiledFn)ctx->tmap_encode)(&mc, c16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3,
+                                                               cbase, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                                               CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                if (r != CUDA_SUCCESS) return fail(WB_ERR_CUDA, "cuTensorMapEncodeTiled (result) failed with code %d", (int)r);
+            }
             e = launch_gemm_pair(mt, mx, mw, tma_store ? &mc : nullptr, p, plan.grid_x, plan.grid_y, S, ctx->stream, ctx->sm_count);
         } else {
             e = launch_tc_mt<false>(mt, nh, mx, mw, p, grid, ctx->stream, ctx->sm_count);
@@ -920,8 +936,8 @@ int launch_gemm_tc(wb_context *ctx, const Weight &w, const void *A, void *C, con
     if (S > 1) {
         const int64_t MN = M * w.N;
         if (w.N % 4 == 0 && place.ld % 4 == 0 && place.col0 % 4 == 0)
-            tc::splitk_reduce_vec4_kernel<<<(unsigned)((MN / 4 + 255) / 256), 256, 0, ctx->stream>>>(p.partial, bias, place, MN / 4,
-                                                                                                       (int)(w.N / 4), S, out_dtype == WB_F16);
+            WB_CUDA(launch_pdl(tc::splitk_reduce_vec4_kernel, dim3((unsigned)((MN / 4 + 255) / 256)), dim3(256), 0, ctx->stream,
+                               (const float *)p.partial, bias, place, MN / 4, (int)(w.N / 4), S, (int)(out_dtype == WB_F16)));
         else
             tc::splitk_reduce_kernel<<<(unsigned)((MN + 255) / 256), 256, 0, ctx->stream>>>(p.partial, bias, place, MN, (int)w.N, S,
                                                                                              out_dtype == WB_F16);

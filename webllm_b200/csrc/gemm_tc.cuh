@@ -11,8 +11,18 @@ namespace tc {
 
 constexpr int BN = 128;       // output columns per accumulator (UMMA M); a CTA holds NH = 1 or 2 of them
 constexpr int BK = 64;        // k per stage: one 128-byte swizzle atom of fp16
-constexpr int UNPACK_WARPS = 16;  // a multiple of 4: they also drain TMEM, one lane quarter per warp % 4
-constexpr int THREADS = 64 + 32 * UNPACK_WARPS;
+constexpr int UNPACK_WARPS = 16;
+// Warp roles, shared by the three kernels. The thread that issues the MMAs paces a kernel with its own instruction
+// latency (a wait, four to eight tcgen05.mma, a commit per k-block), and a warp scheduler serves the warps with the same
+// id % 4: so the scheduler of the issuing warp carries no unpack warp. Warp 1 = MMA issuer, 5 = TMA producer, 9 / 13 / 17
+// have no part in the k-loop; the sixteen warps 0 .. 20 with id % 4 != 1 unpack. Measured on the 7B-class gate
+// projection at M = 4096 (CTA-pair kernel): 383 us with the unpack warps spread over all four schedulers, 337 us so.
+constexpr int MMA_WARP = 1, TMA_WARP = 5;
+constexpr int WARPS = 21;             // the one-tile kernel: every warp takes part in the epilogue
+constexpr int THREADS = 32 * WARPS;
+__device__ __forceinline__ bool is_unpack_warp(int warp) { return (warp & 3) != 1 && warp <= 20; }
+// 0 .. 15 for the unpack warps in warp-id order
+__device__ __forceinline__ int unpack_index(int warp) { return (warp >> 2) * 3 + ((warp & 3) == 0 ? 0 : (warp & 3) - 1); }
 constexpr uint32_t SPIN_LIMIT = 1u << 20;
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }

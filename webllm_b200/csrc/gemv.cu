@@ -779,7 +779,7 @@ static int plan_linear_ex(wb_context *ctx, const Weight &w, int64_t M, int act_d
         const int pair_mode = kind == WB_KERNEL_GEMM_TC_PAIR ? 2 : ctx->force_kernel == 0 ? 1 : 0;
         const int rc = plan_gemm_tc(ctx, w, M, act_dtype, exact, pair_mode, plan);
         if (rc == WB_OK && plan->kernel == 0)
-            return fail(WB_ERR_UNSUPPORTED, "GEMM_TC_PAIR needs a GPTQ weight, M >= 128, N >= 256 and a dense local result");
+            return fail(WB_ERR_UNSUPPORTED, "GEMM_TC_PAIR needs a GPTQ weight, M >= 128 and N >= 256");
         return rc;
     }
     case WB_KERNEL_GENERIC:
