@@ -194,6 +194,10 @@ __device__ __forceinline__ void pdl_sync()
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
 }
+// The two halves, for kernels whose roles reach the dependence at different points (a producer that requests constant
+// weights first, warps that only ever touch shared memory, an epilogue that must not store before its predecessor is done).
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 // WEBLLM_B200_NO_PDL=1 in the environment launches every kernel fully serialised (for A/B timing).
 inline bool pdl_enabled()

@@ -161,7 +161,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     cluster_sync_all();  // the other CTA's barriers are initialised before anything arrives on them
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    pdl_sync();
+    // Programmatic dependent launch: the packed weights are constants, so their first boxes are requested (and unpacked)
+    // while the kernel before this one still runs; only the activation loads and the result stores wait for it.
+    pdl_trigger();
 
     const int unpack_idx = unpack_index(warp);
     if (warp == TMA_WARP) {
@@ -170,13 +172,26 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             int s = 0;
             uint32_t ph = 0;
             bool ok = true;
+            // weight boxes of the first STAGES k-blocks (fresh stages, nothing to wait for), then the dependence
+            int pre = 0;
+            for (int ti = 0; ti < items_cta && pre < STAGES; ti++) {
+                const int n0 = item_n0(ti), kb0 = item_kb0(ti), kbn = item_kbn(ti);
+                for (int kb = 0; kb < kbn && pre < STAGES; kb++, pre++) {
+                    mbar_expect_tx(&full_w[pre], S::WP_BYTES);
+                    tma_load_2d(wp(pre), &map_w, n0, (kb0 + kb) * 8, &full_w[pre]);
+                }
+            }
+            pdl_wait();
+            int seq = 0;
             for (int ti = 0; ti < items_cta && ok; ti++) {
                 const int m0 = item_m0(ti) + (int)rank * (MT / 2), n0 = item_n0(ti), kb0 = item_kb0(ti), kbn = item_kbn(ti);
-                for (int kb = 0; kb < kbn; kb++) {
+                for (int kb = 0; kb < kbn; kb++, seq++) {
                     ok = mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 1);
                     if (!ok) break;
-                    mbar_expect_tx(&full_w[s], S::WP_BYTES);
-                    tma_load_2d(wp(s), &map_w, n0, (kb0 + kb) * 8, &full_w[s]);
+                    if (seq >= pre) {
+                        mbar_expect_tx(&full_w[s], S::WP_BYTES);
+                        tma_load_2d(wp(s), &map_w, n0, (kb0 + kb) * 8, &full_w[s]);
+                    }
                     if (rank == 0) mbar_expect_tx(&ready[s], 2 * S::X_BYTES);
                     tma_load_2d_pairbar(xs(s), &map_x, (kb0 + kb) * BK, m0, cluster_map_shared(&ready[s], 0));
                     if (++s == STAGES) s = 0, ph ^= 1;
@@ -317,6 +332,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         const uint32_t acc_empty0 = cluster_map_shared(&acc_empty[0], 0);
         bool ok = true;
         int stg_sel = 0;
+        pdl_wait();  // nothing is stored before the kernel before this one is done with its reads and writes
         for (int ti = 0; ti < items_cta && ok; ti++) {
             const int buf = ti & 1, use = ti >> 1;
             ok = mbar_wait_idle(&acc_full[buf], (uint32_t)use & 1u, abort_flag, p.status, 5);

@@ -92,21 +92,33 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     // Everything above (barriers, TMEM) ran under the tail of the previous kernel when this one was launched with
-    // programmatic stream serialization; nothing that the previous kernel writes or reads is touched before this point.
-    pdl_sync();
+    // programmatic stream serialization. The weights are constants: their first boxes are requested before the wait
+    // on that kernel; the activation loads and the result stores come after it.
+    pdl_trigger();
 
     bool ok = true;
     if (warp == TMA_WARP) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
+            auto load_w = [&](int s, int kb) {
+                if constexpr (DENSE) tma_load_2d(wd(s), &map_w, kb * BK, n0, &full[s]);
+                else tma_load_2d(wp(s), &map_w, n0, kb * 8, &full[s]);
+            };
+            int pre = 0;
+            for (int kb = kb0; kb < KB && pre < STAGES; kb++, pre++) {  // fresh stages: nothing to wait for
+                mbar_expect_tx(&full[pre], S::X_BYTES + (DENSE ? S::WD_BYTES : S::WP_BYTES));
+                load_w(pre, kb);
+            }
+            pdl_wait();
             int s = 0;
             uint32_t ph = 0;
             for (int kb = kb0; kb < KB; kb++) {
                 if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 1)) break;
-                mbar_expect_tx(&full[s], S::X_BYTES + (DENSE ? S::WD_BYTES : S::WP_BYTES));
+                if (kb - kb0 >= pre) {
+                    mbar_expect_tx(&full[s], S::X_BYTES + (DENSE ? S::WD_BYTES : S::WP_BYTES));
+                    load_w(s, kb);
+                }
                 tma_load_2d(xs(s), &map_x, kb * BK, m0, &full[s]);
-                if constexpr (DENSE) tma_load_2d(wd(s), &map_w, kb * BK, n0, &full[s]);
-                else tma_load_2d(wp(s), &map_w, n0, kb * 8, &full[s]);
                 if (++s == STAGES) s = 0, ph ^= 1;
             }
         }
@@ -225,6 +237,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     // TMEM lanes 32 * (w % 4) .. + 31; the warps of a lane quarter (six for quarter 0, five for the others) take the
     // 16-token blocks of the accumulator in turn
     ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;  // the single-thread roles report for their warp
+    pdl_wait();  // nothing is stored before the kernel before this one is done
     {
         if (ok) ok = mbar_wait(acc_full, 0, abort_flag, p.status, 5);
         if (ok) {
@@ -334,24 +347,37 @@ gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     // Everything above (barriers, TMEM) ran under the tail of the previous kernel when this one was launched with
-    // programmatic stream serialization; nothing that the previous kernel writes or reads is touched before this point.
-    pdl_sync();
+    // programmatic stream serialization; the first weight boxes are requested before the wait on that kernel, the
+    // activation loads and the result stores come after it.
+    pdl_trigger();
 
     if (warp == TMA_WARP) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
-            int s = 0;
+            auto load_w = [&](int s, int kb, int n0) {
+                if constexpr (DENSE) tma_load_2d(wd(s), &map_w, kb * BK, n0, &full[s]);
+                else tma_load_2d(wp(s), &map_w, n0, kb * 8, &full[s]);
+            };
+            int pre = 0;
+            for (int ti = 0; ti < tiles_cta && pre < STAGES; ti++)
+                for (int kb = 0; kb < KBt && pre < STAGES; kb++, pre++) {  // fresh stages: nothing to wait for
+                    mbar_expect_tx(&full[pre], S::X_BYTES + (DENSE ? S::WD_BYTES : S::WP_BYTES));
+                    load_w(pre, kb, tile_n0(ti));
+                }
+            pdl_wait();
+            int s = 0, seq = 0;
             uint32_t ph = 0;
             bool ok = true;
             for (int ti = 0; ti < tiles_cta && ok; ti++) {
                 const int m0 = tile_m0(ti), n0 = tile_n0(ti);
-                for (int kb = 0; kb < KBt; kb++) {
+                for (int kb = 0; kb < KBt; kb++, seq++) {
                     ok = mbar_wait(&empty[s], ph ^ 1, abort_flag, p.status, 1);
                     if (!ok) break;
-                    mbar_expect_tx(&full[s], S::X_BYTES + (DENSE ? S::WD_BYTES : S::WP_BYTES));
+                    if (seq >= pre) {
+                        mbar_expect_tx(&full[s], S::X_BYTES + (DENSE ? S::WD_BYTES : S::WP_BYTES));
+                        load_w(s, kb, n0);
+                    }
                     tma_load_2d(xs(s), &map_x, kb * BK, m0, &full[s]);
-                    if constexpr (DENSE) tma_load_2d(wd(s), &map_w, kb * BK, n0, &full[s]);
-                    else tma_load_2d(wp(s), &map_w, n0, kb * 8, &full[s]);
                     if (++s == STAGES) s = 0, ph ^= 1;
                 }
             }
@@ -484,6 +510,7 @@ gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
         // ------------------------------------------------------------------ epilogue: warp w drains TMEM lanes 32 * (w % 4) ..
         const int q = warp & 3;
         bool ok = true;
+        pdl_wait();  // nothing is stored before the kernel before this one is done
         for (int ti = 0; ti < tiles_cta && ok; ti++) {
             const int buf = ti % NBUF, use = ti / NBUF;
             ok = mbar_wait_idle(&acc_full[buf], (uint32_t)use & 1u, abort_flag, p.status, 5);
