@@ -130,8 +130,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             int s = 0;
             uint32_t ph = 0;
             for (int kb = kb0; kb < KB && ok; kb++) {
-                ok = mbar_wait(&full[s], ph, abort_flag, p.status, 2);
-                if (ok && !DENSE) ok = mbar_wait(&deq[s], ph, abort_flag, p.status, 3);
+                // the unpack sets waited for the stage's boxes themselves: their barrier covers both
+                ok = DENSE ? mbar_wait(&full[s], ph, abort_flag, p.status, 2) : mbar_wait(&deq[s], ph, abort_flag, p.status, 3);
                 if (!ok) break;
                 tc_fence_after();
                 const uint64_t a0 = smem_desc_sw128(smem_u32(wd(s)));
@@ -396,8 +396,7 @@ gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
                 tc_fence_after();
                 const uint32_t acc = tmem_base + (uint32_t)buf * ACC_ALL;
                 for (int kb = 0; kb < KBt; kb++) {
-                    ok = mbar_wait(&full[s], ph, abort_flag, p.status, 2);
-                    if (ok && !DENSE) ok = mbar_wait(&deq[s], ph, abort_flag, p.status, 3);
+                    ok = DENSE ? mbar_wait(&full[s], ph, abort_flag, p.status, 2) : mbar_wait(&deq[s], ph, abort_flag, p.status, 3);
                     if (!ok) break;
                     tc_fence_after();
                     const uint64_t a0 = smem_desc_sw128(smem_u32(wd(s)));
