@@ -34,7 +34,8 @@ struct Smem {
     static constexpr int WD_BYTES = COLS * BK * 2;
     static constexpr int WP_BYTES = DENSE ? 0 : 8 * COLS * 4;
     static constexpr int STAGE_BYTES = X_BYTES + WD_BYTES + WP_BYTES;  // every piece is a multiple of 1024
-    static constexpr int STAGES = (4 * STAGE_BYTES + 1280 <= 227 * 1024) ? 4 : 3;
+    static constexpr int FIT = (227 * 1024 - 1280) / STAGE_BYTES;
+    static constexpr int STAGES = FIT > 8 ? 8 : FIT;  // small tiles are latency-bound: as deep as the barrier area allows
     static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
     static_assert(TOTAL <= 227 * 1024, "tile does not fit the shared memory of one CTA");
     
@@ -713,7 +714,7 @@ static double pick_plan(int64_t M, int64_t N, int kblocks, int sms, int force_sp
         for (int nh = 1; nh <= 2; nh++) {
             if (force_nh && nh != force_nh && mt >= 128 && N >= 256) continue;  // pinned wherever it exists
             if (nh == 2 && (mt < 128 || N < 256)) continue;
-            const double t_kb = nh == 2 ? (mt == 256 ? 0.89 : mt == 192 ? 0.84 : 0.80) : (mt == 256 ? 0.56 : mt == 192 ? 0.52 : 0.45);
+            const double t_kb = nh == 2 ? (mt == 256 ? 0.89 : mt == 192 ? 0.84 : 0.80) : (mt == 256 ? 0.54 : mt == 192 ? 0.48 : mt == 128 ? 0.33 : 0.25);
             const double t_tile = 1.5 + 2.7 * nh * mt / 256.;
             const int64_t tiles = ((M + mt - 1) / mt) * ((N + 128 * nh - 1) / (128 * nh));
             for (int S = 1; S <= 16; S++) {
@@ -732,7 +733,7 @@ static double pick_plan(int64_t M, int64_t N, int kblocks, int sms, int force_sp
                 // a column-sharded call also stores the result into the peers: under the next tile's MMAs in the
                 // persistent loop, at the end of every CTA (on top of the arithmetic) otherwise
                 if (t_remote > 0.) t = persist ? (t > t_remote ? t : t_remote) : t + t_remote;
-                if (S > 1) t += 2.5 + (S + 1) * (double)M * N * 4. / 4e6;
+                if (S > 1) t += 1.5 + (S + 1) * (double)M * N * 4. / 5e6;
                 if (best < 0. || t < best) best = t, *mt_out = mt, *nh_out = nh, *s_out = S;
             }
         }
@@ -763,7 +764,7 @@ static double pick_plan_pair(int64_t M, int64_t N, int kblocks, int sms, int for
             if (S > 1 && (double)S * M * N * 4. > 64e6) continue;
             const int64_t rounds = (tiles * S + pairs - 1) / pairs;
             double t = 3.3 + t_tile + rounds * (per * t_kb + kPairItem);
-            if (S > 1) t += 2.5 + (S + 1) * (double)M * N * 4. / 4e6;
+            if (S > 1) t += 1.5 + (S + 1) * (double)M * N * 4. / 5e6;
             if (best < 0. || t < best) best = t, *mt_out = mt, *s_out = S;
         }
     }
