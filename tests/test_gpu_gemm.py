@@ -102,6 +102,39 @@ def test_gemm_pair_kernel(gpu, oracle, name, K, N, M, split):
         gpu.plan_override(0, 0)
 
 
+@pytest.mark.parametrize("M", [4096, 4000])
+def test_gemm_pair_last_round_cut_along_k(gpu, oracle, M):
+    """3584 -> 3584 at M ~ 4096 is 224 work items of 256 x 256 for 74 CTA pairs: three whole rounds and 2 items left over.
+    The launch cuts those 2 along K (28 slices of 2 k-blocks, one per otherwise idle pair) and a second small launch adds
+    the slices; the plan shows the extra launch and its scratch, and every column (the leftover items are the last 256
+    columns of the last two token tiles) matches the oracle, with a bias, for f32 and fp16 results and with a ragged
+    last token tile."""
+    K = N = 3584
+    h, W16 = _weight(gpu, oracle, "q7", K, N, zeros="7or8")
+    bias = np.random.default_rng(N).standard_normal(N).astype(np.float32)
+    try:
+        hb = gpu.weight("tcb_q7")
+    except WebllmError:
+        hb = gpu.f32_upload("tcb_q7", bias)
+    x16 = np.random.default_rng(M).standard_normal((M, K)).astype(np.float16)
+    gpu.plan_override(_lib.WB_KERNEL_GEMM_TC_PAIR, 0)
+    try:
+        p = gpu.plan(h, M, "f16")
+        assert p["kernel_name"] == "gemm_tc_pair" and p["split_k"] == 1
+        if p["tile_m"] == 256:  # 148 SMs: 74 pairs, one partial tile each
+            assert p["launches"] == 2 and p["scratch_bytes"] == 74 * 256 * 256 * 4
+        got = run_linear(gpu, h, x16, M, N, hb, act="f16")
+        gpu.synchronize()
+        rows = sorted(set(np.random.default_rng(3).integers(0, M, 24).tolist()) | {0, 3583, 3584, 3839, 3840, M - 1})
+        assert_close(oracle, got[rows], _ref_rows(oracle, x16, W16, rows, bias), F16_RTOL, f"pair tail M={M}")
+        got16 = run_linear(gpu, h, x16, M, N, hb, act="f16", out="f16")
+        assert np.array_equal(got16.astype(np.float16).view(np.uint16), got.astype(np.float16).view(np.uint16))
+        again = run_linear(gpu, h, x16, M, N, hb, act="f16")
+        assert np.array_equal(got.view(np.uint32), again.view(np.uint32))
+    finally:
+        gpu.plan_override(0, 0)
+
+
 def test_gemm_pair_kernel_refuses_what_it_cannot_do(gpu, oracle):
     h, _ = _weight(gpu, oracle, "k", 896, 128)
     gpu.plan_override(_lib.WB_KERNEL_GEMM_TC_PAIR, 0)

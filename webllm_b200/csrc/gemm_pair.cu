@@ -98,12 +98,21 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr)
 {
     asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
 }
+// The last, partly filled round of work items (items % pairs of them) would leave most pairs idle for a whole item. With
+// `slots` > 0 those items are cut along K instead: every pair runs `rounds` whole items and then at most one K slice
+// (`per` k-blocks, `St` slices per item) of a leftover item, whose f32 partial tile it writes to partial[pair]; a
+// small launch adds the slices. Whole items are unaffected.
+struct PairTail {
+    int rounds = 0, slots = 0, St = 1, per = 0;
+    float *partial = nullptr;  // [slots][MT][256]
+};
+
 // GATHER: the result goes to the placement in Params (this GPU's slab and its peers', row pitch ld_out) from registers.
 template <int MT, bool SPLIT, bool STG, bool GATHER = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS_PAIR, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                  const __grid_constant__ CUtensorMap map_c, const Params p, const int tiles_m, const int tiles_n, const int n_items,
-                 const int use_tma_store)
+                 const int use_tma_store, const PairTail tail)
 {
     using S = SmemPair<MT, STG>;
     constexpr int STAGES = S::STAGES;
@@ -125,17 +134,22 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     const uint32_t rank = cluster_cta_rank();           // 0 issues the MMAs
     const int pair = (int)blockIdx.x >> 1, n_pairs = (int)gridDim.x >> 1;
     const int KB = p.K / BK;
-    const int items_cta = pair < n_items ? (n_items - pair + n_pairs - 1) / n_pairs : 0;
+    const bool tail_on = !SPLIT && tail.slots > 0;
+    const int items_cta = tail_on ? tail.rounds + (pair < tail.slots ? 1 : 0)
+                                  : pair < n_items ? (n_items - pair + n_pairs - 1) / n_pairs : 0;
     const int tiles_mn = tiles_m * tiles_n;
     // work item ti of this pair: K slice, first token, this CTA's first column, k-blocks
-    auto item_slice = [&](int ti) { return (pair + ti * n_pairs) / tiles_mn; };
-    auto item_m0 = [&](int ti) { return ((pair + ti * n_pairs) % tiles_mn % tiles_m) * MT; };
-    auto item_n0 = [&](int ti) { return ((pair + ti * n_pairs) % tiles_mn / tiles_m) * (2 * BN) + (int)rank * BN; };
-    auto item_kb0 = [&](int ti) { return SPLIT ? item_slice(ti) * p.kb_per_slice : 0; };
+    auto is_tail = [&](int ti) { return tail_on && ti == tail.rounds; };
+    auto item_index = [&](int ti) { return is_tail(ti) ? tail.rounds * n_pairs + pair / tail.St : pair + ti * n_pairs; };
+    auto item_slice = [&](int ti) { return item_index(ti) / tiles_mn; };
+    auto item_m0 = [&](int ti) { return (item_index(ti) % tiles_mn % tiles_m) * MT; };
+    auto item_n0 = [&](int ti) { return (item_index(ti) % tiles_mn / tiles_m) * (2 * BN) + (int)rank * BN; };
+    auto item_kb0 = [&](int ti) { return SPLIT ? item_slice(ti) * p.kb_per_slice : is_tail(ti) ? (pair % tail.St) * tail.per : 0; };
     auto item_kbn = [&](int ti) {
-        if (!SPLIT) return KB;
-        const int left = KB - item_slice(ti) * p.kb_per_slice;
-        return left < p.kb_per_slice ? left : p.kb_per_slice;
+        if (!SPLIT && !is_tail(ti)) return KB;
+        const int per = SPLIT ? p.kb_per_slice : tail.per;
+        const int left = KB - item_kb0(ti);
+        return left < per ? left : per;
     };
 
     auto xs = [&](int s) { return smem + s * S::STAGE_BYTES; };
@@ -363,7 +377,18 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             const int n_warp = n0 + q * 32;
             const int n = n_warp + lane;
             const float bias = (!SPLIT && p.bias && n < p.N) ? p.bias[n] : 0.f;
-            if (!STG || !use_tma_store) {
+            if (is_tail(ti)) {
+                // a K slice of a leftover item: the f32 partial tile [MT][256] of this pair, no bias
+                StoreDst dt;
+                dt.dst[0] = tail.partial + (size_t)pair * MT * (2 * BN), dt.n_dst = 1, dt.ld = 2 * BN, dt.col0 = 0;
+#pragma unroll 1
+                for (int c = 0; c < MT; c += 16) {
+                    uint32_t r[16];
+                    tmem_ld_32x32b_x16(acc + (uint32_t)c, r);
+                    tmem_ld_wait();
+                    store_block16<false>(dt, false, true, r, 0.f, c, MT, (int)rank * BN + q * 32, 2 * BN, lane);
+                }
+            } else if (!STG || !use_tma_store) {
 #pragma unroll 1
                 for (int c = 0; c < MT; c += 16) {
                     uint32_t r[16];
@@ -427,7 +452,57 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     if (warp == MMA_WARP) tmem_dealloc_pair(tmem_base, TMEM_COLS);
 }
 
+// Adds the K slices of the leftover items (PairTail) and stores the tiles: grid (MT rows, leftover items) x 64 threads
+// of four columns each.
+__global__ void __launch_bounds__(64) pair_tail_reduce_kernel(const float *__restrict__ partial, const int St, const int first_item,
+                                                              const int tiles_m, const int MT, const float *__restrict__ bias,
+                                                              void *__restrict__ out, const int out_f16, const int M, const int N)
+{
+    const int r = blockIdx.x, t = blockIdx.y, item = first_item + t;
+    const int m = (item % tiles_m) * MT + r, n = (item / tiles_m) * (2 * BN) + (int)threadIdx.x * 4;
+    pdl_sync();
+    if (m >= M || n >= N) return;  // N % 4 == 0
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < St; s++) {
+        const float4 a = *reinterpret_cast<const float4 *>(partial + (((size_t)(t * St + s) * MT + r) * (2 * BN) + threadIdx.x * 4));
+        v.x += a.x, v.y += a.y, v.z += a.z, v.w += a.w;
+    }
+    if (bias) {
+        const float4 b = *reinterpret_cast<const float4 *>(bias + n);
+        v.x += b.x, v.y += b.y, v.z += b.z, v.w += b.w;
+    }
+    const size_t o = (size_t)m * N + n;
+    if (out_f16) {
+        const __half2 a = __floats2half2_rn(v.x, v.y), b = __floats2half2_rn(v.z, v.w);
+        uint2 w;
+        w.x = *reinterpret_cast<const uint32_t *>(&a), w.y = *reinterpret_cast<const uint32_t *>(&b);
+        *reinterpret_cast<uint2 *>((__half *)out + o) = w;
+    } else {
+        *reinterpret_cast<float4 *>((float *)out + o) = v;
+    }
+}
+
 }  // namespace tcp
+
+// How a launch of n_items whole items on `pairs` pairs cuts its last round (see PairTail). False: no cut (the items
+// fill the rounds, or the leftover is more than half a round, or K is too short to slice).
+bool pair_tail_plan(int64_t n_items, int pairs, int kblocks, int *rounds, int *rem, int *St, int *per)
+{
+    static const bool on = [] { const char *e = getenv("WEBLLM_B200_GEMM_TAIL"); return !(e && e[0] == '0'); }();
+    if (!on || pairs < 2 || n_items <= pairs || kblocks < 8) return false;
+    *rounds = (int)(n_items / pairs), *rem = (int)(n_items % pairs);
+    if (*rem == 0 || 2 * *rem > pairs) return false;
+    int st = pairs / *rem;
+    int pr = (kblocks + st - 1) / st;
+    if (pr < 2) pr = 2;
+    st = (kblocks + pr - 1) / pr;
+    if (st < 2) return false;
+    // the cut costs a register epilogue of partial tiles and a second launch (~10 us measured): it pays where the k-blocks
+    // it takes off the critical path are worth more (K = 3584: 20 us; K = 896: 4 us, where it measured 4.5 us slower)
+    if ((kblocks - pr) * 0.37 < 12.) return false;
+    *St = st, *per = pr;
+    return true;
+}
 
 // WEBLLM_B200_GEMM_PAIR=0 keeps every launch on the one-CTA kernels (for comparisons).
 static bool pair_enabled()
@@ -443,7 +518,7 @@ bool gemm_pair_supports(const Weight &w, int64_t M)
 
 template <int MT>
 static cudaError_t launch_pair_mt(const CUtensorMap &mx, const CUtensorMap &mw, const CUtensorMap *mc, const tc::Params &p, int tiles_m,
-                                  int tiles_n, int S, cudaStream_t st, int sms)
+                                  int tiles_n, int S, cudaStream_t st, int sms, const tcp::PairTail &tail)
 {
     static bool attr_set[5][16] = {};
     int dev = 0;
@@ -458,7 +533,7 @@ static cudaError_t launch_pair_mt(const CUtensorMap &mx, const CUtensorMap &mw, 
             if (dev >= 0 && dev < 16) attr_set[variant][dev] = true;
         }
         return launch_pdl(kernel, dim3((unsigned)(2 * pairs)), dim3(tcp::THREADS_PAIR), (size_t)smem, st, mx, mw, mc ? *mc : mx, p, tiles_m,
-                          tiles_n, n_items, mc ? 1 : 0);
+                          tiles_n, n_items, mc ? 1 : 0, tail);
     };
     if (S > 1)
         return mc ? go(tcp::gemm_pair_kernel<MT, true, true>, 3, tcp::SmemPair<MT, true>::TOTAL)
@@ -471,14 +546,29 @@ static cudaError_t launch_pair_mt(const CUtensorMap &mx, const CUtensorMap &mw, 
 // mc: tensor map of the result or of the K slices' partial sums ([slices, M, N], boxes of 128 columns x 64 fp16 or 32 f32
 // rows) for the epilogue's TMA stores, or nullptr (a row pitch that is not a multiple of 16 bytes; a long-K launch that
 // would rather have the shared memory as a pipeline stage): then the epilogue stores from registers.
+// tail_partial: room for sms / 2 partial tiles [mt][256] f32 (the launch cuts its last round along K where that pays, and
+// then also launches the small kernel that adds the slices; *extra_launches says so), or nullptr to never cut.
 cudaError_t launch_gemm_pair(int mt, const CUtensorMap &mx, const CUtensorMap &mw, const CUtensorMap *mc, const tc::Params &p, int tiles_m,
-                             int tiles_n, int S, cudaStream_t st, int sms)
+                             int tiles_n, int S, cudaStream_t st, int sms, float *tail_partial, int *extra_launches)
 {
-    switch (mt) {
-    case 128: return launch_pair_mt<128>(mx, mw, mc, p, tiles_m, tiles_n, S, st, sms);
-    case 192: return launch_pair_mt<192>(mx, mw, mc, p, tiles_m, tiles_n, S, st, sms);
-    default: return launch_pair_mt<256>(mx, mw, mc, p, tiles_m, tiles_n, S, st, sms);
+    tcp::PairTail tail;
+    int rem = 0;
+    *extra_launches = 0;
+    if (S == 1 && p.n_dst == 0 && tail_partial &&
+        pair_tail_plan((int64_t)tiles_m * tiles_n, sms / 2, p.K / tc::BK, &tail.rounds, &rem, &tail.St, &tail.per)) {
+        tail.slots = rem * tail.St;
+        tail.partial = tail_partial;
     }
+    cudaError_t e;
+    switch (mt) {
+    case 128: e = launch_pair_mt<128>(mx, mw, mc, p, tiles_m, tiles_n, S, st, sms, tail); break;
+    case 192: e = launch_pair_mt<192>(mx, mw, mc, p, tiles_m, tiles_n, S, st, sms, tail); break;
+    default: e = launch_pair_mt<256>(mx, mw, mc, p, tiles_m, tiles_n, S, st, sms, tail); break;
+    }
+    if (e != cudaSuccess || tail.slots == 0) return e;
+    *extra_launches = 1;
+    return launch_pdl(tcp::pair_tail_reduce_kernel, dim3((unsigned)mt, (unsigned)rem), dim3(64), 0, st, (const float *)tail.partial, tail.St,
+                      tail.rounds * (sms / 2), tiles_m, mt, p.bias, p.out, p.out_f16, p.M, p.N);
 }
 
 }  // namespace wb

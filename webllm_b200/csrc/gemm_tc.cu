@@ -667,7 +667,8 @@ static int make_map_2d(wb_context *ctx, CUtensorMap *map, CUtensorMapDataType dt
 // gemm_pair.cu
 bool gemm_pair_supports(const Weight &w, int64_t M);
 cudaError_t launch_gemm_pair(int mt, const CUtensorMap &mx, const CUtensorMap &mw, const CUtensorMap *mc, const tc::Params &p, int tiles_m,
-                             int tiles_n, int S, cudaStream_t st, int sms);
+                             int tiles_n, int S, cudaStream_t st, int sms, float *tail_partial, int *extra_launches);
+bool pair_tail_plan(int64_t n_items, int pairs, int kblocks, int *rounds, int *rem, int *St, int *per);
 
 bool gemm_tc_supports(const Weight &w, int64_t M)
 {
@@ -743,7 +744,7 @@ static double pick_plan(int64_t M, int64_t N, int kblocks, int sms, int force_sp
 
 // The same model for the CTA-pair kernel (gemm_pair.cu): work items of mt tokens x 256 columns x one K slice, walked by
 // sms / 2 persistent pairs; fill, drain and stores are paid once per pair.
-static double pick_plan_pair(int64_t M, int64_t N, int kblocks, int sms, int force_split, int *mt_out, int *s_out)
+static double pick_plan_pair(int64_t M, int64_t N, int kblocks, int sms, int force_split, bool tail_ok, int *mt_out, int *s_out)
 {
     static const int force_mt = env_int("WEBLLM_B200_GEMM_MT"), env_split = env_int("WEBLLM_B200_GEMM_SPLIT");
     if (force_split <= 0) force_split = env_split;
@@ -764,6 +765,9 @@ static double pick_plan_pair(int64_t M, int64_t N, int kblocks, int sms, int for
             if (S > 1 && (double)S * M * N * 4. > 64e6) continue;
             const int64_t rounds = (tiles * S + pairs - 1) / pairs;
             double t = 3.3 + t_tile + rounds * (per * t_kb + kPairItem);
+            int tr, trem, tst, tper;
+            if (S == 1 && tail_ok && pair_tail_plan(tiles, pairs, kblocks, &tr, &trem, &tst, &tper))  // the last round cut along K
+                t = 3.3 + t_tile + tr * (per * t_kb + kPairItem) + (tper * t_kb + kPairItem) + 3.0;
             if (S > 1) t += 1.5 + (S + 1) * (double)M * N * 4. / 5e6;
             if (best < 0. || t < best) best = t, *mt_out = mt, *s_out = S;
         }
@@ -787,7 +791,7 @@ int plan_gemm_tc(wb_context *ctx, const Weight &w, int64_t M, int act_dtype, int
     if (pair_mode == 2 && !pair_ok) return WB_OK;
     if (pair_ok) {
         int pmt, pS;
-        double t_pair = pick_plan_pair(M, w.N, kblocks, ctx->sm_count, ctx->force_split, &pmt, &pS);
+        double t_pair = pick_plan_pair(M, w.N, kblocks, ctx->sm_count, ctx->force_split, ctx->place.n_dst == 0, &pmt, &pS);
         if (t_remote > 0. && pS == 1 && t_pair < t_remote) t_pair = t_remote;  // the stores to the peers run under the MMAs
         if (pair_mode == 2 || (t_pair > 0. && t_pair < t_one)) {
             plan->kernel = WB_KERNEL_GEMM_TC_PAIR;
@@ -811,8 +815,13 @@ int plan_gemm_tc(wb_context *ctx, const Weight &w, int64_t M, int act_dtype, int
         plan->tile_n = 128 * nh;
     }
     const uint64_t stage_bytes = act_dtype == WB_F32 ? align_up((uint64_t)M * w.K * 2) : 0;
-    plan->launches = (act_dtype == WB_F32 ? 2 : 1) + (S > 1 ? 1 : 0);
-    plan->scratch_bytes = stage_bytes + (S > 1 ? (uint64_t)S * M * w.N * 4 : 0);
+    // a pair launch that cuts its last round along K (PairTail, gemm_pair.cu) parks one partial tile per pair and adds a launch
+    int tr, trem, tst, tper;
+    const bool pair_tail = plan->kernel == WB_KERNEL_GEMM_TC_PAIR && S == 1 && ctx->place.n_dst == 0 &&
+                           pair_tail_plan((int64_t)plan->grid_x * plan->grid_y, ctx->sm_count / 2, kblocks, &tr, &trem, &tst, &tper);
+    plan->launches = (act_dtype == WB_F32 ? 2 : 1) + (S > 1 || pair_tail ? 1 : 0);
+    plan->scratch_bytes = stage_bytes + (S > 1 ? (uint64_t)S * M * w.N * 4 : 0) +
+                          (pair_tail ? (uint64_t)(ctx->sm_count / 2) * mt * 256 * 4 : 0);
     if (plan->scratch_bytes > kWorkspaceBytes)
         return fail(WB_ERR_OOM, "fp16 staging of %lld x %lld activations exceeds the workspace; pass fp16 activations or split M",
                     (long long)M, (long long)w.K);
@@ -946,7 +955,10 @@ int launch_gemm_tc(wb_context *ctx, const Weight &w, const void *A, void *C, con
                                                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
                 if (r != CUDA_SUCCESS) return fail(WB_ERR_CUDA, "cuTensorMapEncodeTiled (result) failed with code %d", (int)r);
             }
-            e = launch_gemm_pair(mt, mx, mw, tma_store ? &mc : nullptr, p, plan.grid_x, plan.grid_y, S, ctx->stream, ctx->sm_count);
+            int extra = 0;
+            e = launch_gemm_pair(mt, mx, mw, tma_store ? &mc : nullptr, p, plan.grid_x, plan.grid_y, S, ctx->stream, ctx->sm_count,
+                                 S == 1 ? p.partial : nullptr, &extra);
+            ctx->launches += (uint64_t)extra;
         } else {
             e = launch_tc_mt<false>(mt, nh, mx, mw, p, grid, ctx->stream, ctx->sm_count);
         }
