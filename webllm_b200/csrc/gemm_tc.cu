@@ -6,18 +6,21 @@
 // One CTA computes a (128 * NH output columns n) x (MT tokens m) tile of C^T, NH = 1 or 2: each 128-column half of
 // the weight tile is the 128-row operand of a tcgen05.mma, the activation tile the MT-column operand both halves
 // share, and each half has its f32 accumulator in TMEM (128 lanes x MT columns). With NH = 2 an activation tile
-// fetched from L2 feeds twice the arithmetic. Roles, 18 warps:
-//   warp 0      TMA producer: per 64-k block one box of activations [MT x 64] fp16 (128-byte swizzle) and
-//               one box of packed weights [8 packed rows x 128 * NH columns] int32, into a ring of 4 stages
-//               (3 when 4 do not fit the shared memory).
-//   warp 1      allocates TMEM, then one elected lane issues 4 x NH tcgen05.mma (K = 16 each) per block and
-//               commits the stage back to the producer.
-//   warps 2-17  unpack, in 4 / NH sets of one thread per column that take the k-blocks in turn: a thread turns
+// fetched from L2 feeds twice the arithmetic. Roles, 21 warps (which warp id has which role, and why, is at MMA_WARP in
+// gemm_tc.cuh: the issuing warp shares its warp scheduler with no unpack warp):
+//   TMA warp    producer: per 64-k block one box of activations [MT x 64] fp16 (128-byte swizzle) and one box of
+//               packed weights [8 packed rows x 128 * NH columns] int32, into a ring of up to 8 stages (as many as
+//               fit the shared memory). The weight boxes of the first stages are requested before the wait on the
+//               previous kernel (the weights are constants), the activation boxes after it.
+//   MMA warp    allocates TMEM, then one elected lane issues 4 x NH tcgen05.mma (K = 16 each) per block, after ONE
+//               wait (the unpack sets' barrier, which covers the boxes), and commits the stage back to the producer.
+//   16 unpack   warps, in 4 / NH sets of one thread per column that take the k-blocks in turn: a thread turns
 //               the 8 words of its column into 64 fp16 values w = (q - zero) * scale (exact integer in fp16, one
 //               rounding in the multiply: the fp16 weight the reference uploads, src/gpu/buffer.ts:103-120) and
 //               stores them as the K-major, 128-byte-swizzled operand tile; the scale and zero point of the
-//               set's next k-block are requested while the current one is unpacked. Afterwards the same warps
-//               drain TMEM (tcgen05.ld), add the bias and store.
+//               set's next k-block are requested while the current one is unpacked.
+//   epilogue    all 21 warps drain TMEM (tcgen05.ld, the lane quarter id % 4), add the bias and store, after the wait
+//               on the previous kernel.
 // With the unpack's work left out the rest of the kernel runs at 0.84 of the cuBLAS fp16 rate; with it, at 0.82.
 // Every wait on an mbarrier is bounded: when a wait gives up it raises a CTA-wide abort flag, records a
 // code in the context's status word, and all roles fall through to the common exit where TMEM is freed.
@@ -290,7 +293,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 // boundaries, the accumulators are double-buffered in TMEM wherever two sets fit its 512 columns, and four warps of
 // their own drain a finished accumulator while the MMAs of the next tile are issued: pipeline fill, TMEM drain and
 // the stores (to peers too, in a column-sharded call) leave the critical path of every tile but the last.
-// Roles, 22 warps: 0 = TMA, 1 = MMA, 2-17 = unpack (as above), 18-21 = epilogue (TMEM lane quarter warp % 4).
+// Roles as above plus four epilogue warps (ids 21 .. 24, TMEM lane quarter id % 4): 25 warps.
 constexpr int EPI_WARPS = 4;         // warps 21 .. 24, after the roles listed at MMA_WARP
 constexpr int THREADS_P = 32 * (WARPS + EPI_WARPS);
 
