@@ -36,6 +36,8 @@ struct wb_qwen {
     int *d_cache_len = nullptr, *d_step = nullptr, *d_bidx = nullptr;
     float *d_bval = nullptr, *att_scratch = nullptr;
     unsigned *att_counters = nullptr;
+    uint32_t *host_pin = nullptr;  // pinned host buffer the sampled ids come back through
+    size_t host_pin_cap = 0;
     uint32_t *d_history = nullptr;
     int64_t history_cap = 0;
     cudaGraphExec_t graph = nullptr;

@@ -305,6 +305,8 @@ int wb_qwen_create(wb_context *ctx, const wb_qwen_config *cfg, wb_qwen **out)
         WB_CUDA(cudaMemcpyAsync(m->cs_table, cs.data(), cs.size() * 4, cudaMemcpyHostToDevice, ctx->stream));
         WB_CHECK(alloc_bufs(m.get(), WB_ARENA_WEIGHTS, 1, 1, &m->dec));
         m->history_cap = cfg->max_t;
+        m->host_pin_cap = (size_t)cfg->max_t;
+        WB_CUDA(cudaHostAlloc((void **)&m->host_pin, m->host_pin_cap * sizeof(uint32_t), cudaHostAllocDefault));
         WB_CHECK(carve_t(ctx, WB_ARENA_WEIGHTS, (uint64_t)m->history_cap, &m->d_history));
         WB_CHECK(carve_t(ctx, WB_ARENA_WEIGHTS, 64, &m->d_cache_len));
         m->d_step = m->d_cache_len + 1;
@@ -319,6 +321,7 @@ int wb_qwen_create(wb_context *ctx, const wb_qwen_config *cfg, wb_qwen **out)
     }();
     if (rc != WB_OK) {
         cudaStreamSynchronize(ctx->stream);
+        if (m->host_pin) cudaFreeHost(m->host_pin);
         ctx->arena[WB_ARENA_WEIGHTS].used = m->carve_mark;
         return rc;
     }
@@ -336,6 +339,7 @@ int wb_qwen_destroy(wb_qwen *m)
     // the model's carve is handed back when it still is the top of the weight arena
     ArenaState &wa = m->ctx->arena[WB_ARENA_WEIGHTS];
     if (wa.used == m->carve_top) wa.used = m->carve_mark;
+    if (m->host_pin) cudaFreeHost(m->host_pin);
     delete m;
     return WB_OK;
 }
@@ -413,6 +417,11 @@ int wb_qwen_decode_step(wb_qwen *m, uint32_t token, uint64_t *logits_offset)
     return run_eager(m, &token, 1, 1, 1, m->cache_len, true, true, logits_offset);
 }
 
+__global__ void set_decode_state_kernel(int *cache_len, int *step, uint32_t *tokens, int len, uint32_t first_token)
+{
+    *cache_len = len, *step = 0, *tokens = first_token;
+}
+
 // One decode step on the persistent M = 1 buffers, positions read from device memory, followed by the
 // on-device argmax that also appends the token and bumps the cache length.
 static int enqueue_graph_step(wb_qwen *m)
@@ -431,9 +440,15 @@ int wb_qwen_decode_greedy(wb_qwen *m, uint32_t first_token, int64_t n_steps, uin
     if (m->cache_len + n_steps > m->cfg.max_t)
         return fail(WB_ERR_BAD_ARG, "上下文长度 %lld 超过 blockSize=%d", (long long)(m->cache_len + n_steps), m->cfg.max_t);
     WB_CHECK(check_tokens(m, &first_token, 1));
-    const int state[2] = {(int)m->cache_len, 0};
-    WB_CUDA(cudaMemcpyAsync(m->d_cache_len, state, sizeof state, cudaMemcpyHostToDevice, ctx->stream));
-    WB_CUDA(cudaMemcpyAsync(m->dec.tokens, &first_token, 4, cudaMemcpyHostToDevice, ctx->stream));
+    // the decode state (cache length, step counter, first token) goes to the device as the arguments of one tiny kernel:
+    // no staging of pageable host memory on the per-token path
+    auto set_state = [&]() -> int {
+        set_decode_state_kernel<<<1, 1, 0, ctx->stream>>>(m->d_cache_len, m->d_step, m->dec.tokens, (int)m->cache_len, first_token);
+        ctx->launches++;
+        WB_CUDA(cudaGetLastError());
+        return WB_OK;
+    };
+    WB_CHECK(set_state());
     if (m->graph && (m->graph_stream != ctx->stream || m->graph_exact != m->exact)) drop_graph(m);
     if (!m->graph) {
         // Warm-up step outside capture (sets kernel attributes, counts the step's kernels), then restore the
@@ -441,8 +456,7 @@ int wb_qwen_decode_greedy(wb_qwen *m, uint32_t first_token, int64_t n_steps, uin
         const uint64_t launches_warm = ctx->launches;
         WB_CHECK(enqueue_graph_step(m));
         m->graph_launches = ctx->launches - launches_warm;
-        WB_CUDA(cudaMemcpyAsync(m->d_cache_len, state, sizeof state, cudaMemcpyHostToDevice, ctx->stream));
-        WB_CUDA(cudaMemcpyAsync(m->dec.tokens, &first_token, 4, cudaMemcpyHostToDevice, ctx->stream));
+        WB_CHECK(set_state());
         WB_CUDA(cudaStreamSynchronize(ctx->stream));
         cudaGraph_t g = nullptr;
         WB_CUDA(cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
@@ -464,8 +478,11 @@ int wb_qwen_decode_greedy(wb_qwen *m, uint32_t first_token, int64_t n_steps, uin
     const uint64_t per_step = m->graph_launches;  // kernels per replayed step, for wb_launch_count
     for (int64_t s = 0; s < n_steps; s++) WB_CUDA(cudaGraphLaunch(m->graph, ctx->stream));
     ctx->launches += per_step * (uint64_t)n_steps;
-    WB_CUDA(cudaMemcpyAsync(out_tokens, m->d_history, (size_t)n_steps * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    // the sampled ids come back through pinned memory (a pageable destination would be staged by the driver)
+    uint32_t *back = n_steps <= (int64_t)m->host_pin_cap ? m->host_pin : out_tokens;
+    WB_CUDA(cudaMemcpyAsync(back, m->d_history, (size_t)n_steps * 4, cudaMemcpyDeviceToHost, ctx->stream));
     WB_CHECK(wb_synchronize(ctx));
+    if (back != out_tokens) memcpy(out_tokens, back, (size_t)n_steps * 4);
     m->cache_len += n_steps;
     return WB_OK;
 }
