@@ -135,6 +135,31 @@ def test_gemm_pair_last_round_cut_along_k(gpu, oracle, M):
         gpu.plan_override(0, 0)
 
 
+@pytest.mark.parametrize("group,zeros", [(64, "any"), (256, "any"), (128, "none"), (64, "sym")])
+@pytest.mark.parametrize("kind", ["gemm_tc", "gemm_tc_pair"])
+def test_gemm_group_sizes_and_zero_modes(gpu, oracle, kind, group, zeros):
+    """Both tensor-core kernels with one and with four k-blocks per group, arbitrary zero points, and a checkpoint
+    without a qzeros tensor (the symmetric default, stored 7); K = 1024, N = 640 (2.5 column tiles of the pair kernel),
+    M = 300."""
+    K, N, M = 1024, 640, 300
+    t = synthetic.random_gptq(K, N, group, seed=group + len(zeros), zeros=zeros)
+    name = f"tc_g{group}_{zeros}"
+    try:
+        h = gpu.weight(name)
+    except WebllmError:
+        h = register(gpu, name, t)
+    W16 = oracle.round_f16(oracle_weight(oracle, t)).reshape(N, K)
+    x16 = np.random.default_rng(group).standard_normal((M, K)).astype(np.float16)
+    gpu.plan_override(_lib.WB_KERNEL_GEMM_TC if kind == "gemm_tc" else _lib.WB_KERNEL_GEMM_TC_PAIR, 0)
+    try:
+        assert gpu.plan(h, M, "f16")["kernel_name"] == kind
+        got = run_linear(gpu, h, x16, M, N, None, act="f16")
+        gpu.synchronize()
+        assert_close(oracle, got, _ref_rows(oracle, x16, W16, list(range(M))), F16_RTOL, f"{kind} g={group} zeros={zeros}")
+    finally:
+        gpu.plan_override(0, 0)
+
+
 def test_gemm_pair_kernel_refuses_what_it_cannot_do(gpu, oracle):
     h, _ = _weight(gpu, oracle, "k", 896, 128)
     gpu.plan_override(_lib.WB_KERNEL_GEMM_TC_PAIR, 0)
