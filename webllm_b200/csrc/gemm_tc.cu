@@ -30,16 +30,16 @@ namespace wb {
 
 namespace tc {
 
-template <int MT, bool DENSE, int NH>
+template <int MT, bool DENSE, int NH, int EXTRA = 0>
 struct Smem {
     static constexpr int COLS = BN * NH;  // output columns per CTA
     static constexpr int X_BYTES = MT * BK * 2;
     static constexpr int WD_BYTES = COLS * BK * 2;
     static constexpr int WP_BYTES = DENSE ? 0 : 8 * COLS * 4;
     static constexpr int STAGE_BYTES = X_BYTES + WD_BYTES + WP_BYTES;  // every piece is a multiple of 1024
-    static constexpr int FIT = (227 * 1024 - 1280) / STAGE_BYTES;
+    static constexpr int FIT = (227 * 1024 - 1280 - EXTRA) / STAGE_BYTES;
     static constexpr int STAGES = FIT > 8 ? 8 : FIT;  // small tiles are latency-bound: as deep as the barrier area allows
-    static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + EXTRA;
     static_assert(TOTAL <= 227 * 1024, "tile does not fit the shared memory of one CTA");
     
 };
@@ -295,6 +295,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 // the stores (to peers too, in a column-sharded call) leave the critical path of every tile but the last.
 // Roles as above plus four epilogue warps (ids 21 .. 24, TMEM lane quarter id % 4): 25 warps.
 constexpr int EPI_WARPS = 4;         // warps 21 .. 24, after the roles listed at MMA_WARP
+constexpr int kGatherStageBytes = 16384;  // staging tile of a column-sharded call's epilogue: [64][128] fp16 or [32][128] f32
 constexpr int THREADS_P = 32 * (WARPS + EPI_WARPS);
 
 template <int MT, bool DENSE, int NH, bool GATHER>
@@ -302,7 +303,7 @@ __global__ void __launch_bounds__(THREADS_P, 1)
 gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, const Params p,
                        const int tiles_m, const int n_tiles)
 {
-    using S = Smem<MT, DENSE, NH>;
+    using S = Smem<MT, DENSE, NH, GATHER ? kGatherStageBytes : 0>;
     constexpr int STAGES = S::STAGES;
     constexpr int COLS = S::COLS;
     constexpr uint32_t ACC_COLS = MT < 32 ? 32 : MT;
@@ -517,7 +518,7 @@ gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
         for (int ti = 0; ti < tiles_cta && ok; ti++) {
             const int buf = ti % NBUF, use = ti / NBUF;
             ok = mbar_wait_idle(&acc_full[buf], (uint32_t)use & 1u, abort_flag, p.status, 5);
-            if (!ok) break;
+            if (!GATHER && !ok) break;  // (the GATHER epilogue's warps meet at barriers: they agree below)
             tc_fence_after();
             const int m0 = tile_m0(ti), n0 = tile_n0(ti);
             const uint32_t acc = tmem_base + (uint32_t)buf * ACC_ALL + ((uint32_t)(q * 32) << 16);
@@ -531,6 +532,65 @@ gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_c
             }
             const bool out16 = p.out_f16 != 0;
             const bool vec = (p.N & 7) == 0 && (d.ld & 7) == 0 && (d.col0 & 7) == 0;
+            if constexpr (GATHER) {
+                // A column-sharded call: the four warps first put 64 (fp16) or 32 (f32) token rows of the tile side by side
+                // in a 16 KB staging tile, then copy whole rows of it (256 or 512 contiguous bytes) to every destination,
+                // this GPU's slab and the peers'. A warp's own columns are only 64 bytes of a row, and stores of that
+                // size are what held the peer stores back.
+                bool staged = vec;
+                {
+                    uint32_t all;
+                    asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 p, %1, 0;\n\tbar.red.and.pred q, 1, 128, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+                                 : "=r"(all) : "r"((uint32_t)(ok ? 1 : 0)) : "memory");
+                    if (!all) break;  // the four warps go on together or not at all
+                }
+                if (staged) {
+                    uint8_t *stg = reinterpret_cast<uint8_t *>(bars) + 256;
+                    const int epi_tid = (warp - WARPS) * 32 + lane;
+                    const int esz = out16 ? 2 : 4, rows = out16 ? 64 : 32, cpr = BN * esz / 16;  // 16-byte chunks per row
+#pragma unroll 1
+                    for (int h = 0; h < NH; h++) {
+                        const int n_base = n0 + h * BN;
+                        const int n = n_base + q * 32 + lane;
+                        const float bias = (p.bias && n < p.N) ? p.bias[n] : 0.f;
+#pragma unroll 1
+                        for (int c = 0; c < MT; c += rows) {
+                            asm volatile("bar.sync 1, 128;" ::: "memory");  // the copy-out of the previous chunk is done
+#pragma unroll 1
+                            for (int cc = 0; cc < rows; cc += 16) {
+                                uint32_t r[16];
+                                tmem_ld_32x32b_x16(acc + (uint32_t)(h * ACC_COLS + c + cc), r);
+                                tmem_ld_wait();
+                                if (out16) {
+                                    __half *tile = reinterpret_cast<__half *>(stg) + q * 32 + lane;
+#pragma unroll
+                                    for (int j = 0; j < 16; j++) tile[(cc + j) * BN] = __float2half_rn(__uint_as_float(r[j]) + bias);
+                                } else {
+                                    float *tile = reinterpret_cast<float *>(stg) + q * 32 + lane;
+#pragma unroll
+                                    for (int j = 0; j < 16; j++) tile[(cc + j) * BN] = __uint_as_float(r[j]) + bias;
+                                }
+                            }
+                            asm volatile("bar.sync 1, 128;" ::: "memory");
+                            for (int idx = epi_tid; idx < rows * cpr; idx += 128) {
+                                const int row = idx / cpr, seg = idx - row * cpr;
+                                const int m = m0 + c + row, ncol = n_base + seg * (16 / esz);
+                                if (m < p.M && ncol < p.N) {
+                                    const uint4 v = reinterpret_cast<const uint4 *>(stg)[idx];
+                                    const int64_t off = ((int64_t)m * d.ld + d.col0 + ncol) * esz;
+#pragma unroll
+                                    for (int g = 0; g < kMaxGatherDst; g++)
+                                        if (g < d.n_dst) *reinterpret_cast<uint4 *>(reinterpret_cast<char *>(d.dst[g]) + off) = v;
+                                }
+                            }
+                        }
+                    }
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&acc_empty[buf]);
+                    continue;
+                }
+            }
 #pragma unroll 1
             for (int h = 0; h < NH; h++) {
                 const int n_warp = n0 + h * BN + q * 32;
@@ -855,9 +915,14 @@ static cudaError_t launch_tc(const CUtensorMap &mx, const CUtensorMap &mw, const
     const bool persist_on = persist_enabled();
     const int n_tiles = (int)(grid.x * grid.y);
     auto go_persist = [&](auto kernel, int variant) {
-        cudaError_t e = ensure_attr(kernel, variant);
-        if (e != cudaSuccess) return e;
-        return launch_pdl(kernel, dim3((unsigned)sms), dim3(tc::THREADS_P), (size_t)smem, st, mx, mw, p, (int)grid.x, n_tiles);
+        // the column-sharded instantiation carries a staging tile (and sizes its ring around it)
+        const int smem_p = variant == 4 ? tc::Smem<MT, DENSE, NH, tc::kGatherStageBytes>::TOTAL : smem;
+        if (!(dev >= 0 && dev < 16 && attr_set[variant][dev])) {
+            const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_p);
+            if (e != cudaSuccess) return e;
+            if (dev >= 0 && dev < 16) attr_set[variant][dev] = true;
+        }
+        return launch_pdl(kernel, dim3((unsigned)sms), dim3(tc::THREADS_P), (size_t)smem_p, st, mx, mw, p, (int)grid.x, n_tiles);
     };
     if (grid.z > 1) return go(tc::gemm_tc_kernel<MT, DENSE, true, NH, false>, 1);  // slices write partial sums: no placement
     // only where TMEM holds two accumulator sets: with one set the MMAs would wait for four warps to drain it
