@@ -11,8 +11,17 @@
 // Roles per CTA: a TMA producer warp (own packed-weight box, own half of the activation box), an MMA issuer warp
 // (rank 0 of the pair only; both ranks allocate and free tensor memory), sixteen unpack warps (four sets of one thread
 // per column that take the k-blocks in turn) and four epilogue warps (drain one of the two accumulator sets while the
-// MMAs of the next item run); which warp id has which role is listed at WARPS_PAIR. The pair walks the work items pair, pair + pairs, ...; an item is (K slice, column tile, token
-// tile); with more than one K slice the items write f32 partial sums that the split-K reduce launch adds.
+// MMAs of the next item run); which warp id has which role is listed at WARPS_PAIR. The pair walks the work items pair,
+// pair + pairs, ...; an item is (K slice, column tile, token tile); with more than one K slice the items write f32
+// partial sums that the split-K reduce launch adds.
+//   * The weights are constants: the producer requests the packed boxes of the first stages, and the unpack sets unpack
+//     them, before the wait on the previous kernel (programmatic dependent launch); the activation loads and the
+//     epilogue's stores come after it.
+//   * Where a work item is short (K = 896: 14 k-blocks) the result leaves through two 16 KB staging tiles and TMA stores
+//     (fp16, f32, or the f32 partial sums of a K slice; STG instantiations); where it is long, from registers, and the
+//     shared memory holds a sixth pipeline stage instead.
+//   * A launch whose last round of work items would leave most pairs idle for a long item cuts those items along K over
+//     the idle pairs (PairTail) and adds the slices in a small second launch.
 //
 // Barriers (mbarriers in shared memory, all waits bounded):
 //   full_w[s]   local    the packed-weight box of stage s has landed (own TMA)
