@@ -191,8 +191,8 @@ __device__ __forceinline__ uint4 ldg_stream_v4(const void *p)
 // return at once.
 __device__ __forceinline__ void pdl_sync()
 {
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 // The two halves, for kernels whose roles reach the dependence at different points (a producer that requests constant
 // weights first, warps that only ever touch shared memory, an epilogue that must not store before its predecessor is done).
