@@ -185,10 +185,13 @@ __device__ __forceinline__ uint4 ldg_stream_v4(const void *p)
 // ---- programmatic dependent launch -------------------------------------------------------------------------
 // Kernels of the decode step are launched so that the next one may become resident while the previous one is
 // still running. A kernel first does whatever touches only constant data (index arithmetic, requesting its
-// first weight chunks), then calls pdl_sync(): it lets ITS successor start the same way, and blocks until
-// every kernel before it in the stream has completed and its writes are visible. Nothing that an earlier
-// kernel writes or reads may be touched before pdl_sync(). Without the launch attribute both instructions
-// return at once.
+// first weight chunks), then calls pdl_sync(): it blocks until every kernel before it in the stream has
+// completed and its writes are visible, and only THEN lets its own successor start the same way. Nothing that an
+// earlier kernel writes or reads may be touched before pdl_sync(). The order matters: with the trigger in front of
+// the wait every kernel released its successor the moment it started, so a chain of kernels several deep sat
+// resident and waiting behind the one that ran; releasing the successor after the wait keeps exactly one kernel
+// ahead (its prologue overlaps the whole of this kernel) and took the 125-launch decode step from 0.577 to 0.550 ms.
+// Without the launch attribute both instructions return at once.
 __device__ __forceinline__ void pdl_sync()
 {
     asm volatile("griddepcontrol.wait;" ::: "memory");
