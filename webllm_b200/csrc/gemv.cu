@@ -52,9 +52,10 @@ namespace wb {
 
 // DIRECT (MB == 1 only): every warp holds at most one chunk of one tile and loads it straight into registers with
 // 128-bit streaming loads instead of going through the cp.async ring. Issuing six cp.async per thread costs ~0.4 us
-// more than plain loads; that is hidden when the kernel's prologue runs under its predecessor (programmatic dependent
-// launch), so the variant is used where it is not: the split-K projection that follows a kernel which fills the SMs.
-// It needs more registers (two CTAs per SM instead of three).
+// more than plain loads. It needs more registers (122 to 128: two CTAs per SM instead of three), so it is used where the
+// launch has at most one CTA per SM: the split-K down projection and, since every kernel releases its successor only
+// after its own wait (the prologue then has just one kernel to hide under), the unsplit q|k|v and o projections of a
+// decode step (0.541 -> 0.528 ms per step). The 304-CTA gate|up launch needs three CTAs per SM and keeps the ring.
 template <int MB, bool EXACT, bool DIRECT>
 __global__ void __launch_bounds__(MB == 1 ? 256 : 512, MB == 1 ? (DIRECT ? 2 : 3) : 1) gptq_gemv_mma_kernel(const GemvParams p)
 {
@@ -881,8 +882,8 @@ int launch_linear(wb_context *ctx, const Weight &w, const void *A, void *C, cons
         const int MB = M <= 8 ? 1 : (M <= 16 ? 2 : 4);
         p.stages = gemv_pick_stages(M, p.chunks_per_split, ex_gemv, p.wn, p.wk);
         p.cluster = gemv_cluster_merge(M, p.S) ? 1 : 0;
-        // register path: one chunk per warp, one tile per CTA, and a split-K launch (see the kernel's comment)
-        p.direct = (M <= 8 && p.cluster && p.chunks_per_split <= p.wk && plan.grid_x * plan.grid_y <= ctx->sm_count) ? 1 : 0;
+        // register path: one chunk per warp and one tile per CTA, at most one CTA per SM (see the kernel's comment)
+        p.direct = (M <= 8 && (p.cluster || p.S == 1) && p.chunks_per_split <= p.wk && plan.grid_x * plan.grid_y <= ctx->sm_count) ? 1 : 0;
         const size_t smem = gemv_smem_bytes(M, p.chunks_per_split, ex_gemv, p.wn, p.wk, p.stages, &p.ring_off, &p.red_off,
                                             p.cluster ? p.S : 0, &p.cl_off);
         if (smem > (size_t)kGemvSmemLimit) return fail(WB_ERR_UNSUPPORTED, "GEMV_MMA: activations do not fit shared memory");
