@@ -139,8 +139,11 @@ int forward_impl(wb_qwen *m, const Bufs &b, int64_t M, int64_t B, int64_t T, int
             f.kind = 1, f.delta = delta, f.x_out = delta ? x_in : nullptr, f.norm_w = f32w(L.in_norm), f.eps = m->cfg.rms_eps;
             WB_CHECK(linear(m, L.qkv, x, b.q, L.qkvb, 1, L.o, &f));
             x = x_in;
+            // (the kernel in front is the q|k|v GEMV, which releases this one after its own wait: the cache and the position
+            // are complete by the time this kernel can start, so it reads them before it waits)
+            static const int early_kv = [] { const char *e = getenv("WEBLLM_B200_ATT_EARLY"); return (e && e[0] == '0') ? 0 : 1; }();
             WB_CHECK(op_attention_decode(ctx, b.q, kc, vc, kv16, b.att, m->att_scratch, m->att_counters, H, KVH, D, past_ptr,
-                                         (int)past, max_keys, KV, b.k, b.v, m->cs_table));
+                                         (int)past, max_keys, KV, b.k, b.v, m->cs_table, early_kv));
             WB_CHECK(linear(m, L.o, b.att, b.proj, -1, 1, L.gate_up));
             float *xa = (x == b.x ? b.xa : b.x);
             f.delta = b.proj, f.x_out = xa, f.norm_w = f32w(L.post_norm);

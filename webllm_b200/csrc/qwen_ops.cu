@@ -322,9 +322,13 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const float *__re
                                                                int H, int KVH, int D, const int *__restrict__ past_ptr,
                                                                int past_imm, int kv_ld, float scale,
                                                                const float *__restrict__ k_raw, const float *__restrict__ v_raw,
-                                                               const float *__restrict__ cs_table, int chunk_max)
+                                                               const float *__restrict__ cs_table, int chunk_max, int early_kv)
 {
-    pdl_sync();
+    // early_kv: the cache rows of the earlier positions, the position itself and the rotary table entry are requested
+    // BEFORE the wait on the previous kernel; only q and the new k, v (what that kernel wrote) come after it. The caller
+    // sets it where every kernel in front of this one releases its successor after its own wait (pdl_sync), so that this
+    // kernel cannot start before the kernel two places ahead, and everything older (the cache, the position), is complete.
+    if (!early_kv) pdl_sync();
     // [D] query (pre-scaled), [2][D] new k, v, [chunk] scores, [4][D] per-warp value sums, [ATT_SPLITS][D + 2] merge slots
     // (written by the other CTAs of the cluster), then (16-byte aligned) the split's V rows [chunk_max][D] in the cache type
     extern __shared__ float sm[];
@@ -334,13 +338,16 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const float *__re
     const int half = D >> 1;  // D <= 128: one (i, i + half) pair per thread
     const bool fused = k_raw != nullptr;
     float q0 = 0.f, q1 = 0.f, x0 = 0.f, x1 = 0.f, v0f = 0.f, v1f = 0.f;
-    if (tid < half) {
-        q0 = q[h * D + tid], q1 = q[h * D + tid + half];
-        if (fused) {
-            x0 = k_raw[kvh * D + tid], x1 = k_raw[kvh * D + tid + half];
-            v0f = v_raw[kvh * D + tid], v1f = v_raw[kvh * D + tid + half];
+    auto load_new = [&]() {
+        if (tid < half) {
+            q0 = q[h * D + tid], q1 = q[h * D + tid + half];
+            if (fused) {
+                x0 = k_raw[kvh * D + tid], x1 = k_raw[kvh * D + tid + half];
+                v0f = v_raw[kvh * D + tid], v1f = v_raw[kvh * D + tid + half];
+            }
         }
-    }
+    };
+    if (!early_kv) load_new();
     const int pos = past_ptr ? *past_ptr : past_imm;
     const int n_keys = pos + 1;
     const int chunk = (n_keys + ATT_SPLITS - 1) / ATT_SPLITS;
@@ -377,6 +384,10 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const float *__re
 #pragma unroll
         for (int c = 0; c < KREGS; c++)
             if (c < k_pieces) kreg[c] = kp[c];
+    }
+    if (early_kv) {
+        pdl_sync();
+        load_new();
     }
     if (tid < half) {
         if (!fused) {
@@ -642,7 +653,7 @@ size_t op_attention_decode_smem(int D, int max_keys, int kv_f16)
 
 int op_attention_decode(wb_context *ctx, const float *q, void *kmem, void *vmem, int kv_f16, float *out, float *scratch,
                         unsigned *counters, int H, int KVH, int D, const int *past_ptr, int past_imm, int max_keys, int kv_ld,
-                        const float *k_raw, const float *v_raw, const float *cs_table)
+                        const float *k_raw, const float *v_raw, const float *cs_table, int early_kv)
 {
     const int chunk = (max_keys + ATT_SPLITS - 1) / ATT_SPLITS;
     const size_t smem = op_attention_decode_smem(D, max_keys, kv_f16);
@@ -651,11 +662,11 @@ int op_attention_decode(wb_context *ctx, const float *q, void *kmem, void *vmem,
     if (kv_f16) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(attention_decode_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         WB_CUDA(launch_pdl_cluster(attention_decode_kernel<__half>, grid, dim3(128), smem, ctx->stream, ATT_SPLITS, q, (__half *)kmem, (__half *)vmem, out,
-                           scratch, counters, H, KVH, D, past_ptr, past_imm, kv_ld, scale, k_raw, v_raw, cs_table, chunk));
+                           scratch, counters, H, KVH, D, past_ptr, past_imm, kv_ld, scale, k_raw, v_raw, cs_table, chunk, early_kv));
     } else {
         if (smem > 48 * 1024) cudaFuncSetAttribute(attention_decode_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         WB_CUDA(launch_pdl_cluster(attention_decode_kernel<float>, grid, dim3(128), smem, ctx->stream, ATT_SPLITS, q, (float *)kmem, (float *)vmem, out,
-                           scratch, counters, H, KVH, D, past_ptr, past_imm, kv_ld, scale, k_raw, v_raw, cs_table, chunk));
+                           scratch, counters, H, KVH, D, past_ptr, past_imm, kv_ld, scale, k_raw, v_raw, cs_table, chunk, early_kv));
     }
     LAUNCH_OK(ctx);
 }

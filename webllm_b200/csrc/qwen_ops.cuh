@@ -26,10 +26,12 @@ int op_attention_prefill(wb_context *ctx, const float *q, const void *kmem, cons
 // One query row against the cache, keys split over several CTAs per head; scratch holds the per-slice
 // softmax state (op_attention_decode_scratch_floats floats), counters one zeroed word per head.
 // With k_raw / v_raw / cs_table set, q, k_raw and v_raw are the un-rotated projection outputs: the kernel applies the
-// rotary embedding and appends the new key and value to the cache itself (no op_rope_kv before it).
+// rotary embedding and appends the new key and value to the cache itself (no op_rope_kv before it). early_kv: the kernel
+// reads the cache and the position before it waits for the kernel in front of it (see the kernel).
 int op_attention_decode(wb_context *ctx, const float *q, void *kmem, void *vmem, int kv_f16, float *out, float *scratch,
                         unsigned *counters, int H, int KVH, int D, const int *past_ptr, int past_imm, int max_keys, int kv_ld,
-                        const float *k_raw = nullptr, const float *v_raw = nullptr, const float *cs_table = nullptr);
+                        const float *k_raw = nullptr, const float *v_raw = nullptr, const float *cs_table = nullptr,
+                        int early_kv = 0);
 int op_attention_decode_scratch_floats(int H, int D);
 // Dynamic shared memory of the decode attention kernel for up to max_keys keys (it stages a split's V rows).
 size_t op_attention_decode_smem(int D, int max_keys, int kv_f16);
