@@ -303,7 +303,9 @@ __device__ __forceinline__ float dot_row<float>(const float *qs, const float *kp
 // softmax per split, the last split to arrive merges). The kernel is a chain of dependent memory round trips, so the
 // order of its loads is the design: q (and the raw k, v) are requested before the position is known; as soon as it
 // is, the split's V rows start moving into shared memory (cp.async) and its K rows into registers, and they arrive
-// while the scores and the softmax are computed; the merge issues all of its loads before it uses any.
+// while the scores and the softmax are computed; the merge issues all of its loads before it uses any. In a decode
+// step (early_kv) the position, the rotary entry and the cache rows are even requested before the kernel waits for its
+// predecessor, and only q and the raw k, v after it.
 //
 // With k_raw != nullptr the kernel also does the work of rope_half.wgsl + kv_store.wgsl for the new position
 // (ropeHalfRef, src/reference/qwen-ref.ts:35-64): q, k_raw, v_raw are the projection outputs; q is rotated while it is
