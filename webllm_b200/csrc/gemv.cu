@@ -60,7 +60,6 @@ template <int MB, bool EXACT, bool DIRECT>
 __global__ void __launch_bounds__(MB == 1 ? 256 : 512, MB == 1 ? (DIRECT ? 2 : 3) : 1) gptq_gemv_mma_kernel(const GemvParams p)
 {
     extern __shared__ uint4 smem_u4[];
-    const uint64_t l2_policy = MB == 1 ? l2_evict_first_policy() : 0ull;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int wn = warp % p.wn, wk = warp / p.wn;
@@ -93,7 +92,7 @@ __global__ void __launch_bounds__(MB == 1 ? 256 : 512, MB == 1 ? (DIRECT ? 2 : 3
     auto request = [&](int slot) {
         if (rq_tile < tiles_cta && n_i > 0) {
             const int cc = col_of(rq_tile);
-            fetch_chunk_async<MB == 1>(p, ch_begin + wk + rq_i * p.wk, t, cc, cc < p.N, ring + slot * stage_stride, l2_policy);
+            fetch_chunk_async(p, ch_begin + wk + rq_i * p.wk, t, cc, cc < p.N, ring + slot * stage_stride);
             if (++rq_i == n_i) rq_i = 0, rq_tile++;
         }
         cp_async_commit();

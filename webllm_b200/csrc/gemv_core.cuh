@@ -100,17 +100,14 @@ __device__ __forceinline__ void fetch_chunk(const GemvParams &p, int ch, int t, 
 // without holding a register: this is what keeps enough bytes in flight to cover the HBM latency.
 constexpr int kSlotBytes = 80;
 
-// 16-byte copy of packed weights. HINT adds an L2 evict-first policy (weights are read once per token and must not
-// push the KV cache and the activations out of L2). The hint is only used by the 256-thread instance of the GEMV
-// kernel: in the 512-thread instance it raised "illegal instruction" at M = 16 (not at M <= 9, same code) and the
-// cause was not found, so that instance copies without it.
-template <bool HINT>
-__device__ __forceinline__ void cp_async_16(uint32_t dst, const void *src, uint64_t policy)
+// 16-byte copy of packed weights. Without an L2 cache-policy operand: the copy with an evict-first policy
+// (cp.async ... L2::cache_hint) made a decode step ~3 % faster while every projection used this ring, but the kernel
+// raised "illegal instruction" twice with it, in different instances and only in some builds (512 threads at M = 16;
+// 256 threads with K slices as a cluster at M = 1); reading did not show why, and nothing else in the ring path takes a
+// register operand that can be invalid, so no copy carries the policy any more. The register path's plain loads keep it.
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void *src)
 {
-    if constexpr (HINT)
-        asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "l"(policy) : "memory");
-    else
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
 __device__ __forceinline__ void cp_async_8(uint32_t dst, const void *src)
 {
@@ -131,9 +128,7 @@ __device__ __forceinline__ void cp_async_wait(int pending)
     }
 }
 
-template <bool HINT>
-__device__ __forceinline__ void fetch_chunk_async(const GemvParams &p, int ch, int t, int c, bool col_ok, unsigned char *slot,
-                                                  uint64_t policy)
+__device__ __forceinline__ void fetch_chunk_async(const GemvParams &p, int ch, int t, int c, bool col_ok, unsigned char *slot)
 {
     const uint32_t dst = (uint32_t)__cvta_generic_to_shared(slot);
     const uint32_t *base = p.qw + (int64_t)(ch * 16 + t) * p.N + c;
@@ -141,7 +136,7 @@ __device__ __forceinline__ void fetch_chunk_async(const GemvParams &p, int ch, i
     const uint4 zero4 = make_uint4(0, 0, 0, 0);
 #pragma unroll
     for (int st = 0; st < 4; st++) {
-        if (col_ok && ch * 16 + st * 4 + t < p.pack_rows) cp_async_16<HINT>(dst + st * 16, base + st * step, policy);
+        if (col_ok && ch * 16 + st * 4 + t < p.pack_rows) cp_async_16(dst + st * 16, base + st * step);
         else *reinterpret_cast<uint4 *>(slot + st * 16) = zero4;
     }
     const int G = p.group_chunks == 1 ? ch : ch / p.group_chunks;
