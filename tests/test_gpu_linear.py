@@ -279,3 +279,46 @@ def test_streaming_kernel_refuses_a_last_slice_without_a_chunk_per_warp(gpu, ora
         assert_close(oracle, run_linear(gpu, h, x, 1, N), ref, F32_RTOL, "streaming kernel, 13 slices")
     finally:
         gpu.plan_override(0, 0)
+
+
+_MERGE_TIMEOUT_CHILD = r"""
+import numpy as np
+from webllm_b200 import Gpu, _lib, synthetic
+from webllm_b200._lib import WebllmError
+g = Gpu(0, weight_bytes=256 << 20, act_bytes=64 << 20)
+t = synthetic.random_gptq(4864, 896, 128, seed=5, zeros="any")
+h = g.gptq_register("down", t.qweight, t.qzeros, t.scales, 4864, 896, 128, 4, None)
+p = g.plan(h, 1)
+assert p["kernel_name"] == "gemv_mma" and p["split_k"] > 1, p
+def run(M):
+    g.arena.reset()
+    A = g.arena.alloc(M * 4864, [M, 4864], "f32")
+    C = g.arena.alloc(M * 896, [M, 896], "f32")
+    g.write(A, np.random.default_rng(M).standard_normal((M, 4864)).astype(np.float32))
+    g.linear(h, A, C, None, M)
+    return C
+run(1)                      # K slices as a cluster; the first CTA waits for 4 bytes that nobody sends
+try:
+    g.synchronize()
+    raise SystemExit("the wait did not run out")
+except WebllmError as e:
+    assert e.status == _lib.WB_ERR_TIMEOUT, e
+g.synchronize()             # the status word was consumed
+y = g.read(run(64)).astype(np.float32)   # another kernel on the same context still works
+assert np.isfinite(y).all() and float(np.abs(y).max()) > 0
+g.close()
+print("merge-timeout-ok")
+"""
+
+
+def test_cluster_merge_wait_gives_up_instead_of_hanging(built_lib):
+    """The first CTA of a split-K cluster waits on an mbarrier for the other slices' partial sums. With the test setting
+    that arms the barrier for 4 bytes more than are sent the wait runs out after its poll limit, the kernel returns, the
+    next synchronize reports WB_ERR_TIMEOUT and the context keeps working. (The setting is read once per process, so
+    the case runs in a child process.)"""
+    import os, subprocess, sys
+    from pathlib import Path
+    env = dict(os.environ, WEBLLM_B200_CLUSTER_ASYNC="2")
+    r = subprocess.run([sys.executable, "-c", _MERGE_TIMEOUT_CHILD], env=env, cwd=str(Path(__file__).resolve().parent.parent),
+                       capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "merge-timeout-ok" in r.stdout, r.stdout + r.stderr

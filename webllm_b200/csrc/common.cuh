@@ -276,6 +276,49 @@ __device__ __forceinline__ void cluster_barrier()
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
+// ---- merge through an mbarrier in the cluster's first CTA instead of a second cluster barrier ----
+// The senders write their values with st.async (the store itself reports its bytes to the barrier) and leave; the first
+// CTA waits on the barrier's phase, bounded. The barrier is initialised at the top of the kernel and made known with one
+// relaxed cluster barrier there, off the critical path: what the closing barrier.cluster.arrive.release cost the senders
+// and the receiver (a fence at cluster scope, then a round trip) no longer follows the last partial sum.
+constexpr int kStatusClusterMergeTimeout = 31;
+__device__ __forceinline__ void cluster_merge_init(uint64_t *bar, uint32_t expect_bytes, bool receiver)
+{
+    if (receiver && threadIdx.x == 0) {
+        const uint32_t a = (uint32_t)__cvta_generic_to_shared(bar);
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(a));
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(a), "r"(expect_bytes) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();  // the .aligned forms want the warp converged
+    asm volatile("barrier.cluster.arrive.relaxed.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// remote_addr, remote_bar: shared::cluster addresses (cluster_map_shared) in the receiving CTA
+__device__ __forceinline__ void cluster_send_f32(uint32_t remote_addr, float v, uint32_t remote_bar)
+{
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.f32 [%0], %1, [%2];" ::"r"(remote_addr), "f"(v), "r"(remote_bar)
+                 : "memory");
+}
+// Every thread of the receiver that reads the merged values calls this. False (and `status` set) when the bytes did not
+// arrive within ~2^20 polls; the caller carries on with what it has, the host sees the code at its next synchronize.
+__device__ __forceinline__ bool cluster_merge_wait(uint64_t *bar, int *status)
+{
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(bar);
+    for (uint32_t it = 0; it < (1u << 20); it++) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(a)
+            : "memory");
+        if (ok) return true;
+    }
+    if (status) *(volatile int *)status = kStatusClusterMergeTimeout;
+    return false;
+}
+
 #endif  // __CUDACC__
 
 }  // namespace wb

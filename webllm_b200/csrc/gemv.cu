@@ -118,6 +118,9 @@ __global__ void __launch_bounds__(MB == 1 ? 256 : 512, MB == 1 ? (DIRECT ? 2 : 3
             asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.pf_ptr + off), "r"(n) : "memory");
         }
     }
+    __shared__ uint64_t cl_bar;
+    // (cl_async == 2, a test's setting: the barrier is armed for 4 bytes more than are sent, so the receiver's wait runs out)
+    if (p.cl_async) cluster_merge_init(&cl_bar, (uint32_t)((p.S - 1) * p.M * p.wn * 32 * 4) + (p.cl_async == 2 ? 4u : 0u), blockIdx.y == 0);
     // The bias is a constant too. A thread's column within a tile is fixed when the block size is a multiple of the tile
     // width; its bias value for the CTA's first tile is requested here, so that the load does not stand in front of the
     // final store (it measured ~0.5 us there on the q|k|v projection of a decode step).
@@ -357,6 +360,7 @@ __global__ void __launch_bounds__(MB == 1 ? 256 : 512, MB == 1 ? (DIRECT ? 2 : 3
     const bool direct = p.S == 1;
     float *cl_part = reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(smem_u4) + p.cl_off);  // [S][M * tile_cols]
     const uint32_t cl_dst = p.cluster ? cluster_map_shared(cl_part + (size_t)blockIdx.y * p.M * p.wn * 32, 0) : 0u;
+    const uint32_t cl_bar_remote = p.cl_async ? cluster_map_shared(&cl_bar, 0) : 0u;
     int slot_use = 0, slot_req = p.stages - 1;
     for (int tj = 0; tj < tiles_cta; tj++) {
         const int tile = (int)blockIdx.x + tj * (int)gridDim.x;
@@ -408,6 +412,9 @@ __global__ void __launch_bounds__(MB == 1 ? 256 : 512, MB == 1 ? (DIRECT ? 2 : 3
                 if (p.bias) v += (bias_pre_ok && tj == 0) ? bias_pre : p.bias[n];
                 if (p.out_f16) ((__half *)p.out)[(int64_t)m * p.N + n] = __float2half_rn(v);
                 else ((float *)p.out)[(int64_t)m * p.N + n] = v;
+            } else if (p.cl_async) {
+                if (blockIdx.y == 0) cl_part[idx] = v;
+                else cluster_send_f32(cl_dst + (uint32_t)idx * 4u, v, cl_bar_remote);
             } else if (p.cluster) {
                 cluster_store_f32(cl_dst + (uint32_t)idx * 4u, v);
             } else {
@@ -418,8 +425,9 @@ __global__ void __launch_bounds__(MB == 1 ? 256 : 512, MB == 1 ? (DIRECT ? 2 : 3
             // The S slices of this column tile are the CTAs of one cluster: each has just stored its partial tile into
             // the first CTA's shared memory; after the cluster barrier that CTA adds them in slice order and the bias
             // once. No workspace, fence or atomic, and the result does not depend on scheduling.
-            cluster_barrier();
+            if (!p.cl_async) cluster_barrier();
             if (blockIdx.y == 0) {
+                if (p.cl_async && tid < outputs) cluster_merge_wait(&cl_bar, p.status);  // the reader's own slice-0 value is its own store
                 for (int idx = tid; idx < outputs; idx += nthreads) {
                     const int m = idx / tile_cols;
                     const int n = n_base + (idx - m * tile_cols);
@@ -898,6 +906,11 @@ int launch_linear(wb_context *ctx, const Weight &w, const void *A, void *C, cons
         if (smem > (size_t)kGemvSmemLimit) return fail(WB_ERR_UNSUPPORTED, "GEMV_MMA: activations do not fit shared memory");
         // plan.grid_x counts column tiles; the launch covers them with one evenly loaded wave of CTAs
         dim3 grid(gemv_grid_x(ctx->sm_count, plan.grid_x, plan.grid_y, plan.block, smem), plan.grid_y);
+        // slices of a cluster send their partial tiles to an mbarrier of the first CTA where every CTA has one whole tile
+        // WEBLLM_B200_CLUSTER_ASYNC: 0 = closing cluster barrier instead, 2 = the receiver expects bytes that never come
+        static const int cl_async_mode = [] { const char *e = getenv("WEBLLM_B200_CLUSTER_ASYNC"); return e ? atoi(e) : 1; }();
+        p.cl_async = (cl_async_mode > 0 && p.cluster && (int)grid.x == plan.grid_x && w.N % (p.wn * 32) == 0) ? (cl_async_mode == 2 ? 2 : 1) : 0;
+        p.status = ctx->status_word;
         cudaError_t e = MB == 1   ? launch_gemv_mb<1>(p, grid, plan.block, smem, ex_gemv, ctx->stream)
                         : MB == 2 ? launch_gemv_mb<2>(p, grid, plan.block, smem, ex_gemv, ctx->stream)
                                   : launch_gemv_mb<4>(p, grid, plan.block, smem, ex_gemv, ctx->stream);
@@ -1048,7 +1061,7 @@ extern "C" int wb_gptq_gemv_static(const void *qweight, const void *qzeros, cons
     p.M = (int)M, p.N = (int)N, p.K = (int)K, p.pack_rows = pack_rows, p.zcols = (int)((N + 7) / 8);
     p.chunks = chunks, p.chunks_per_split = cps, p.group_chunks = (int)(group_size / 128), p.S = S;
     p.wn = wn, p.wk = wk, p.x_f16 = act_dtype == WB_F16, p.out_f16 = out_dtype == WB_F16, p.xs_stride = xs_stride;
-    p.stages = stages, p.ring_off = ring_off, p.red_off = red_off, p.cluster = 0, p.cl_off = 0, p.direct = 0;
+    p.stages = stages, p.ring_off = ring_off, p.red_off = red_off, p.cluster = 0, p.cl_off = 0, p.direct = 0, p.cl_async = 0, p.status = nullptr;
     p.pf_ptr = nullptr, p.pf_bytes = 0;
     p.prologue = kPrologueNone, p.delta = nullptr, p.x_out = nullptr, p.norm_w = nullptr, p.eps = 0.f, p.up = nullptr, p.ld_x = (int)K;
     int sms = 148;

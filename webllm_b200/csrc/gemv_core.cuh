@@ -34,6 +34,8 @@ struct GemvParams {
     int direct;         // 1: every warp holds at most one chunk of one tile: it is loaded straight into registers
     int cluster;        // 1: the S slices of a column tile are one thread-block cluster and merge through its shared memory
     int cl_off;         // byte offset of the [S][M * tile columns] merge buffer (used in the cluster's first CTA)
+    int cl_async;       // 1: the slices send their partial tiles with st.async to an mbarrier of the first CTA (one tile per CTA)
+    int *status;        // error word of the context (bounded waits)
     const char *pf_ptr;   // weight of a later call to pull into L2 while this one runs (nullable)
     unsigned pf_bytes;    // multiple of 16
     // Optional work fused in front of the projection (f32 activations, M <= 8); see GemvPrologue.

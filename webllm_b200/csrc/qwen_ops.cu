@@ -324,8 +324,12 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const float *__re
                                                                int H, int KVH, int D, const int *__restrict__ past_ptr,
                                                                int past_imm, int kv_ld, float scale,
                                                                const float *__restrict__ k_raw, const float *__restrict__ v_raw,
-                                                               const float *__restrict__ cs_table, int chunk_max, int early_kv)
+                                                               const float *__restrict__ cs_table, int chunk_max, int early_kv,
+                                                               int cl_async, int *status)
 {
+    // cl_async: the splits send their partial results to an mbarrier of the head's first CTA (cluster_merge_init)
+    __shared__ uint64_t merge_bar;
+    if (cl_async) cluster_merge_init(&merge_bar, (uint32_t)((ATT_SPLITS - 1) * (D + 2) * 4), blockIdx.y == 0);
     // early_kv: the cache rows of the earlier positions, the position itself and the rotary table entry are requested
     // BEFORE the wait on the previous kernel; only q and the new k, v (what that kernel wrote) come after it. The caller
     // sets it where every kernel in front of this one releases its successor after its own wait (pdl_sync), so that this
@@ -478,13 +482,25 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const float *__re
     // The ATT_SPLITS CTAs of a head form one cluster: each stores its (max, sum, weighted values) into the shared memory
     // of the cluster's first CTA, and after the cluster barrier that CTA merges them in split order. No global scratch,
     // no fence, no atomic, and nothing depends on which CTA finishes last.
-    {
+    if (cl_async) {
+        if (s != 0) {
+            const uint32_t dst = cluster_map_shared(merge + (size_t)s * (D + 2), 0), bar = cluster_map_shared(&merge_bar, 0);
+            for (int d = tid; d < D; d += blockDim.x)
+                cluster_send_f32(dst + (2 + d) * 4, wacc[d] + wacc[D + d] + wacc[2 * D + d] + wacc[3 * D + d], bar);
+            if (tid == 0) cluster_send_f32(dst, mx, bar), cluster_send_f32(dst + 4, total, bar);
+            return;
+        }
+        for (int d = tid; d < D; d += blockDim.x) merge[2 + d] = wacc[d] + wacc[D + d] + wacc[2 * D + d] + wacc[3 * D + d];
+        if (tid == 0) merge[0] = mx, merge[1] = total;
+        __syncthreads();
+        if (tid < D) cluster_merge_wait(&merge_bar, status);
+    } else {
         const uint32_t dst = cluster_map_shared(merge + (size_t)s * (D + 2), 0);
         for (int d = tid; d < D; d += blockDim.x)
             cluster_store_f32(dst + (2 + d) * 4, wacc[d] + wacc[D + d] + wacc[2 * D + d] + wacc[3 * D + d]);
         if (tid == 0) cluster_store_f32(dst, mx), cluster_store_f32(dst + 4, total);
+        cluster_barrier();
     }
-    cluster_barrier();
     if (s != 0) return;
     for (int d = tid; d < D; d += blockDim.x) {
         float M = -INFINITY;
@@ -660,15 +676,16 @@ int op_attention_decode(wb_context *ctx, const float *q, void *kmem, void *vmem,
     const int chunk = (max_keys + ATT_SPLITS - 1) / ATT_SPLITS;
     const size_t smem = op_attention_decode_smem(D, max_keys, kv_f16);
     const float scale = 1.0f / sqrtf((float)D);
+    static const int cl_async = [] { const char *e = getenv("WEBLLM_B200_CLUSTER_ASYNC"); return (e && e[0] == '0') ? 0 : 1; }();  // see gemv.cu
     dim3 grid(H, ATT_SPLITS);
     if (kv_f16) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(attention_decode_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         WB_CUDA(launch_pdl_cluster(attention_decode_kernel<__half>, grid, dim3(128), smem, ctx->stream, ATT_SPLITS, q, (__half *)kmem, (__half *)vmem, out,
-                           scratch, counters, H, KVH, D, past_ptr, past_imm, kv_ld, scale, k_raw, v_raw, cs_table, chunk, early_kv));
+                           scratch, counters, H, KVH, D, past_ptr, past_imm, kv_ld, scale, k_raw, v_raw, cs_table, chunk, early_kv, cl_async, ctx->status_word));
     } else {
         if (smem > 48 * 1024) cudaFuncSetAttribute(attention_decode_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         WB_CUDA(launch_pdl_cluster(attention_decode_kernel<float>, grid, dim3(128), smem, ctx->stream, ATT_SPLITS, q, (float *)kmem, (float *)vmem, out,
-                           scratch, counters, H, KVH, D, past_ptr, past_imm, kv_ld, scale, k_raw, v_raw, cs_table, chunk, early_kv));
+                           scratch, counters, H, KVH, D, past_ptr, past_imm, kv_ld, scale, k_raw, v_raw, cs_table, chunk, early_kv, cl_async, ctx->status_word));
     }
     LAUNCH_OK(ctx);
 }
