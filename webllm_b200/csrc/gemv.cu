@@ -423,8 +423,9 @@ __global__ void __launch_bounds__(MB == 1 ? 256 : 512, MB == 1 ? (DIRECT ? 2 : 3
         }
         if (!direct && p.cluster) {
             // The S slices of this column tile are the CTAs of one cluster: each has just stored its partial tile into
-            // the first CTA's shared memory; after the cluster barrier that CTA adds them in slice order and the bias
-            // once. No workspace, fence or atomic, and the result does not depend on scheduling.
+            // the first CTA's shared memory; after the cluster barrier (or, with cl_async, once its mbarrier has counted
+            // the other slices' bytes) that CTA adds them in slice order and the bias once. No workspace, fence or atomic,
+            // and the result does not depend on scheduling.
             if (!p.cl_async) cluster_barrier();
             if (blockIdx.y == 0) {
                 if (p.cl_async && tid < outputs) cluster_merge_wait(&cl_bar, p.status);  // the reader's own slice-0 value is its own store

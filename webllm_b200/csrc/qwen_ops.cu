@@ -480,8 +480,9 @@ __global__ void __launch_bounds__(128) attention_decode_kernel(const float *__re
     }
     __syncthreads();
     // The ATT_SPLITS CTAs of a head form one cluster: each stores its (max, sum, weighted values) into the shared memory
-    // of the cluster's first CTA, and after the cluster barrier that CTA merges them in split order. No global scratch,
-    // no fence, no atomic, and nothing depends on which CTA finishes last.
+    // of the cluster's first CTA, and after the cluster barrier (with cl_async: once its mbarrier has counted the other
+    // splits' bytes) that CTA merges them in split order. No global scratch, no atomic, and nothing depends on which CTA
+    // finishes last.
     if (cl_async) {
         if (s != 0) {
             const uint32_t dst = cluster_map_shared(merge + (size_t)s * (D + 2), 0), bar = cluster_map_shared(&merge_bar, 0);
