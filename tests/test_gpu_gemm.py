@@ -33,7 +33,7 @@ def _ref_rows(oracle, x16, W16, rows, bias=None):
 
 
 @pytest.mark.parametrize("name,K,N", [("q", 896, 896), ("k", 896, 128), ("gate", 896, 4864), ("down", 4864, 896)])
-@pytest.mark.parametrize("M", [16, 17, 32, 64, 100, 128, 300])
+@pytest.mark.parametrize("M", [9, 12, 16, 17, 32, 64, 100, 128, 300])
 def test_gemm_tc_small_and_ragged_m(gpu, oracle, name, K, N, M):
     """Every tile height (16, 32, 64, 128, 256) incl. token counts that do not fill the tile."""
     h, W16 = _weight(gpu, oracle, name, K, N)
@@ -187,8 +187,8 @@ def test_linearity_at_full_size(gpu, oracle):
 
 
 def test_gemv_and_gemm_paths_agree(gpu, oracle):
-    """The switch between the streaming kernel and the tensor-core kernel (M = 16 / 17, and forced both ways
-    at M = 32) must not be visible beyond fp16-weight rounding."""
+    """The switch between the GEMV and the tensor-core kernel (forced both ways at M = 32) must not be visible beyond
+    fp16-weight rounding."""
     h, _ = _weight(gpu, oracle, "gate", 896, 4864)
     x16 = np.random.default_rng(5).standard_normal((32, 896)).astype(np.float16)
     outs = {}
@@ -200,8 +200,30 @@ def test_gemv_and_gemm_paths_agree(gpu, oracle):
             gpu.plan_override(0, 0)
     # the tensor-core path multiplies weights rounded to fp16 (2^-11), the streaming path exact ones
     assert_close(oracle, outs[_lib.WB_KERNEL_GEMM_TC], outs[_lib.WB_KERNEL_GEMV_MMA], 4e-3, "paths")
-    assert gpu.plan(h, 16, "f16")["kernel_name"] == "gemv_mma"
+    # where the planner switches: after M = 8, except on short-K wide-N shapes like this one (12 with fp16, 16 with f32)
+    assert gpu.plan(h, 12, "f16")["kernel_name"] == "gemv_mma" and gpu.plan(h, 13, "f16")["kernel_name"] == "gemm_tc"
+    assert gpu.plan(h, 16, "f32")["kernel_name"] == "gemv_mma" and gpu.plan(h, 17, "f32")["kernel_name"] == "gemm_tc"
     assert gpu.plan(h, 33, "f16")["kernel_name"] == "gemm_tc"
+    hq, _ = _weight(gpu, oracle, "q", 896, 896)
+    for act in ("f16", "f32"):
+        assert gpu.plan(hq, 8, act)["kernel_name"] == "gemv_mma" and gpu.plan(hq, 9, act)["kernel_name"] == "gemm_tc"
+    assert gpu.plan(hq, 16, "f32", exact=True)["kernel_name"] == "gemv_mma"  # exact mode keeps f32 activations off the fp16 path
+
+
+@pytest.mark.parametrize("name,K,N", [("q", 896, 896), ("down", 4864, 896), ("kv7", 3584, 512)])
+@pytest.mark.parametrize("M", [9, 12, 16])
+def test_small_batch_default_goes_to_the_tensor_cores(gpu, oracle, name, K, N, M):
+    """9 <= M <= 16 with the planner's own choice (the tensor-core kernel on these shapes), fp16 and f32 activations
+    (the latter rounded to fp16 first, as the reference's tiled GEMM stages them: gemm_nt_f16_from_f32.wgsl:58-62)."""
+    h, W16 = _weight(gpu, oracle, name, K, N)
+    x = np.random.default_rng(M * 7 + K).standard_normal((M, K)).astype(np.float32)
+    x16 = x.astype(np.float16)
+    ref = _ref_rows(oracle, x16, W16, list(range(M)))
+    for act, xin in (("f16", x16), ("f32", x)):
+        assert gpu.plan(h, M, act)["kernel_name"] == "gemm_tc"
+        got = run_linear(gpu, h, xin, M, N, None, act=act, out=act)
+        assert_close(oracle, got, ref, F16_RTOL, f"{name} M={M} {act}")
+    gpu.synchronize()
 
 
 @pytest.mark.parametrize("M", [9, 64, 200])

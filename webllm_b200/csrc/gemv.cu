@@ -645,7 +645,7 @@ static size_t gemv_smem_bytes(int64_t M, int cps, bool two_halves, int wn, int w
 // of tiles (a partial second wave would otherwise double the time of a kernel that lasts one wave).
 static int gemv_grid_x(int sm_count, int ctas_n, int S, int block, size_t smem)
 {
-    int per_sm = (int)((220 * 1024) / (smem + 1024));
+    int per_sm = (int)((227 * 1024) / (smem + 1024));  // 228 KB per SM, 1 KB of it reserved per resident CTA
     const int by_threads = 2048 / block, by_regs = block <= 256 ? 3 : 1;
     if (per_sm > by_threads) per_sm = by_threads;
     if (per_sm > by_regs) per_sm = by_regs;
@@ -761,7 +761,14 @@ static int plan_linear_ex(wb_context *ctx, const Weight &w, int64_t M, int act_d
     memset(plan, 0, sizeof *plan);
     int kind = ctx->force_kernel;
     if (kind == 0) {
-        if (gemv_mma_supports(w, M) && (M <= 16 || !gemm_tc_supports(w, M))) kind = WB_KERNEL_GEMV_MMA;
+        // M <= 8: the GEMV (its one-row-block instance, 2 - 8 us). 9 <= M <= 16: its two-row-block instance costs 6 - 16 us
+        // and grows with M and K, the tensor-core kernel a flat 5 - 8 us (+ 2.3 us for the cast of f32 activations); measured
+        // on the 0.5B and the 7B-class shapes the GEMV still wins there only on short-K, wide-N projections (896 -> 4864,
+        // 896 -> 9728): up to M = 12 with fp16 activations, up to 16 with f32 ones.
+        const bool tc_ok = gemm_tc_supports(w, M) && !(exact && act_dtype == WB_F32);
+        const bool short_wide = w.K <= 2048 && w.N >= 4096;
+        const bool gemv_first = M <= 8 || (M <= 16 && (!tc_ok || (short_wide && M <= (act_dtype == WB_F32 ? 16 : 12))));
+        if (gemv_mma_supports(w, M) && (gemv_first || !gemm_tc_supports(w, M))) kind = WB_KERNEL_GEMV_MMA;
         else if (dense_gemv_supports(w, M)) kind = WB_KERNEL_DENSE_GEMV;
         else if (gemm_tc_supports(w, M) && !(exact && act_dtype == WB_F32)) kind = WB_KERNEL_GEMM_TC;
         else kind = WB_KERNEL_GENERIC;  // incl. exact f32 activations at large M: k-ascending double sums
@@ -841,7 +848,7 @@ static cudaError_t launch_gemv_mb(const GemvParams &p, dim3 grid, int block, siz
 bool linear_fusion_supported(wb_context *ctx, const Weight &w, int64_t M)
 {
     if (M < 1 || M > 8 || ctx->force_kernel != 0) return false;
-    return gemv_mma_supports(w, M);  // what plan_linear picks first for M <= 16
+    return gemv_mma_supports(w, M);  // what plan_linear picks first for M <= 8
 }
 
 int launch_linear(wb_context *ctx, const Weight &w, const void *A, void *C, const float *bias, int64_t M,

@@ -15,7 +15,7 @@ struct LayerW {
 struct Bufs {
     uint32_t *tokens;
     float *x, *xa, *n, *q, *k, *v, *att, *proj, *gu, *act, *logits;
-    __half *h16;  // fp16 copy of whichever activation feeds the next tensor-core GEMM ([M, max(C, I)]; M > 16 only)
+    __half *h16;  // fp16 copy of whichever activation feeds the next tensor-core GEMM ([M, max(C, I)]; M > 8 only)
     int ldq, ldk, ldv, ld_gu;
 };
 

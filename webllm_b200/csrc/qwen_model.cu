@@ -76,7 +76,7 @@ int alloc_bufs(wb_qwen *m, int arena, int64_t M, int64_t logit_rows, Bufs *b)
     b->ld_gu = fused_gu ? 2 * I : I;
     WB_CHECK(carve_t(ctx, arena, M * I, &b->act));
     b->h16 = nullptr;
-    if (M > 16) WB_CHECK(carve_t(ctx, arena, M * (int64_t)std::max(C, I), &b->h16));
+    if (M > 8) WB_CHECK(carve_t(ctx, arena, M * (int64_t)std::max(C, I), &b->h16));
     WB_CHECK(carve_t(ctx, arena, logit_rows * m->V, &b->logits));
     return WB_OK;
 }
