@@ -37,7 +37,7 @@ def test_single_linear_benchmark_case(gpu, oracle):
 
 @pytest.mark.parametrize("name,K,N", [(n, k, nn) for n, (k, nn) in synthetic.QWEN05B_SHAPES.items() if n in ("q", "k", "gate", "down")]
                          + [("q7b", 3584, 3584), ("kv7b", 3584, 512), ("down7b", 18944, 3584)])
-@pytest.mark.parametrize("M", [1, 2, 3, 4, 8, 9, 16, 32])
+@pytest.mark.parametrize("M", [1, 2, 3, 4, 6, 8, 9, 16, 32])
 def test_small_batch_all_shapes(gpu, oracle, name, K, N, M):
     if K == 18944 and M not in (1, 8):
         pytest.skip("one small and one larger batch are enough at the largest K")

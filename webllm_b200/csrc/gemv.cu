@@ -680,7 +680,11 @@ static void plan_gemv_mma(wb_context *ctx, const Weight &w, int64_t M, int two_h
 {
     const int chunks = (int)((w.pack_rows + 15) / 16);
     const int col_tiles = (int)((w.N + 31) / 32);
-    int wn = M <= 2 ? 1 : (M <= 4 ? 2 : 4);
+    // Warps side by side along N (wn x 32 columns per CTA). Up to 8 rows ride in one MMA, so a wider CTA only pays where
+    // the matrix has both many column tiles and a long K (7B-class: 3584 -> 3584 at M = 6 took 7.7 us with wn = 4, 10.6 with
+    // wn = 1); on the 0.5B shapes narrow CTAs are 10 - 30 % faster at M = 5 .. 8 (down 4864 -> 896, M = 8: 8.1 -> 5.7 us).
+    const bool wide_and_long = col_tiles >= 100 && chunks >= 24;
+    int wn = M <= 2 ? 1 : M <= 4 ? 2 : M > 8 || wide_and_long ? 4 : M <= 6 ? 1 : 2;
     while (wn > 1 && col_tiles < wn) wn >>= 1;
     int wk = M <= 8 ? 8 / wn : 4;  // 256 threads up to 8 rows (3 CTAs per SM), 512 beyond
     if (wk > chunks) wk = chunks;
@@ -1027,7 +1031,11 @@ extern "C" int wb_gptq_gemv_static(const void *qweight, const void *qzeros, cons
 
     // launch shape: the regular planner's layout for M, the caller's (or a simple automatic) split
     const int pack_rows = (int)(K / 8), chunks = (pack_rows + 15) / 16, col_tiles = (int)((N + 31) / 32);
-    int wn = M <= 2 ? 1 : (M <= 4 ? 2 : 4);
+    // Warps side by side along N (wn x 32 columns per CTA). Up to 8 rows ride in one MMA, so a wider CTA only pays where
+    // the matrix has both many column tiles and a long K (7B-class: 3584 -> 3584 at M = 6 took 7.7 us with wn = 4, 10.6 with
+    // wn = 1); on the 0.5B shapes narrow CTAs are 10 - 30 % faster at M = 5 .. 8 (down 4864 -> 896, M = 8: 8.1 -> 5.7 us).
+    const bool wide_and_long = col_tiles >= 100 && chunks >= 24;
+    int wn = M <= 2 ? 1 : M <= 4 ? 2 : M > 8 || wide_and_long ? 4 : M <= 6 ? 1 : 2;
     while (wn > 1 && col_tiles < wn) wn >>= 1;
     int wk = M <= 8 ? 8 / wn : 4;
     if (wk > chunks) wk = chunks;
