@@ -913,6 +913,14 @@ int launch_linear(wb_context *ctx, const Weight &w, const void *A, void *C, cons
         p.cluster = gemv_cluster_merge(M, p.S) ? 1 : 0;
         // register path: one chunk per warp and one tile per CTA, at most one CTA per SM (see the kernel's comment)
         p.direct = (M <= 8 && (p.cluster || p.S == 1) && p.chunks_per_split <= p.wk && plan.grid_x * plan.grid_y <= ctx->sm_count) ? 1 : 0;
+        // a ring one slot shallower where that is what lets the launch fit one wave of resident CTAs (7B-class 3584 -> 3584 at
+        // M = 8 with f32 activations: 117 KB per CTA = one per SM and two waves, 13.6 us; 97 KB = two per SM)
+        auto waves_with = [&](int stages) {
+            const size_t sm = gemv_smem_bytes(M, p.chunks_per_split, ex_gemv, p.wn, p.wk, stages, nullptr, nullptr, p.cluster ? p.S : 0, nullptr);
+            const int gx = gemv_grid_x(ctx->sm_count, plan.grid_x, plan.grid_y, plan.block, sm);
+            return (plan.grid_x + gx - 1) / gx;
+        };
+        while (p.stages > 2 && waves_with(p.stages - 1) < waves_with(p.stages)) p.stages--;
         const size_t smem = gemv_smem_bytes(M, p.chunks_per_split, ex_gemv, p.wn, p.wk, p.stages, &p.ring_off, &p.red_off,
                                             p.cluster ? p.S : 0, &p.cl_off);
         if (smem > (size_t)kGemvSmemLimit) return fail(WB_ERR_UNSUPPORTED, "GEMV_MMA: activations do not fit shared memory");
