@@ -657,6 +657,12 @@ def run_ours(args) -> None:
     extras = {}
     if rank == 0:
         line["roofline"] = kernel_sections(gpu, clock, cfg, peaks)
+        # the same question for the whole step (all 125 launches, lm_head included), from the headline's own timing:
+        # weight bytes that one token has to stream / the measured step time
+        step_bytes = int4_bytes_per_token(cfg) + cfg.vocab_size * cfg.n_embd * 2
+        step_gbs = step_bytes / (line["ms_per_step"] * 1e-3) / 1e9
+        line["roofline"]["whole_step"] = {"algorithmic_bytes": step_bytes, "achieved": step_gbs, "unit": "GB/s",
+                                          "frac": step_gbs / peaks["hbm_gbs"], "hbm_floor_ms": step_bytes / peaks["hbm_gbs"] / 1e6}
     if not args.no_extras:
         if rank == 0:
             progress("extras: gemv")
