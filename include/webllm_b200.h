@@ -51,8 +51,10 @@ typedef enum { WB_ARENA_WEIGHTS = 0, WB_ARENA_ACT = 1 } wb_arena;
 
 /* Which kernel a linear call uses (see wb_plan_query). */
 typedef enum {
-    WB_KERNEL_GEMV_MMA = 1,   /* M <= 32: weights streamed once, register unpack, warp-level MMA, split-K */
-    WB_KERNEL_GEMM_TC = 2,    /* tcgen05 / TMEM GEMM, TMA-fed, dequant in shared memory */
+    WB_KERNEL_GEMV_MMA = 1,   /* M <= 32: weights streamed once, register unpack, warp-level MMA, split-K. The planner's
+                                 choice up to M = 8 (up to 12 / 16 with fp16 / f32 activations on short-K, wide-N shapes) */
+    WB_KERNEL_GEMM_TC = 2,    /* tcgen05 / TMEM GEMM, TMA-fed, dequant in shared memory; f32 activations are rounded to
+                                 fp16 first (as the reference's tiled GEMM stages them), never in exact mode */
     WB_KERNEL_GENERIC = 3,    /* shape-agnostic CUDA kernel for ragged sizes (K%8, N%4, group%32 != 0) */
     WB_KERNEL_DENSE_GEMV = 4, /* fp16 [N,K] weight, M <= 8 */
     WB_KERNEL_GEMV_STREAM = 5, /* M <= 4 on bandwidth-bound shapes (whole 128-k chunks, N % 32 == 0, >= 20 chunks per K
